@@ -1,0 +1,112 @@
+"""ctypes binding of ``libgrape_b200.so`` (the C ABI declared in ``include/grape_b200.h``).
+
+The library is the product: if it is missing or cannot be loaded this module raises, there is no
+Python or CPU stand-in for any entry point.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import re
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "libgrape_b200.so"
+HEADER = PKG.parent / "include" / "grape_b200.h"
+
+GRAPE_OK = 0
+ERR_NAMES = {1: "GRAPE_ERR_INVALID", 2: "GRAPE_ERR_CUDA", 3: "GRAPE_ERR_CHECK", 4: "GRAPE_ERR_NOMEM",
+             5: "GRAPE_ERR_LIMIT"}
+
+
+class GrapeError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"{ERR_NAMES.get(code, code)}: {msg}")
+        self.code = code
+
+
+def declared_symbols() -> list[str]:
+    """Names of every function the public header declares."""
+    text = HEADER.read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(grape_[a-z0-9_]+)\s*\(", text)))
+
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python grape_b200/csrc/build.py` (needs nvcc). "
+            "grape_b200 has no CPU fallback.")
+    lib = C.CDLL(str(LIB_PATH))
+    _declare(lib)
+    _lib = lib
+    return lib
+
+
+def _declare(lib):
+    vp, u64, u32, i32p = C.c_void_p, C.c_uint64, C.c_uint32, C.c_void_p
+    sz = C.c_size_t
+
+    def f(name, args, res=C.c_int):
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = res
+
+    f("grape_version", [])
+    f("grape_ctx_create", [C.c_int, C.POINTER(vp)])
+    f("grape_ctx_destroy", [vp])
+    f("grape_ctx_error", [vp], C.c_char_p)
+    f("grape_ctx_sync", [vp])
+    f("grape_ctx_stream", [vp], vp)
+    f("grape_ctx_launches", [vp], u64)
+    f("grape_ctx_status", [vp, C.POINTER(u32)])
+    f("grape_rng_seed", [vp, u64])
+    f("grape_rng_fr", [vp, vp, u64])
+    f("grape_dev_alloc", [vp, sz, C.POINTER(vp)])
+    f("grape_dev_free", [vp, vp])
+    f("grape_h2d", [vp, vp, vp, sz])
+    f("grape_d2h", [vp, vp, vp, sz])
+    f("grape_d2d", [vp, vp, vp, sz])
+    f("grape_dev_zero", [vp, vp, sz])
+    f("grape_host_alloc_pinned", [vp, sz, C.POINTER(vp)])
+    f("grape_host_free_pinned", [vp, vp])
+    f("grape_table_create", [vp, vp, u32, u32, u32, C.POINTER(vp)])
+    f("grape_table_from_reference", [vp, vp, u32, C.POINTER(vp)])
+    f("grape_table_destroy", [vp])
+    f("grape_table_bytes", [vp], u64)
+    f("grape_table_data", [vp], vp)
+    f("grape_commit_i32", [vp, vp, i32p, u64, u32, u32, vp])
+    f("grape_commit_fr", [vp, vp, vp, u64, u32, vp])
+    f("grape_commit_i32_host", [vp, vp, vp, u64, u32, u32, vp])
+    f("grape_fr_from_i32", [vp, vp, vp, u64])
+    f("grape_fr_from_u32", [vp, vp, vp, u64])
+    f("grape_fr_to_mont", [vp, vp, u64])
+    f("grape_fr_from_mont", [vp, vp, u64])
+    for name in ("grape_fr_add", "grape_fr_sub", "grape_fr_mul", "grape_fr_scale", "grape_fr_add_scalar"):
+        f(name, [vp, vp, vp, vp, u64])
+    f("grape_fp_binary", [vp, C.c_int, vp, vp, vp, u64])
+    f("grape_fr_axpy", [vp, vp, vp, vp, vp, u64])
+    f("grape_fr_inverse", [vp, vp, vp, vp, u64])
+    f("grape_pad_i32", [vp, vp, vp, u32, u32, u64])
+    f("grape_fr_pad", [vp, vp, vp, u32, u32, u64, vp])
+    f("grape_fr_sum", [vp, vp, u64, vp])
+    f("grape_fr_rowsum", [vp, vp, vp, u64, u32])
+    f("grape_fr_fold", [vp, vp, u64, vp, u32, u64, vp])
+    f("grape_fold_i32", [vp, vp, u64, vp, u32, u64, vp])
+    f("grape_measure_int_peak", [vp, C.c_int, C.POINTER(C.c_double)])
+    f("grape_timer_begin", [vp])
+    f("grape_timer_end", [vp, C.POINTER(C.c_float)])
+    f("grape_prof_enable", [vp, C.c_int])
+    f("grape_prof_read", [vp, C.POINTER(C.c_float), C.POINTER(u32)])
+    for name in _OPTIONAL:
+        if hasattr(lib, name):
+            f(name, _OPTIONAL[name])
+
+
+# entry points added by later parts of the library register their signatures here
+_OPTIONAL: dict[str, list] = {}

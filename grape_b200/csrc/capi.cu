@@ -1,0 +1,192 @@
+// Context, memory and RNG entry points of the C ABI.
+#include <cstring>
+#include <vector>
+
+#include "ctx.cuh"
+#include "hostfr.hpp"
+
+using namespace grape;
+
+extern "C" int grape_version(void) { return 1; }
+
+extern "C" int grape_ctx_create(int device, grape_ctx** out) {
+  if (!out) return GRAPE_ERR_INVALID;
+  *out = nullptr;
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0 || device < 0 || device >= n)
+    return GRAPE_ERR_CUDA;  // no usable GPU: there is deliberately no CPU fallback
+  grape_ctx* ctx = new grape_ctx();
+  ctx->device = device;
+  if (cudaSetDevice(device) != cudaSuccess ||
+      cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+    delete ctx;
+    return GRAPE_ERR_CUDA;
+  }
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) == cudaSuccess) ctx->sm_count = prop.multiProcessorCount;
+  if (cudaMalloc(&ctx->d_status, 64) != cudaSuccess) {
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return GRAPE_ERR_NOMEM;
+  }
+  cudaMemsetAsync(ctx->d_status, 0, 64, ctx->stream);
+  ctx->rng_state = splitmix_init(0, 0);
+  *out = ctx;
+  return GRAPE_OK;
+}
+
+extern "C" int grape_ctx_destroy(grape_ctx* ctx) {
+  if (!ctx) return GRAPE_OK;
+  cudaSetDevice(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  for (auto& b : ctx->arena) cudaFree(b.ptr);
+  if (ctx->dstage) cudaFree(ctx->dstage);
+  if (ctx->pinned) cudaFreeHost(ctx->pinned);
+  if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->t0) { cudaEventDestroy(ctx->t0); cudaEventDestroy(ctx->t1); }
+  for (auto& pr : ctx->prof_events) { cudaEventDestroy(pr.first); cudaEventDestroy(pr.second); }
+  cudaStreamDestroy(ctx->stream);
+  delete ctx;
+  return GRAPE_OK;
+}
+
+extern "C" const char* grape_ctx_error(const grape_ctx* ctx) { return ctx ? ctx->err.c_str() : "null context"; }
+
+extern "C" int grape_ctx_sync(grape_ctx* ctx) {
+  if (!ctx) return GRAPE_ERR_INVALID;
+  GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  return GRAPE_OK;
+}
+
+extern "C" void* grape_ctx_stream(grape_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+
+extern "C" uint64_t grape_ctx_launches(const grape_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+extern "C" int grape_ctx_status(grape_ctx* ctx, uint32_t* flags) {
+  if (!ctx || !flags) return GRAPE_ERR_INVALID;
+  uint32_t h = 0;
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(&h, ctx->d_status, 4, cudaMemcpyDeviceToHost, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  if (h) GRAPE_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, 4, ctx->stream));
+  *flags = h;
+  return GRAPE_OK;
+}
+
+extern "C" int grape_rng_seed(grape_ctx* ctx, uint64_t seed) {
+  if (!ctx) return GRAPE_ERR_INVALID;
+  ctx->rng_state = splitmix_init(seed, 0);
+  return GRAPE_OK;
+}
+
+extern "C" int grape_rng_fr(grape_ctx* ctx, void* h_out, uint64_t n) {
+  if (!ctx || (!h_out && n)) return GRAPE_ERR_INVALID;
+  HostFr* o = reinterpret_cast<HostFr*>(h_out);
+  for (uint64_t i = 0; i < n; i++) o[i] = rng_next_fr(ctx->rng_state);
+  return GRAPE_OK;
+}
+
+extern "C" int grape_dev_alloc(grape_ctx* ctx, size_t bytes, void** d_out) {
+  if (!ctx || !d_out) return GRAPE_ERR_INVALID;
+  *d_out = nullptr;
+  if (bytes == 0) return GRAPE_OK;
+  cudaError_t e = cudaMalloc(d_out, bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(ctx, GRAPE_ERR_NOMEM, std::string("cudaMalloc: ") + cudaGetErrorString(e));
+  }
+  return GRAPE_OK;
+}
+
+extern "C" int grape_dev_free(grape_ctx* ctx, void* d_ptr) {
+  if (!ctx) return GRAPE_ERR_INVALID;
+  if (!d_ptr) return GRAPE_OK;
+  GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaFree(d_ptr));
+  return GRAPE_OK;
+}
+
+extern "C" int grape_h2d(grape_ctx* ctx, void* d_dst, const void* h_src, size_t bytes) {
+  if (!ctx) return GRAPE_ERR_INVALID;
+  if (bytes == 0) return GRAPE_OK;
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+  // pageable sources are staged by the runtime before the call returns; pinned ones are not,
+  // so callers that reuse a pinned source must grape_ctx_sync() first.
+  return GRAPE_OK;
+}
+
+extern "C" int grape_d2h(grape_ctx* ctx, void* h_dst, const void* d_src, size_t bytes) {
+  if (!ctx) return GRAPE_ERR_INVALID;
+  if (bytes)
+    GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  return GRAPE_OK;
+}
+
+extern "C" int grape_d2d(grape_ctx* ctx, void* d_dst, const void* d_src, size_t bytes) {
+  if (!ctx) return GRAPE_ERR_INVALID;
+  if (bytes)
+    GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_dst, d_src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+  return GRAPE_OK;
+}
+
+extern "C" int grape_dev_zero(grape_ctx* ctx, void* d_dst, size_t bytes) {
+  if (!ctx) return GRAPE_ERR_INVALID;
+  if (bytes) GRAPE_CUDA_TRY(ctx, cudaMemsetAsync(d_dst, 0, bytes, ctx->stream));
+  return GRAPE_OK;
+}
+
+extern "C" int grape_host_alloc_pinned(grape_ctx* ctx, size_t bytes, void** h_out) {
+  if (!ctx || !h_out) return GRAPE_ERR_INVALID;
+  cudaError_t e = cudaMallocHost(h_out, bytes);
+  if (e != cudaSuccess) return fail(ctx, GRAPE_ERR_NOMEM, "cudaMallocHost failed");
+  return GRAPE_OK;
+}
+
+extern "C" int grape_host_free_pinned(grape_ctx* ctx, void* h_ptr) {
+  if (!ctx) return GRAPE_ERR_INVALID;
+  if (h_ptr) GRAPE_CUDA_TRY(ctx, cudaFreeHost(h_ptr));
+  return GRAPE_OK;
+}
+
+// ---- timing helpers (CUDA events on the context's stream) --------------------------------------
+extern "C" int grape_timer_begin(grape_ctx* ctx) {
+  if (!ctx) return GRAPE_ERR_INVALID;
+  if (!ctx->t0) {
+    GRAPE_CUDA_TRY(ctx, cudaEventCreate(&ctx->t0));
+    GRAPE_CUDA_TRY(ctx, cudaEventCreate(&ctx->t1));
+  }
+  GRAPE_CUDA_TRY(ctx, cudaEventRecord(ctx->t0, ctx->stream));
+  return GRAPE_OK;
+}
+
+extern "C" int grape_timer_end(grape_ctx* ctx, float* ms) {
+  if (!ctx || !ms || !ctx->t0) return GRAPE_ERR_INVALID;
+  GRAPE_CUDA_TRY(ctx, cudaEventRecord(ctx->t1, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaEventSynchronize(ctx->t1));
+  GRAPE_CUDA_TRY(ctx, cudaEventElapsedTime(ms, ctx->t0, ctx->t1));
+  return GRAPE_OK;
+}
+
+extern "C" int grape_prof_enable(grape_ctx* ctx, int on) {
+  if (!ctx) return GRAPE_ERR_INVALID;
+  ctx->profile = on != 0;
+  return GRAPE_OK;
+}
+
+// Sums and clears the recorded dominant-kernel intervals.
+extern "C" int grape_prof_read(grape_ctx* ctx, float* total_ms, uint32_t* count) {
+  if (!ctx || !total_ms || !count) return GRAPE_ERR_INVALID;
+  GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  float sum = 0;
+  for (auto& pr : ctx->prof_events) {
+    float ms = 0;
+    cudaEventElapsedTime(&ms, pr.first, pr.second);
+    sum += ms;
+    cudaEventDestroy(pr.first);
+    cudaEventDestroy(pr.second);
+  }
+  *total_ms = sum;
+  *count = (uint32_t)ctx->prof_events.size();
+  ctx->prof_events.clear();
+  return GRAPE_OK;
+}

@@ -1,0 +1,142 @@
+// Internal definitions behind the opaque handles of the C ABI.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <vector>
+
+#include "../../include/grape_b200.h"
+
+struct grape_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  // scratch arena: a bump allocator over a few device blocks.  A top-level call resets it,
+  // carves what its kernels need, and the next call on the stream reuses the same memory.
+  struct ArenaBlock { void* ptr; size_t size; size_t off; };
+  std::vector<ArenaBlock> arena;
+  // pinned staging buffer for the host-buffer entry points
+  void* pinned = nullptr;
+  size_t pinned_bytes = 0;
+  void* dstage = nullptr;
+  size_t dstage_bytes = 0;
+  uint64_t rng_state = 0;
+  // device status word: kernels OR a GRAPE_STATUS_* bit into it instead of trapping
+  uint32_t* d_status = nullptr;
+  std::string err;
+  int sm_count = 148;
+  // launch counters (own kernels launched since creation), read by the benchmark
+  uint64_t launches = 0;
+  // wall-clock bracket on the stream (grape_timer_begin / grape_timer_end)
+  cudaEvent_t t0 = nullptr, t1 = nullptr;
+  // optional per-kernel timing of the dominant kernel of a call (commit_accumulate, ...):
+  // event pairs recorded around it while `profile` is set, summed by grape_prof_read
+  bool profile = false;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof_events;
+};
+
+struct grape_table {
+  grape_ctx* ctx = nullptr;
+  void* data = nullptr;  // affine records
+  bool owned = false;
+  uint32_t n_gens = 0;
+  uint32_t window_bits = 8;
+  uint32_t n_windows = 1;
+  uint32_t n_digits = 128;      // addressable magnitudes per window: 1..n_digits
+  uint64_t window_stride = 0;   // records between consecutive windows
+  uint32_t first_digit_row = 0; // row holding magnitude 1 (1 for the reference's 256-row layout)
+};
+
+namespace grape {
+
+// Brackets the dominant kernel of a call with events when profiling is on.
+struct ProfScope {
+  grape_ctx* ctx;
+  cudaEvent_t a = nullptr, b = nullptr;
+  explicit ProfScope(grape_ctx* c) : ctx(c) {
+    if (ctx->profile) {
+      cudaEventCreate(&a);
+      cudaEventCreate(&b);
+      cudaEventRecord(a, ctx->stream);
+    }
+  }
+  ~ProfScope() {
+    if (a) {
+      cudaEventRecord(b, ctx->stream);
+      ctx->prof_events.push_back({a, b});
+    }
+  }
+};
+
+constexpr uint32_t STATUS_DIGIT_RANGE = 1u;  // a scalar exceeded the declared max_bits
+constexpr uint32_t STATUS_HIST_RANGE = 2u;   // a lookup query fell outside the table
+
+inline int fail(grape_ctx* ctx, int code, const std::string& msg) {
+  if (ctx) ctx->err = msg;
+  return code;
+}
+
+#define GRAPE_CUDA_TRY(ctx, expr)                                                         \
+  do {                                                                                    \
+    cudaError_t _e = (expr);                                                              \
+    if (_e != cudaSuccess) {                                                              \
+      return grape::fail((ctx), GRAPE_ERR_CUDA,                                           \
+                         std::string(#expr) + ": " + cudaGetErrorString(_e));             \
+    }                                                                                     \
+  } while (0)
+
+// Starts a new top-level call: everything handed out before is up for reuse (stream order keeps
+// earlier kernels safe).  Several blocks left by a call that outgrew the arena are merged into one.
+inline int arena_reset(grape_ctx* ctx) {
+  if (ctx->arena.size() > 1) {
+    GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    size_t total = 0;
+    for (auto& b : ctx->arena) { total += b.size; cudaFree(b.ptr); }
+    ctx->arena.clear();
+    void* p = nullptr;
+    if (cudaMalloc(&p, total) == cudaSuccess) ctx->arena.push_back({p, total, 0});
+    else cudaGetLastError();
+  }
+  for (auto& b : ctx->arena) b.off = 0;
+  return GRAPE_OK;
+}
+
+// Hands out `bytes` of scratch (256-byte aligned), adding a device block when the arena is full.
+inline int arena_alloc(grape_ctx* ctx, size_t bytes, void** out) {
+  bytes = (bytes + 255) & ~size_t(255);
+  if (bytes == 0) bytes = 256;
+  for (auto& b : ctx->arena) {
+    if (b.off + bytes <= b.size) {
+      *out = reinterpret_cast<char*>(b.ptr) + b.off;
+      b.off += bytes;
+      return GRAPE_OK;
+    }
+  }
+  size_t want = bytes < (size_t(32) << 20) ? (size_t(32) << 20) : bytes;
+  void* p = nullptr;
+  if (cudaMalloc(&p, want) != cudaSuccess) {
+    cudaGetLastError();
+    return fail(ctx, GRAPE_ERR_NOMEM, "scratch arena allocation failed");
+  }
+  ctx->arena.push_back({p, want, bytes});
+  *out = p;
+  return GRAPE_OK;
+}
+
+template <class T>
+inline int arena_alloc_t(grape_ctx* ctx, size_t count, T** out) {
+  void* p = nullptr;
+  int rc = arena_alloc(ctx, count * sizeof(T), &p);
+  *out = reinterpret_cast<T*>(p);
+  return rc;
+}
+
+inline uint32_t log2ceil(uint64_t n) {  // the reference's Log2 (src/ioutils.cu:173-190)
+  if (n == 0) return 0;
+  n--;
+  uint32_t r = 0;
+  while (n > 0) { n >>= 1; r++; }
+  return r;
+}
+
+}  // namespace grape

@@ -1,0 +1,110 @@
+// Measured integer-pipe ceilings used as roofline denominators for the multiplication-bound
+// kernels: dependent-free multiply-add loops at full occupancy, timed with CUDA events.
+//   kind 0: mad.lo.u32           (32-bit multiply-add, one result word)
+//   kind 1: mad.wide.u32         (32x32 -> 64-bit multiply-add)
+//   kind 2: mad.lo.cc + madc.hi  (the lo/hi pair form the field arithmetic is written in)
+//   kind 3: Montgomery multiplications in Fp (field muls per second)
+#include "ctx.cuh"
+#include "field.cuh"
+
+namespace grape {
+
+constexpr int PEAK_ITERS = 2048;
+constexpr int PEAK_CHAINS = 8;
+
+template <int KIND>
+__global__ void __launch_bounds__(256) k_int_peak(uint32_t* sink, uint32_t seed) {
+  uint32_t a = seed + threadIdx.x, b = seed * 3 + blockIdx.x;
+  if (KIND == 0) {
+    uint32_t acc[PEAK_CHAINS];
+#pragma unroll
+    for (int k = 0; k < PEAK_CHAINS; k++) acc[k] = a + k;
+    for (int it = 0; it < PEAK_ITERS; it++) {
+#pragma unroll
+      for (int k = 0; k < PEAK_CHAINS; k++)
+        asm volatile("mad.lo.u32 %0, %1, %2, %0;" : "+r"(acc[k]) : "r"(a), "r"(b));
+    }
+    uint32_t s = 0;
+#pragma unroll
+    for (int k = 0; k < PEAK_CHAINS; k++) s ^= acc[k];
+    if (s == 0x12345) sink[0] = s;
+  } else if (KIND == 1) {
+    unsigned long long acc[PEAK_CHAINS];
+#pragma unroll
+    for (int k = 0; k < PEAK_CHAINS; k++) acc[k] = a + k;
+    for (int it = 0; it < PEAK_ITERS; it++) {
+#pragma unroll
+      for (int k = 0; k < PEAK_CHAINS; k++)
+        asm volatile("mad.wide.u32 %0, %1, %2, %0;" : "+l"(acc[k]) : "r"(a), "r"(b));
+    }
+    unsigned long long s = 0;
+#pragma unroll
+    for (int k = 0; k < PEAK_CHAINS; k++) s ^= acc[k];
+    if (s == 0x12345) sink[0] = (uint32_t)s;
+  } else if (KIND == 2) {
+    uint32_t lo[PEAK_CHAINS], hi[PEAK_CHAINS];
+#pragma unroll
+    for (int k = 0; k < PEAK_CHAINS; k++) { lo[k] = a + k; hi[k] = b + k; }
+    for (int it = 0; it < PEAK_ITERS; it++) {
+#pragma unroll
+      for (int k = 0; k < PEAK_CHAINS; k++)
+        asm volatile("mad.lo.cc.u32 %0, %2, %3, %0;\n\tmadc.hi.u32 %1, %2, %3, %1;"
+                     : "+r"(lo[k]), "+r"(hi[k]) : "r"(a), "r"(b));
+    }
+    uint32_t s = 0;
+#pragma unroll
+    for (int k = 0; k < PEAK_CHAINS; k++) s ^= lo[k] ^ hi[k];
+    if (s == 0x12345) sink[0] = s;
+  } else {
+    Fp x[2], y;
+#pragma unroll
+    for (int i = 0; i < 8; i++) { x[0].v[i] = a + i; x[1].v[i] = b + i; y.v[i] = (a ^ b) + i; }
+    x[0].v[7] &= 0x0fffffffu; x[1].v[7] &= 0x0fffffffu; y.v[7] &= 0x0fffffffu;
+    for (int it = 0; it < PEAK_ITERS / 8; it++) {
+      x[0] = fe_mul(x[0], y);
+      x[1] = fe_mul(x[1], y);
+    }
+    if (x[0].v[0] == 0x12345 && x[1].v[3] == 7) sink[0] = x[0].v[1];
+  }
+}
+
+}  // namespace grape
+
+using namespace grape;
+
+// Writes operations per second: kinds 0-2 count multiply-add instructions (a lo/hi pair counts 2),
+// kind 3 counts field multiplications.
+extern "C" int grape_measure_int_peak(grape_ctx* ctx, int kind, double* ops_per_second) {
+  if (!ctx || !ops_per_second || kind < 0 || kind > 3) return GRAPE_ERR_INVALID;
+  arena_reset(ctx);
+  uint32_t* sink = nullptr;
+  int rc = arena_alloc_t(ctx, 64, &sink);
+  if (rc) return rc;
+  const int blocks = ctx->sm_count * 8, threads = 256;
+  cudaEvent_t e0, e1;
+  GRAPE_CUDA_TRY(ctx, cudaEventCreate(&e0));
+  GRAPE_CUDA_TRY(ctx, cudaEventCreate(&e1));
+  float best = 1e30f;
+  for (int rep = 0; rep < 4; rep++) {
+    cudaEventRecord(e0, ctx->stream);
+    if (kind == 0) k_int_peak<0><<<blocks, threads, 0, ctx->stream>>>(sink, rep + 1);
+    else if (kind == 1) k_int_peak<1><<<blocks, threads, 0, ctx->stream>>>(sink, rep + 1);
+    else if (kind == 2) k_int_peak<2><<<blocks, threads, 0, ctx->stream>>>(sink, rep + 1);
+    else k_int_peak<3><<<blocks, threads, 0, ctx->stream>>>(sink, rep + 1);
+    cudaEventRecord(e1, ctx->stream);
+    ctx->launches += 1;
+    GRAPE_CUDA_TRY(ctx, cudaEventSynchronize(e1));
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    if (rep > 0 && ms < best) best = ms;
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  GRAPE_CUDA_TRY(ctx, cudaGetLastError());
+  double per_thread;
+  if (kind == 0 || kind == 1) per_thread = (double)PEAK_ITERS * PEAK_CHAINS;
+  else if (kind == 2) per_thread = 2.0 * PEAK_ITERS * PEAK_CHAINS;
+  else per_thread = 2.0 * (PEAK_ITERS / 8);
+  *ops_per_second = per_thread * blocks * threads / (best * 1e-3);
+  return GRAPE_OK;
+}

@@ -1,0 +1,428 @@
+// Field-tensor kernels over BN254 Fr (device arrays of 32-byte Montgomery residues).
+//
+// Replaces the FrTensor runtime of the reference (src/fr-tensor.cu): int -> Fr conversion
+// (:30-46), Montgomery in/out (:110-120), element-wise and broadcast arithmetic (:74-108),
+// inversion (:122-126), padding (:18-28), tree sum (:128-153, 415-440), row sums (:155-163) and
+// the multilinear fold (:53-72, 168-188, 330-344).
+//
+// Differences in mechanism, not in results: kernels are grid-stride and sized to the SM count,
+// loads/stores are 16-byte vectors, inversion is batched (Montgomery's trick across a block, one
+// field inversion per 2048 elements), and the fold of an axis is a single pass that multiplies
+// by a table of eq-weights instead of log2(c) in-place passes.
+#include "ctx.cuh"
+#include <algorithm>
+#include "field.cuh"
+
+namespace grape {
+
+constexpr int EW_THREADS = 256;
+
+static inline uint32_t ew_blocks(const grape_ctx* ctx, uint64_t n) {
+  uint64_t b = (n + EW_THREADS - 1) / EW_THREADS;
+  uint64_t cap = (uint64_t)ctx->sm_count * 16;
+  if (b > cap) b = cap;
+  if (b == 0) b = 1;
+  return (uint32_t)b;
+}
+
+#define GRID_STRIDE(i, n) \
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < (n); i += (uint64_t)gridDim.x * blockDim.x)
+
+__global__ void k_from_i32(const int32_t* __restrict__ in, uint32_t* __restrict__ out, uint64_t n) {
+  GRID_STRIDE(i, n) fe_from_i32<FrParams>(__ldg(in + i)).store(out + i * 8);
+}
+__global__ void k_from_u32(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, uint64_t n) {
+  GRID_STRIDE(i, n) fe_from_u32<FrParams>(__ldg(in + i)).store(out + i * 8);
+}
+__global__ void k_to_mont(uint32_t* t, uint64_t n) {
+  GRID_STRIDE(i, n) fe_to_mont(Fr::load(t + i * 8)).store(t + i * 8);
+}
+__global__ void k_from_mont(uint32_t* t, uint64_t n) {
+  GRID_STRIDE(i, n) fe_from_mont(Fr::load(t + i * 8)).store(t + i * 8);
+}
+
+template <int OP, class F>
+__global__ void k_binary(const uint32_t* a, const uint32_t* b, uint32_t* out, uint64_t n) {
+  GRID_STRIDE(i, n) {
+    F x = F::load(a + i * 8), y = F::load(b + i * 8);
+    F r = OP == 0 ? fe_add(x, y) : OP == 1 ? fe_sub(x, y) : fe_mul(x, y);
+    r.store(out + i * 8);
+  }
+}
+
+// out = a (op) s[0], s a device scalar
+template <int OP>
+__global__ void k_broadcast(const uint32_t* a, const uint32_t* __restrict__ s, uint32_t* out, uint64_t n) {
+  Fr y = Fr::load_nc(s);
+  GRID_STRIDE(i, n) {
+    Fr x = Fr::load(a + i * 8);
+    Fr r = OP == 0 ? fe_add(x, y) : fe_mul(x, y);
+    r.store(out + i * 8);
+  }
+}
+
+// out = a * s[0] + b     (z = c*x + d of the opening, src/Hyrax.cu:281-284)
+__global__ void k_axpy(const uint32_t* a, const uint32_t* __restrict__ s, const uint32_t* b,
+                       uint32_t* out, uint64_t n) {
+  Fr y = Fr::load_nc(s);
+  GRID_STRIDE(i, n) fe_add(fe_mul(Fr::load(a + i * 8), y), Fr::load(b + i * 8)).store(out + i * 8);
+}
+
+// Row padding: out[g] = (g % pad_n < n) ? in[(g / pad_n) * n + g % pad_n] : pad
+__global__ void k_pad_i32(const int32_t* __restrict__ in, int32_t* __restrict__ out, uint32_t n,
+                          uint32_t pad_n, uint64_t size) {
+  GRID_STRIDE(g, size) {
+    uint64_t r = g / pad_n, c = g % pad_n;
+    out[g] = c < n ? __ldg(in + r * n + c) : 0;
+  }
+}
+__global__ void k_pad_fr(const uint32_t* __restrict__ in, uint32_t* __restrict__ out, uint32_t n,
+                         uint32_t pad_n, uint64_t size, const uint32_t* __restrict__ pad) {
+  Fr pv = Fr::load_nc(pad);
+  GRID_STRIDE(g, size) {
+    uint64_t r = g / pad_n, c = g % pad_n;
+    Fr v = c < n ? Fr::load_nc(in + (r * n + c) * 8) : pv;
+    v.store(out + g * 8);
+  }
+}
+
+// ---- batched inversion --------------------------------------------------------------------
+// out[i] = 1 / (in[i] + shift[0]); an element whose shifted value is zero maps to zero.
+// Montgomery's trick per thread: thread t owns elements t, t+G, t+2G, ... (G = threads in the
+// grid, so every access is coalesced), writes the running product before each element to scratch,
+// inverts its total once, and unwinds in reverse.  About 3 multiplications per element plus one
+// inversion per thread; `in` and `out` may be the same buffer.
+__global__ void __launch_bounds__(128)
+k_batch_inverse(const uint32_t* in, const uint32_t* __restrict__ shift, uint32_t* out,
+                uint32_t* __restrict__ prefix, uint64_t n) {
+  const uint64_t G = (uint64_t)gridDim.x * blockDim.x;
+  const uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n) return;
+  const Fr sh = shift ? Fr::load_nc(shift) : Fr::zero();
+  Fr run = Fr::one();
+  uint64_t i = t;
+  for (; i < n; i += G) {
+    Fr v = fe_add(Fr::load(in + i * 8), sh);
+    run.store(prefix + i * 8);
+    if (!v.is_zero()) run = fe_mul(run, v);
+  }
+  Fr inv = fe_inv(run);
+  // i is now the first index past the end for this thread; walk back
+  while (i >= G + t) {
+    i -= G;
+    Fr v = fe_add(Fr::load(in + i * 8), sh);
+    if (v.is_zero()) {
+      Fr::zero().store(out + i * 8);
+    } else {
+      fe_mul(inv, Fr::load(prefix + i * 8)).store(out + i * 8);
+      inv = fe_mul(inv, v);
+    }
+  }
+}
+
+// ---- sums -----------------------------------------------------------------------------------
+constexpr int SUM_THREADS = 256;
+
+__device__ __forceinline__ Fr block_sum(Fr acc) {
+  __shared__ Fr warp_part[SUM_THREADS / 32];
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc = fe_add(acc, fe_shfl_down(acc, off));
+  if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = acc;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    Fr v = threadIdx.x < (blockDim.x >> 5) ? warp_part[threadIdx.x] : Fr::zero();
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = fe_add(v, fe_shfl_down(v, off));
+    acc = v;
+  }
+  __syncthreads();
+  return acc;  // valid in thread 0
+}
+
+__global__ void __launch_bounds__(SUM_THREADS) k_sum_partial(const uint32_t* __restrict__ in, uint64_t n,
+                                                             uint32_t* __restrict__ partial) {
+  Fr acc = Fr::zero();
+  GRID_STRIDE(i, n) acc = fe_add(acc, Fr::load_nc(in + i * 8));
+  acc = block_sum(acc);
+  if (threadIdx.x == 0) acc.store(partial + (uint64_t)blockIdx.x * 8);
+}
+
+// Row sums broadcast back over the row (softmax denominator; reference sum_by_dim_kernel,
+// src/fr-tensor.cu:155-163).  One warp per row.
+__global__ void k_rowsum_broadcast(const uint32_t* __restrict__ in, uint32_t* __restrict__ out,
+                                   uint64_t rows, uint32_t dim) {
+  uint64_t warp = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  uint32_t lane = threadIdx.x & 31;
+  uint64_t nwarps = ((uint64_t)gridDim.x * blockDim.x) >> 5;
+  for (uint64_t r = warp; r < rows; r += nwarps) {
+    Fr acc = Fr::zero();
+    for (uint32_t i = lane; i < dim; i += 32) acc = fe_add(acc, Fr::load_nc(in + (r * dim + i) * 8));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc = fe_add(acc, fe_shfl_xor(acc, off));
+    for (uint32_t i = lane; i < dim; i += 32) acc.store(out + (r * dim + i) * 8);
+  }
+}
+
+// ---- multilinear fold ---------------------------------------------------------------------
+// eq-weights of an axis of length c under challenges x[0..nv):  w[j] = prod_k (bit_k(j) ? x_k : 1 - x_k)
+__global__ void k_eq_weights(const uint32_t* __restrict__ x, uint32_t nv, uint32_t c,
+                             uint32_t* __restrict__ w) {
+  GRID_STRIDE(j, c) {
+    Fr acc = Fr::one();
+    for (uint32_t k = 0; k < nv; k++) {
+      Fr xk = Fr::load_nc(x + (uint64_t)k * 8);
+      Fr f = ((j >> k) & 1) ? xk : fe_sub(Fr::one(), xk);
+      acc = fe_mul(acc, f);
+    }
+    acc.store(w + j * 8);
+  }
+}
+
+// out[o][g] (+)= sum_{j in slice} w[j] * t[o][j][g].   grid.x tiles the outputs, grid.y splits j.
+// With one j-slice the result goes straight to `out`, otherwise to partial[slice][o*gap+g].
+constexpr int FOLD_THREADS = 128;
+template <bool FROM_I32>
+__global__ void __launch_bounds__(FOLD_THREADS)
+k_fold_axis(const void* __restrict__ t, const uint32_t* __restrict__ w, uint32_t c, uint64_t gap,
+            uint64_t n_out, uint32_t slice_len, uint32_t* __restrict__ dst) {
+  const uint64_t og = (uint64_t)blockIdx.x * FOLD_THREADS + threadIdx.x;
+  if (og >= n_out) return;
+  const uint64_t o = og / gap, g = og % gap;
+  const uint32_t j0 = blockIdx.y * slice_len;
+  const uint32_t j1 = min(c, j0 + slice_len);
+  Fr acc = Fr::zero();
+  for (uint32_t j = j0; j < j1; j++) {
+    const uint64_t idx = (o * c + j) * gap + g;
+    Fr v;
+    if (FROM_I32) v = fe_from_i32<FrParams>(__ldg(reinterpret_cast<const int32_t*>(t) + idx));
+    else v = Fr::load_nc(reinterpret_cast<const uint32_t*>(t) + idx * 8);
+    acc = fe_add(acc, fe_mul(v, Fr::load_nc(w + (uint64_t)j * 8)));
+  }
+  acc.store(dst + ((uint64_t)blockIdx.y * n_out + og) * 8);
+}
+
+// out[i] = sum_s partial[s][i]
+__global__ void k_sum_slices(const uint32_t* __restrict__ partial, uint32_t n_slices, uint64_t n,
+                             uint32_t* __restrict__ out) {
+  GRID_STRIDE(i, n) {
+    Fr acc = Fr::load_nc(partial + i * 8);
+    for (uint32_t s = 1; s < n_slices; s++) acc = fe_add(acc, Fr::load_nc(partial + ((uint64_t)s * n + i) * 8));
+    acc.store(out + i * 8);
+  }
+}
+
+// Innermost-axis fold (gap == 1): out[o] = sum_j w[j] * t[o*c + j], one block per o.
+template <bool FROM_I32>
+__global__ void __launch_bounds__(SUM_THREADS)
+k_fold_inner(const void* __restrict__ t, const uint32_t* __restrict__ w, uint32_t c,
+             uint32_t* __restrict__ out) {
+  const uint64_t o = blockIdx.x;
+  Fr acc = Fr::zero();
+  for (uint32_t j = threadIdx.x; j < c; j += SUM_THREADS) {
+    const uint64_t idx = o * c + j;
+    Fr v;
+    if (FROM_I32) v = fe_from_i32<FrParams>(__ldg(reinterpret_cast<const int32_t*>(t) + idx));
+    else v = Fr::load_nc(reinterpret_cast<const uint32_t*>(t) + idx * 8);
+    acc = fe_add(acc, fe_mul(v, Fr::load_nc(w + (uint64_t)j * 8)));
+  }
+  acc = block_sum(acc);
+  if (threadIdx.x == 0) acc.store(out + o * 8);
+}
+
+// ---- host-side launch helpers shared with the provers ---------------------------------------
+// d_out = sum of n elements.  Uses its own arena allocation for the per-block partial sums.
+int fr_sum_async(grape_ctx* ctx, const void* d_in, uint64_t n, void* d_out) {
+  uint32_t blocks = ew_blocks(ctx, n);
+  if (blocks > 1024) blocks = 1024;
+  void* scratch;
+  int rc = arena_alloc(ctx, (size_t)blocks * 32, &scratch);
+  if (rc) return rc;
+  k_sum_partial<<<blocks, SUM_THREADS, 0, ctx->stream>>>((const uint32_t*)d_in, n, (uint32_t*)scratch);
+  k_sum_partial<<<1, SUM_THREADS, 0, ctx->stream>>>((const uint32_t*)scratch, blocks, (uint32_t*)d_out);
+  ctx->launches += 2;
+  GRAPE_CUDA_TRY(ctx, cudaGetLastError());
+  return GRAPE_OK;
+}
+
+// Folds axis c of the [other][c][gap] view of d_t with challenges d_x[0..log2ceil(c)) into d_out
+// ([other][gap]).  d_out must not alias d_t.  scratch_off: bytes of the arena the caller already uses.
+template <bool FROM_I32>
+int fold_axis_async(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* d_x, uint32_t c,
+                    uint64_t gap, void* d_out) {
+  if (c == 0 || gap == 0 || ntot % ((uint64_t)c * gap) != 0)
+    return fail(ctx, GRAPE_ERR_INVALID, "fold: size is not a multiple of c*gap");
+  const uint64_t other = ntot / ((uint64_t)c * gap);
+  const uint64_t n_out = other * gap;
+  const uint32_t nv = log2ceil(c);
+  // work area: eq weights (c) + slice partials
+  uint32_t n_slices = 1;
+  if (gap > 1) {
+    uint64_t out_blocks = (n_out + FOLD_THREADS - 1) / FOLD_THREADS;
+    uint64_t target = (uint64_t)ctx->sm_count * 8;
+    if (out_blocks < target) n_slices = (uint32_t)std::min<uint64_t>((target + out_blocks - 1) / out_blocks, (c + 15) / 16);
+    if (n_slices < 1) n_slices = 1;
+  }
+  size_t w_bytes = ((size_t)c * 32 + 255) & ~size_t(255);
+  size_t p_bytes = n_slices > 1 ? (size_t)n_slices * n_out * 32 : 0;
+  void* d_work = nullptr;
+  int arc = arena_alloc(ctx, w_bytes + p_bytes, &d_work);
+  if (arc) return arc;
+  uint32_t* w = reinterpret_cast<uint32_t*>(d_work);
+  uint32_t* partial = reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(d_work) + w_bytes);
+  k_eq_weights<<<ew_blocks(ctx, c), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_x, nv, c, w);
+  ctx->launches += 1;
+  if (gap == 1) {
+    if (other > 0x7fffffffull) return fail(ctx, GRAPE_ERR_LIMIT, "fold: too many rows");
+    k_fold_inner<FROM_I32><<<(uint32_t)other, SUM_THREADS, 0, ctx->stream>>>(d_t, w, c, (uint32_t*)d_out);
+    ctx->launches += 1;
+  } else {
+    uint32_t slice_len = (c + n_slices - 1) / n_slices;
+    dim3 grid((uint32_t)((n_out + FOLD_THREADS - 1) / FOLD_THREADS), n_slices);
+    k_fold_axis<FROM_I32><<<grid, FOLD_THREADS, 0, ctx->stream>>>(
+        d_t, w, c, gap, n_out, slice_len, n_slices > 1 ? partial : (uint32_t*)d_out);
+    ctx->launches += 1;
+    if (n_slices > 1) {
+      k_sum_slices<<<ew_blocks(ctx, n_out), EW_THREADS, 0, ctx->stream>>>(partial, n_slices, n_out, (uint32_t*)d_out);
+      ctx->launches += 1;
+    }
+  }
+  GRAPE_CUDA_TRY(ctx, cudaGetLastError());
+  return GRAPE_OK;
+}
+
+template int fold_axis_async<false>(grape_ctx*, const void*, uint64_t, const void*, uint32_t, uint64_t, void*);
+template int fold_axis_async<true>(grape_ctx*, const void*, uint64_t, const void*, uint32_t, uint64_t, void*);
+
+}  // namespace grape
+
+using namespace grape;
+
+#define CHECK_CTX(ctx) if (!(ctx)) return GRAPE_ERR_INVALID
+#define LAUNCH_DONE(ctx, k) do { (ctx)->launches += (k); GRAPE_CUDA_TRY((ctx), cudaGetLastError()); return GRAPE_OK; } while (0)
+
+extern "C" int grape_fr_from_i32(grape_ctx* ctx, const int32_t* d_in, void* d_out, uint64_t n) {
+  CHECK_CTX(ctx);
+  if (n == 0) return GRAPE_OK;
+  k_from_i32<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>(d_in, (uint32_t*)d_out, n);
+  LAUNCH_DONE(ctx, 1);
+}
+extern "C" int grape_fr_from_u32(grape_ctx* ctx, const uint32_t* d_in, void* d_out, uint64_t n) {
+  CHECK_CTX(ctx);
+  if (n == 0) return GRAPE_OK;
+  k_from_u32<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>(d_in, (uint32_t*)d_out, n);
+  LAUNCH_DONE(ctx, 1);
+}
+extern "C" int grape_fr_to_mont(grape_ctx* ctx, void* d_t, uint64_t n) {
+  CHECK_CTX(ctx);
+  if (n == 0) return GRAPE_OK;
+  k_to_mont<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>((uint32_t*)d_t, n);
+  LAUNCH_DONE(ctx, 1);
+}
+extern "C" int grape_fr_from_mont(grape_ctx* ctx, void* d_t, uint64_t n) {
+  CHECK_CTX(ctx);
+  if (n == 0) return GRAPE_OK;
+  k_from_mont<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>((uint32_t*)d_t, n);
+  LAUNCH_DONE(ctx, 1);
+}
+extern "C" int grape_fr_add(grape_ctx* ctx, const void* d_a, const void* d_b, void* d_out, uint64_t n) {
+  CHECK_CTX(ctx);
+  if (n == 0) return GRAPE_OK;
+  k_binary<0, Fr><<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_a, (const uint32_t*)d_b, (uint32_t*)d_out, n);
+  LAUNCH_DONE(ctx, 1);
+}
+extern "C" int grape_fr_sub(grape_ctx* ctx, const void* d_a, const void* d_b, void* d_out, uint64_t n) {
+  CHECK_CTX(ctx);
+  if (n == 0) return GRAPE_OK;
+  k_binary<1, Fr><<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_a, (const uint32_t*)d_b, (uint32_t*)d_out, n);
+  LAUNCH_DONE(ctx, 1);
+}
+extern "C" int grape_fr_mul(grape_ctx* ctx, const void* d_a, const void* d_b, void* d_out, uint64_t n) {
+  CHECK_CTX(ctx);
+  if (n == 0) return GRAPE_OK;
+  k_binary<2, Fr><<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_a, (const uint32_t*)d_b, (uint32_t*)d_out, n);
+  LAUNCH_DONE(ctx, 1);
+}
+// Diagnostics: the same three operations over the base field Fp (used by the curve arithmetic).
+extern "C" int grape_fp_binary(grape_ctx* ctx, int op, const void* d_a, const void* d_b, void* d_out, uint64_t n) {
+  CHECK_CTX(ctx);
+  if (n == 0) return GRAPE_OK;
+  uint32_t g = ew_blocks(ctx, n);
+  if (op == 0) k_binary<0, Fp><<<g, EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_a, (const uint32_t*)d_b, (uint32_t*)d_out, n);
+  else if (op == 1) k_binary<1, Fp><<<g, EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_a, (const uint32_t*)d_b, (uint32_t*)d_out, n);
+  else if (op == 2) k_binary<2, Fp><<<g, EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_a, (const uint32_t*)d_b, (uint32_t*)d_out, n);
+  else return fail(ctx, GRAPE_ERR_INVALID, "fp_binary: op must be 0 (add), 1 (sub) or 2 (mul)");
+  LAUNCH_DONE(ctx, 1);
+}
+extern "C" int grape_fr_scale(grape_ctx* ctx, const void* d_a, const void* d_scalar, void* d_out, uint64_t n) {
+  CHECK_CTX(ctx);
+  if (n == 0) return GRAPE_OK;
+  k_broadcast<1><<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_a, (const uint32_t*)d_scalar, (uint32_t*)d_out, n);
+  LAUNCH_DONE(ctx, 1);
+}
+extern "C" int grape_fr_add_scalar(grape_ctx* ctx, const void* d_a, const void* d_scalar, void* d_out, uint64_t n) {
+  CHECK_CTX(ctx);
+  if (n == 0) return GRAPE_OK;
+  k_broadcast<0><<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_a, (const uint32_t*)d_scalar, (uint32_t*)d_out, n);
+  LAUNCH_DONE(ctx, 1);
+}
+extern "C" int grape_fr_axpy(grape_ctx* ctx, const void* d_a, const void* d_scalar, const void* d_b, void* d_out, uint64_t n) {
+  CHECK_CTX(ctx);
+  if (n == 0) return GRAPE_OK;
+  k_axpy<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_a, (const uint32_t*)d_scalar, (const uint32_t*)d_b, (uint32_t*)d_out, n);
+  LAUNCH_DONE(ctx, 1);
+}
+extern "C" int grape_fr_inverse(grape_ctx* ctx, const void* d_in, const void* d_shift, void* d_out, uint64_t n) {
+  CHECK_CTX(ctx);
+  if (n == 0) return GRAPE_OK;
+  arena_reset(ctx);
+  void* scratch;
+  int rc = arena_alloc(ctx, n * 32, &scratch);
+  if (rc) return rc;
+  // about 96 elements per thread once the tensor is large, at least one block per SM
+  uint64_t threads = n / 96;
+  uint64_t min_threads = (uint64_t)ctx->sm_count * 128;
+  if (threads < min_threads) threads = std::min<uint64_t>(n, min_threads);
+  uint32_t blocks = (uint32_t)((threads + 127) / 128);
+  k_batch_inverse<<<blocks, 128, 0, ctx->stream>>>((const uint32_t*)d_in, (const uint32_t*)d_shift, (uint32_t*)d_out, (uint32_t*)scratch, n);
+  LAUNCH_DONE(ctx, 1);
+}
+extern "C" int grape_pad_i32(grape_ctx* ctx, const int32_t* d_in, int32_t* d_out, uint32_t n, uint32_t pad_n, uint64_t pad_size) {
+  CHECK_CTX(ctx);
+  if (pad_size == 0) return GRAPE_OK;
+  if (n == 0 || pad_n < n) return fail(ctx, GRAPE_ERR_INVALID, "pad: need 0 < n <= pad_n");
+  k_pad_i32<<<ew_blocks(ctx, pad_size), EW_THREADS, 0, ctx->stream>>>(d_in, d_out, n, pad_n, pad_size);
+  LAUNCH_DONE(ctx, 1);
+}
+extern "C" int grape_fr_pad(grape_ctx* ctx, const void* d_in, void* d_out, uint32_t n, uint32_t pad_n, uint64_t pad_size, const void* d_pad_value) {
+  CHECK_CTX(ctx);
+  if (pad_size == 0) return GRAPE_OK;
+  if (n == 0 || pad_n < n) return fail(ctx, GRAPE_ERR_INVALID, "pad: need 0 < n <= pad_n");
+  k_pad_fr<<<ew_blocks(ctx, pad_size), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_in, (uint32_t*)d_out, n, pad_n, pad_size, (const uint32_t*)d_pad_value);
+  LAUNCH_DONE(ctx, 1);
+}
+extern "C" int grape_fr_sum(grape_ctx* ctx, const void* d_in, uint64_t n, void* d_out) {
+  CHECK_CTX(ctx);
+  if (n == 0) return grape_dev_zero(ctx, d_out, 32);
+  arena_reset(ctx);
+  return fr_sum_async(ctx, d_in, n, d_out);
+}
+extern "C" int grape_fr_rowsum(grape_ctx* ctx, const void* d_in, void* d_out, uint64_t rows, uint32_t dim) {
+  CHECK_CTX(ctx);
+  if (rows == 0 || dim == 0) return GRAPE_OK;
+  uint64_t threads = rows * 32;
+  uint32_t blocks = ew_blocks(ctx, threads);
+  k_rowsum_broadcast<<<blocks, EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_in, (uint32_t*)d_out, rows, dim);
+  LAUNCH_DONE(ctx, 1);
+}
+extern "C" int grape_fr_fold(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* d_x, uint32_t c, uint64_t gap, void* d_out) {
+  CHECK_CTX(ctx);
+  if (c == 0 || gap == 0) return fail(ctx, GRAPE_ERR_INVALID, "fold: c and gap must be positive");
+  arena_reset(ctx);
+  return fold_axis_async<false>(ctx, d_t, ntot, d_x, c, gap, d_out);
+}
+extern "C" int grape_fold_i32(grape_ctx* ctx, const int32_t* d_t, uint64_t ntot, const void* d_x, uint32_t c, uint64_t gap, void* d_out) {
+  CHECK_CTX(ctx);
+  if (c == 0 || gap == 0) return fail(ctx, GRAPE_ERR_INVALID, "fold: c and gap must be positive");
+  arena_reset(ctx);
+  return fold_axis_async<true>(ctx, d_t, ntot, d_x, c, gap, d_out);
+}

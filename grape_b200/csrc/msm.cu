@@ -1,0 +1,439 @@
+// Hyrax row commitments: fixed-base multi-scalar multiplication over BN254 G1.
+//
+// Replaces (paths inside the reference project):
+//   precompute_generators / naive_msm                 src/ec_operation.cu:15-49
+//   Hyrax::commit(int*) + int_windows_sum/_reduce     src/Hyrax.cu:312-333, 46-87
+//   Hyrax::commit(FrTensor&) + many_windows_sum/_reduce  src/Hyrax.cu:335-359, 128-167
+//   single_commit + single_windows_sum/_reduce        src/Hyrax.cu:176-185, 89-126
+//
+// Design.  All rows of a Hyrax commitment share the same generators, so the generators are
+// expanded once into a table of small multiples and every (scalar, generator) pair costs one
+// table gather and one mixed addition per non-zero signed digit.  Signed digits halve the table;
+// with 16-bit windows an int16-range scalar is a single digit, i.e. a single addition per pair,
+// at the price of a table of 2^15 rows that lives in HBM rather than in L2.
+//
+//   commit_accumulate:  one WARP per (row, chunk of generators), four warps per block.  A lane
+//                       walks its generators with stride 32 and keeps one XYZZ accumulator; the
+//                       32 accumulators are folded with a shuffle tree (5 general additions,
+//                       amortised over >= 64 mixed additions per lane when rows are long) and
+//                       lane 0 writes the partial sum to scratch memory.
+//   commit_finalize:    one thread per row adds the chunk partials, normalises (one inversion)
+//                       and writes the canonical Jacobian record.
+#include "ctx.cuh"
+#include "curve.cuh"
+
+namespace grape {
+
+struct TableView {
+  const Affine* base;
+  uint32_t n_gens;
+  uint32_t window_bits;    // c
+  uint32_t n_windows;      // windows whose 2^(c*w) multiples are stored
+  uint32_t half;           // 2^(c-1): largest digit magnitude
+  uint64_t window_stride;  // records per window
+  uint32_t first_row;      // row of magnitude 1
+  __device__ __forceinline__ const Affine* entry(uint32_t w, uint32_t mag, uint32_t i) const {
+    return base + (uint64_t)w * window_stride + (uint64_t)(mag - 1 + first_row) * n_gens + i;
+  }
+};
+
+static TableView make_view(const grape_table* t) {
+  TableView v;
+  v.base = reinterpret_cast<const Affine*>(t->data);
+  v.n_gens = t->n_gens;
+  v.window_bits = t->window_bits;
+  v.n_windows = t->n_windows;
+  v.half = 1u << (t->window_bits - 1);
+  v.window_stride = t->window_stride;
+  v.first_row = t->first_digit_row;
+  return v;
+}
+
+// ------------------------------------------------------------------------------------------
+// Table construction
+// ------------------------------------------------------------------------------------------
+constexpr int TABLE_BLOCK = 16;  // consecutive multiples produced (and batch-normalised) per thread
+
+// One thread: generator i, window w, magnitudes d0+1 .. d0+TABLE_BLOCK.
+__global__ void __launch_bounds__(128) table_build_kernel(const Jacobian* __restrict__ gens,
+                                                          Affine* __restrict__ table, uint32_t n_gens,
+                                                          uint32_t window_bits, uint32_t n_windows,
+                                                          uint32_t half) {
+  const uint32_t blocks_per_window = half / TABLE_BLOCK;
+  uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  uint64_t total = (uint64_t)n_gens * n_windows * blocks_per_window;
+  if (gid >= total) return;
+  uint32_t i = gid % n_gens;
+  uint64_t rest = gid / n_gens;
+  uint32_t blk = rest % blocks_per_window;
+  uint32_t w = rest / blocks_per_window;
+
+  Jacobian gj;
+  const char* gp = reinterpret_cast<const char*>(gens + i);
+  gj.x = Fp::load(gp);
+  gj.y = Fp::load(gp + 32);
+  gj.z = Fp::load(gp + 64);
+  Xyzz b = xyzz_from_jacobian(gj);
+  for (uint32_t k = 0; k < window_bits * w; k++) b = xyzz_dbl(b);
+  Affine base = xyzz_to_affine(b);  // 2^(c w) * G_i
+
+  // start = d0 * base by double-and-add
+  uint32_t d0 = blk * TABLE_BLOCK;
+  Xyzz acc = Xyzz::inf();
+  for (int bit = 15; bit >= 0; bit--) {
+    acc = xyzz_dbl(acc);
+    if ((d0 >> bit) & 1u) xyzz_madd(acc, base);
+  }
+
+  Xyzz e[TABLE_BLOCK];
+  Fp pref[TABLE_BLOCK];
+  Fp run = Fp::one();
+#pragma unroll 1
+  for (int k = 0; k < TABLE_BLOCK; k++) {
+    xyzz_madd(acc, base);
+    e[k] = acc;
+    Fp zp = acc.is_inf() ? Fp::one() : fe_mul(acc.zz, acc.zzz);
+    run = fe_mul(run, zp);
+    pref[k] = run;
+  }
+  Fp inv = fe_inv(run);
+  uint64_t wbase = (uint64_t)w * half * n_gens;
+#pragma unroll 1
+  for (int k = TABLE_BLOCK - 1; k >= 0; k--) {
+    Fp zp = e[k].is_inf() ? Fp::one() : fe_mul(e[k].zz, e[k].zzz);
+    Fp zinv = (k == 0) ? inv : fe_mul(inv, pref[k - 1]);  // 1 / (zz*zzz) of entry k
+    inv = fe_mul(inv, zp);
+    Affine out;
+    if (e[k].is_inf()) {
+      out = Affine::inf();
+    } else {
+      out.x = fe_mul(e[k].x, fe_mul(zinv, e[k].zzz));
+      out.y = fe_mul(e[k].y, fe_mul(zinv, e[k].zz));
+    }
+    out.store(table + wbase + (uint64_t)(d0 + k) * n_gens + i);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Scalar preparation for Fr scalars: leave Montgomery form and add the signed-digit bias, so the
+// accumulate kernel can read window e_w = (v + bias) >> (c w) and use digit e_w - 2^(c-1).
+// ------------------------------------------------------------------------------------------
+__global__ void fr_bias_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out,
+                               uint64_t n, uint32_t window_bits, uint32_t total_windows) {
+  uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (gid >= n) return;
+  Fr s = Fr::load_nc(in + gid * 8);
+  s = fe_from_mont(s);
+  uint32_t bias[8];
+#pragma unroll
+  for (int k = 0; k < 8; k++) bias[k] = (window_bits == 8) ? 0x80808080u : 0x80008000u;
+  // the top window keeps its unsigned value: clear the bias of windows >= total_windows - 1
+  uint32_t top_bit = window_bits * (total_windows - 1);
+#pragma unroll
+  for (int k = 0; k < 8; k++) {
+    uint32_t lo = 32u * k;
+    if (lo >= top_bit) bias[k] = 0;
+    else if (lo + 32 > top_bit) bias[k] &= (1u << (top_bit - lo)) - 1u;
+  }
+  uint32_t r[8];
+  add8(r, s.v, bias);
+  uint4* o = reinterpret_cast<uint4*>(out + gid * 8);
+  o[0] = make_uint4(r[0], r[1], r[2], r[3]);
+  o[1] = make_uint4(r[4], r[5], r[6], r[7]);
+}
+
+// ------------------------------------------------------------------------------------------
+// Accumulation
+// ------------------------------------------------------------------------------------------
+constexpr int MSM_THREADS = 128;
+
+// Signed digit of window w.  Int32 path: |s| carries the sign separately.
+struct DigitI32 {
+  uint32_t vb;     // |s| + bias
+  bool neg;
+  __device__ __forceinline__ void load(const int32_t* p, uint32_t bias) {
+    int32_t s = __ldg(p);
+    neg = s < 0;
+    uint32_t v = neg ? (0u - (uint32_t)s) : (uint32_t)s;
+    vb = v + bias;
+  }
+};
+
+template <bool FR>
+__global__ void __launch_bounds__(MSM_THREADS, 4)
+commit_accumulate_kernel(const void* __restrict__ scalars, TableView tab, uint32_t wd,
+                         uint32_t total_windows, uint32_t n_chunks, uint32_t chunk_len,
+                         uint64_t n_units, Xyzz* __restrict__ partials, uint32_t* __restrict__ status) {
+  const uint64_t unit = (uint64_t)blockIdx.x * (MSM_THREADS / 32) + (threadIdx.x >> 5);
+  if (unit >= n_units) return;  // whole warps leave together
+  const uint32_t lane = threadIdx.x & 31;
+  const uint64_t row = unit / n_chunks;
+  const uint32_t chunk = (uint32_t)(unit % n_chunks);
+  const uint32_t i_begin = chunk * chunk_len;
+  const uint32_t i_end = min(wd, i_begin + chunk_len);
+  const uint32_t c = tab.window_bits;
+  const uint32_t mask = (1u << c) - 1u;
+  const uint32_t half = tab.half;
+  const uint32_t tw = tab.n_windows;
+  const uint32_t groups = (total_windows + tw - 1) / tw;
+
+  // bias for the int32 path: 2^(c-1) at every window below the top one
+  uint32_t bias32 = 0;
+  if (!FR) {
+    for (uint32_t w = 0; w + 1 < total_windows; w++) bias32 |= half << (c * w);
+  }
+
+  Xyzz acc = Xyzz::inf();
+  for (int g = (int)groups - 1; g >= 0; g--) {
+    if (g != (int)groups - 1) {
+      for (uint32_t k = 0; k < c * tw; k++) acc = xyzz_dbl(acc);
+    }
+    const uint32_t w_lo = g * tw;
+    const uint32_t w_hi = min(total_windows, w_lo + tw);
+    for (uint32_t i = i_begin + lane; i < i_end; i += 32) {
+      const uint64_t idx = row * wd + i;
+      if (FR) {
+        const uint32_t* sp = reinterpret_cast<const uint32_t*>(scalars) + idx * 8;
+        for (uint32_t w = w_lo; w < w_hi; w++) {
+          uint32_t bit = c * w;
+          uint32_t e = (__ldg(sp + (bit >> 5)) >> (bit & 31)) & mask;
+          int32_t d = (w + 1 == total_windows) ? (int32_t)e : (int32_t)e - (int32_t)half;
+          if (d == 0) continue;
+          uint32_t mag = d < 0 ? (uint32_t)(-d) : (uint32_t)d;
+          Affine p = Affine::load_nc(tab.entry(w - w_lo, mag, i));
+          if (d < 0) p.y = fe_neg(p.y);
+          xyzz_madd(acc, p);
+        }
+      } else {
+        DigitI32 dg;
+        dg.load(reinterpret_cast<const int32_t*>(scalars) + idx, bias32);
+        for (uint32_t w = w_lo; w < w_hi; w++) {
+          uint32_t sh = c * w;
+          int32_t d;
+          if (w + 1 == total_windows) d = (int32_t)(sh < 32 ? (dg.vb >> sh) : 0u);
+          else d = (int32_t)((dg.vb >> sh) & mask) - (int32_t)half;
+          if (d == 0) continue;
+          uint32_t mag = d < 0 ? (uint32_t)(-d) : (uint32_t)d;
+          if (mag > half) {  // scalar larger than the declared bound: report, never read out of range
+            atomicOr(status, STATUS_DIGIT_RANGE);
+            continue;
+          }
+          Affine p = Affine::load_nc(tab.entry(w - w_lo, mag, i));
+          if ((d < 0) != dg.neg) p.y = fe_neg(p.y);
+          xyzz_madd(acc, p);
+        }
+      }
+    }
+  }
+
+  // warp reduction: shuffle tree of general additions
+#pragma unroll 1
+  for (int off = 16; off > 0; off >>= 1) {
+    Xyzz other = xyzz_shfl_down(acc, off);
+    if (lane < off) xyzz_add(acc, other);
+  }
+  if (lane == 0) acc.store(partials + unit);
+}
+
+__global__ void __launch_bounds__(128) commit_finalize_kernel(const Xyzz* __restrict__ partials,
+                                                              uint32_t n_chunks, uint64_t rows,
+                                                              Jacobian* __restrict__ out) {
+  uint64_t row = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  Xyzz acc = Xyzz::load(partials + row * n_chunks);
+#pragma unroll 1
+  for (uint32_t k = 1; k < n_chunks; k++) xyzz_add(acc, Xyzz::load(partials + row * n_chunks + k));
+  bool inf = acc.is_inf();
+  Affine a = xyzz_to_affine(acc);
+  store_jacobian_normalised(out + row, a, inf);
+}
+
+// ------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------
+static int check_table(grape_ctx* ctx, const grape_table* t, uint32_t wd) {
+  if (!ctx || !t || !t->data) return fail(ctx, GRAPE_ERR_INVALID, "null context or table");
+  if (wd == 0 || wd > t->n_gens)
+    return fail(ctx, GRAPE_ERR_INVALID, "row length exceeds the number of generators in the table");
+  return GRAPE_OK;
+}
+
+// Picks how many warps share one row: one when there are enough rows to fill the GPU, otherwise
+// enough to reach a few warps per scheduler while leaving every lane at least two generators.
+static uint32_t pick_chunks(const grape_ctx* ctx, uint64_t rows, uint32_t wd) {
+  uint64_t target_warps = (uint64_t)ctx->sm_count * 32;
+  if (rows >= target_warps) return 1;
+  uint64_t want = (target_warps + rows - 1) / rows;
+  uint64_t max_chunks = (wd + 63) / 64;
+  if (want > max_chunks) want = max_chunks;
+  if (want < 1) want = 1;
+  return (uint32_t)want;
+}
+
+template <bool FR>
+static int launch_commit(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t rows,
+                         uint32_t wd, uint32_t total_windows, Xyzz* partials, uint32_t n_chunks,
+                         void* d_out) {
+  uint32_t chunk_len = (wd + n_chunks - 1) / n_chunks;
+  uint64_t units = rows * n_chunks;
+  if (units == 0) return GRAPE_OK;
+  uint64_t blocks = (units + MSM_THREADS / 32 - 1) / (MSM_THREADS / 32);
+  if (blocks > 0x7fffffffull) return fail(ctx, GRAPE_ERR_LIMIT, "too many commitment rows for one launch");
+  {
+    ProfScope prof(ctx);
+    commit_accumulate_kernel<FR><<<(uint32_t)blocks, MSM_THREADS, 0, ctx->stream>>>(
+        d_scalars, make_view(t), wd, total_windows, n_chunks, chunk_len, units, partials, ctx->d_status);
+  }
+  commit_finalize_kernel<<<(uint32_t)((rows + 127) / 128), 128, 0, ctx->stream>>>(
+      partials, n_chunks, rows, reinterpret_cast<Jacobian*>(d_out));
+  ctx->launches += 2;
+  GRAPE_CUDA_TRY(ctx, cudaGetLastError());
+  return GRAPE_OK;
+}
+
+}  // namespace grape
+
+using namespace grape;
+
+extern "C" int grape_table_create(grape_ctx* ctx, const void* d_gens_jacobian, uint32_t n_gens,
+                                  uint32_t window_bits, uint32_t n_windows, grape_table** out) {
+  if (!ctx || !out || !d_gens_jacobian) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
+  if (window_bits != 8 && window_bits != 16)
+    return fail(ctx, GRAPE_ERR_INVALID, "window_bits must be 8 or 16");
+  if (n_gens == 0 || n_windows == 0 || n_windows * window_bits > 256)
+    return fail(ctx, GRAPE_ERR_INVALID, "bad table geometry");
+  uint32_t half = 1u << (window_bits - 1);
+  uint64_t records = (uint64_t)half * n_gens * n_windows;
+  void* data = nullptr;
+  cudaError_t e = cudaMalloc(&data, records * sizeof(Affine));
+  if (e != cudaSuccess) return fail(ctx, GRAPE_ERR_NOMEM, "generator table allocation failed");
+  uint64_t threads = (uint64_t)n_gens * n_windows * (half / TABLE_BLOCK);
+  uint64_t blocks = (threads + 127) / 128;
+  if (blocks > 0x7fffffffull) {
+    cudaFree(data);
+    return fail(ctx, GRAPE_ERR_LIMIT, "table too large for one launch");
+  }
+  table_build_kernel<<<(uint32_t)blocks, 128, 0, ctx->stream>>>(
+      reinterpret_cast<const Jacobian*>(d_gens_jacobian), reinterpret_cast<Affine*>(data), n_gens,
+      window_bits, n_windows, half);
+  ctx->launches += 1;
+  cudaError_t le = cudaGetLastError();
+  if (le != cudaSuccess) {
+    cudaFree(data);
+    return fail(ctx, GRAPE_ERR_CUDA, std::string("table_build_kernel: ") + cudaGetErrorString(le));
+  }
+  grape_table* t = new grape_table();
+  t->ctx = ctx;
+  t->data = data;
+  t->owned = true;
+  t->n_gens = n_gens;
+  t->window_bits = window_bits;
+  t->n_windows = n_windows;
+  t->n_digits = half;
+  t->window_stride = (uint64_t)half * n_gens;
+  t->first_digit_row = 0;
+  *out = t;
+  return GRAPE_OK;
+}
+
+extern "C" int grape_table_from_reference(grape_ctx* ctx, const void* d_points, uint32_t n_gens,
+                                          grape_table** out) {
+  if (!ctx || !out || !d_points || n_gens == 0) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
+  grape_table* t = new grape_table();
+  t->ctx = ctx;
+  t->data = const_cast<void*>(d_points);
+  t->owned = false;
+  t->n_gens = n_gens;
+  t->window_bits = 8;
+  t->n_windows = 1;
+  t->n_digits = 128;
+  t->window_stride = (uint64_t)256 * n_gens;
+  t->first_digit_row = 1;  // row 0 of that layout is 0*G = infinity
+  *out = t;
+  return GRAPE_OK;
+}
+
+extern "C" int grape_table_destroy(grape_table* t) {
+  if (!t) return GRAPE_OK;
+  if (t->owned && t->data) cudaFree(t->data);
+  delete t;
+  return GRAPE_OK;
+}
+
+extern "C" uint64_t grape_table_bytes(const grape_table* t) {
+  if (!t) return 0;
+  uint64_t rows = t->owned ? (uint64_t)t->n_digits * t->n_windows : 256;
+  return rows * t->n_gens * sizeof(Affine);
+}
+
+extern "C" const void* grape_table_data(const grape_table* t) { return t ? t->data : nullptr; }
+
+extern "C" int grape_commit_i32(grape_ctx* ctx, const grape_table* t, const int32_t* d_scalars,
+                                uint64_t size, uint32_t wd, uint32_t max_bits, void* d_out) {
+  int rc = check_table(ctx, t, wd);
+  if (rc) return rc;
+  if (size % wd != 0) return fail(ctx, GRAPE_ERR_INVALID, "size is not a multiple of the row length");
+  if (max_bits == 0 || max_bits > 32) return fail(ctx, GRAPE_ERR_INVALID, "max_bits must be in 1..32");
+  if (size == 0) return GRAPE_OK;
+  if (!d_scalars || !d_out) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
+  uint64_t rows = size / wd;
+  uint32_t total_windows = (max_bits + t->window_bits - 1) / t->window_bits;
+  uint32_t n_chunks = pick_chunks(ctx, rows, wd);
+  arena_reset(ctx);
+  Xyzz* partials = nullptr;
+  rc = arena_alloc_t(ctx, rows * n_chunks, &partials);
+  if (rc) return rc;
+  return launch_commit<false>(ctx, t, d_scalars, rows, wd, total_windows, partials, n_chunks, d_out);
+}
+
+extern "C" int grape_commit_fr(grape_ctx* ctx, const grape_table* t, const void* d_scalars,
+                               uint64_t size, uint32_t wd, void* d_out) {
+  int rc = check_table(ctx, t, wd);
+  if (rc) return rc;
+  if (size % wd != 0) return fail(ctx, GRAPE_ERR_INVALID, "size is not a multiple of the row length");
+  if (size == 0) return GRAPE_OK;
+  if (!d_scalars || !d_out) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
+  uint64_t rows = size / wd;
+  uint32_t total_windows = (254 + t->window_bits - 1) / t->window_bits;
+  uint32_t n_chunks = pick_chunks(ctx, rows, wd);
+  arena_reset(ctx);
+  Xyzz* partials = nullptr;
+  uint32_t* biased = nullptr;
+  rc = arena_alloc_t(ctx, rows * n_chunks, &partials);
+  if (rc) return rc;
+  rc = arena_alloc_t(ctx, size * 8, &biased);
+  if (rc) return rc;
+  fr_bias_kernel<<<(uint32_t)((size + 255) / 256), 256, 0, ctx->stream>>>(
+      reinterpret_cast<const uint32_t*>(d_scalars), biased, size, t->window_bits, total_windows);
+  ctx->launches += 1;
+  return launch_commit<true>(ctx, t, biased, rows, wd, total_windows, partials, n_chunks, d_out);
+}
+
+extern "C" int grape_commit_i32_host(grape_ctx* ctx, const grape_table* t, const int32_t* h_scalars,
+                                     uint64_t size, uint32_t wd, uint32_t max_bits, void* h_out) {
+  int rc = check_table(ctx, t, wd);
+  if (rc) return rc;
+  if (size % wd != 0) return fail(ctx, GRAPE_ERR_INVALID, "size is not a multiple of the row length");
+  if (size == 0) return GRAPE_OK;
+  uint64_t rows = size / wd;
+  size_t in_bytes = size * sizeof(int32_t);
+  size_t out_bytes = rows * GRAPE_JACOBIAN_BYTES;
+  size_t need = ((in_bytes + 255) & ~size_t(255)) + out_bytes;
+  if (need > ctx->dstage_bytes) {
+    GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->dstage) cudaFree(ctx->dstage);
+    ctx->dstage = nullptr;
+    ctx->dstage_bytes = 0;
+    if (cudaMalloc(&ctx->dstage, need) != cudaSuccess)
+      return fail(ctx, GRAPE_ERR_NOMEM, "staging buffer allocation failed");
+    ctx->dstage_bytes = need;
+  }
+  int32_t* d_in = reinterpret_cast<int32_t*>(ctx->dstage);
+  char* d_out = reinterpret_cast<char*>(ctx->dstage) + ((in_bytes + 255) & ~size_t(255));
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_in, h_scalars, in_bytes, cudaMemcpyHostToDevice, ctx->stream));
+  rc = grape_commit_i32(ctx, t, d_in, size, wd, max_bits, d_out);
+  if (rc) return rc;
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(h_out, d_out, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  return GRAPE_OK;
+}

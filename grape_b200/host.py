@@ -1,0 +1,301 @@
+"""Python host side over the C ABI: contexts, device buffers, generator tables and the
+field-tensor / commitment calls, with numpy arrays as the host representation.
+
+Field elements travel as ``uint32[n, 8]`` arrays (little-endian limbs of the Montgomery residue),
+affine points as ``uint32[n, 16]``, Jacobian points as ``uint32[n, 24]`` -- the byte layouts of the
+reference's ``fr_t`` / ``affine_t`` / ``jacob_t``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import GrapeError
+
+FR_MODULUS = 0x30644E72E131A029B85045B68181585D2833E84879B9709143E1F593F0000001
+FP_MODULUS = 0x30644E72E131A029B85045B68181585D97816A916871CA8D3C208C16D87CFD47
+_MONT = 1 << 256
+COM_SCALE = 16
+
+
+# ----------------------------------------------------------------------------- encoding helpers
+def encode_field(values, modulus=FR_MODULUS) -> np.ndarray:
+    """Python integers (any sign) -> uint32[n, 8] Montgomery limbs."""
+    out = np.empty((len(values), 8), dtype=np.uint32)
+    buf = bytearray()
+    for v in values:
+        buf += ((int(v) % modulus) * _MONT % modulus).to_bytes(32, "little")
+    out[:] = np.frombuffer(bytes(buf), dtype="<u4").reshape(-1, 8)
+    return out
+
+
+def decode_field(arr: np.ndarray, modulus=FR_MODULUS) -> list[int]:
+    """uint32[n, 8] Montgomery limbs -> Python integers in [0, modulus)."""
+    arr = np.ascontiguousarray(arr, dtype="<u4").reshape(-1, 8)
+    rinv = pow(_MONT, -1, modulus)
+    raw = arr.tobytes()
+    return [int.from_bytes(raw[i:i + 32], "little") * rinv % modulus for i in range(0, len(raw), 32)]
+
+
+def encode_jacobian(points) -> np.ndarray:
+    """Affine (x, y) tuples or None (infinity) -> uint32[n, 24] Jacobian records with Z = 1."""
+    vals = []
+    for p in points:
+        vals += [1, 1, 0] if p is None else [p[0], p[1], 1]
+    return encode_field(vals, FP_MODULUS).reshape(-1, 24)
+
+
+def decode_jacobian(arr: np.ndarray):
+    """uint32[n, 24] Jacobian records -> affine (x, y) tuples, None for infinity."""
+    flat = decode_field(np.ascontiguousarray(arr).reshape(-1, 8), FP_MODULUS)
+    out = []
+    for i in range(0, len(flat), 3):
+        X, Y, Z = flat[i:i + 3]
+        if Z == 0:
+            out.append(None)
+        else:
+            zi = pow(Z, -1, FP_MODULUS)
+            out.append((X * zi * zi % FP_MODULUS, Y * zi * zi * zi % FP_MODULUS))
+    return out
+
+
+# ----------------------------------------------------------------------------- context / buffers
+class DeviceBuffer:
+    """A cudaMalloc'd region owned by a context."""
+
+    def __init__(self, ctx: "Context", nbytes: int):
+        self.ctx = ctx
+        self.nbytes = int(nbytes)
+        p = C.c_void_p()
+        ctx._check(ctx.lib.grape_dev_alloc(ctx.handle, self.nbytes, C.byref(p)))
+        self.ptr = p.value or 0
+
+    def free(self):
+        if self.ptr and self.ctx.handle:
+            self.ctx.lib.grape_dev_free(self.ctx.handle, self.ptr)
+        self.ptr = 0
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+    def at(self, byte_offset: int) -> int:
+        return self.ptr + int(byte_offset)
+
+
+class Context:
+    """One GPU, one stream, one scratch arena, one seedable random stream."""
+
+    def __init__(self, device: int = 0):
+        self.lib = _lib.load()
+        h = C.c_void_p()
+        rc = self.lib.grape_ctx_create(int(device), C.byref(h))
+        if rc != 0:
+            raise GrapeError(rc, f"cannot create a context on CUDA device {device} (no GPU?)")
+        self.handle = h.value
+        self.device = device
+
+    def close(self):
+        if self.handle:
+            self.lib.grape_ctx_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, rc: int):
+        if rc != 0:
+            raise GrapeError(rc, self.lib.grape_ctx_error(self.handle).decode())
+
+    # -- memory
+    def alloc(self, nbytes: int) -> DeviceBuffer:
+        return DeviceBuffer(self, nbytes)
+
+    def upload(self, arr: np.ndarray) -> DeviceBuffer:
+        arr = np.ascontiguousarray(arr)
+        buf = DeviceBuffer(self, max(arr.nbytes, 1))
+        if arr.nbytes:
+            self._check(self.lib.grape_h2d(self.handle, buf.ptr, arr.ctypes.data, arr.nbytes))
+            self.sync()
+        return buf
+
+    def download(self, src, nbytes: int, dtype=np.uint32, offset: int = 0) -> np.ndarray:
+        ptr = (src.ptr if isinstance(src, DeviceBuffer) else int(src)) + offset
+        out = np.empty(nbytes // np.dtype(dtype).itemsize, dtype=dtype)
+        self._check(self.lib.grape_d2h(self.handle, out.ctypes.data, ptr, nbytes))
+        return out
+
+    def sync(self):
+        self._check(self.lib.grape_ctx_sync(self.handle))
+
+    def status(self) -> int:
+        f = C.c_uint32()
+        self._check(self.lib.grape_ctx_status(self.handle, C.byref(f)))
+        return f.value
+
+    @property
+    def launches(self) -> int:
+        return int(self.lib.grape_ctx_launches(self.handle))
+
+    @property
+    def stream(self) -> int:
+        return int(self.lib.grape_ctx_stream(self.handle) or 0)
+
+    def timer_begin(self):
+        self._check(self.lib.grape_timer_begin(self.handle))
+
+    def timer_end(self) -> float:
+        """Milliseconds on the context's stream since ``timer_begin`` (synchronises)."""
+        ms = C.c_float()
+        self._check(self.lib.grape_timer_end(self.handle, C.byref(ms)))
+        return ms.value
+
+    def prof_enable(self, on: bool = True):
+        self._check(self.lib.grape_prof_enable(self.handle, int(on)))
+
+    def prof_read(self):
+        """(total milliseconds, launches) of the dominant kernels recorded since the last read."""
+        ms, n = C.c_float(), C.c_uint32()
+        self._check(self.lib.grape_prof_read(self.handle, C.byref(ms), C.byref(n)))
+        return ms.value, n.value
+
+    def pinned_array(self, shape, dtype) -> np.ndarray:
+        """A numpy array over page-locked host memory (kept alive by the context)."""
+        nbytes = int(np.prod(shape)) * np.dtype(dtype).itemsize
+        p = C.c_void_p()
+        self._check(self.lib.grape_host_alloc_pinned(self.handle, max(nbytes, 1), C.byref(p)))
+        buf = (C.c_char * nbytes).from_address(p.value)
+        arr = np.frombuffer(buf, dtype=dtype).reshape(shape)
+        self._pinned = getattr(self, "_pinned", []) + [(p.value, buf)]
+        return arr
+
+    def measure_int_peak(self, kind: int) -> float:
+        """Measured integer-pipe ceiling (ops/s): 0 mad.lo, 1 mad.wide, 2 lo/hi pairs, 3 field muls."""
+        v = C.c_double()
+        self._check(self.lib.grape_measure_int_peak(self.handle, kind, C.byref(v)))
+        return v.value
+
+    # -- randomness seam
+    def seed(self, seed: int):
+        self._check(self.lib.grape_rng_seed(self.handle, seed))
+
+    def random_fr(self, n: int) -> np.ndarray:
+        out = np.empty((n, 8), dtype=np.uint32)
+        self._check(self.lib.grape_rng_fr(self.handle, out.ctypes.data, n))
+        return out
+
+    # -- field tensors (device pointers in, device pointers out)
+    def fr_upload(self, values) -> DeviceBuffer:
+        return self.upload(encode_field(values))
+
+    def fr_download(self, buf, n: int, offset_elems: int = 0) -> list[int]:
+        return decode_field(self.download(buf, n * 32, offset=offset_elems * 32))
+
+    def fr_from_i32(self, d_in, n, d_out):
+        self._check(self.lib.grape_fr_from_i32(self.handle, _p(d_in), _p(d_out), n))
+
+    def fr_from_u32(self, d_in, n, d_out):
+        self._check(self.lib.grape_fr_from_u32(self.handle, _p(d_in), _p(d_out), n))
+
+    def fr_binary(self, op: str, a, b, out, n):
+        fn = {"add": self.lib.grape_fr_add, "sub": self.lib.grape_fr_sub, "mul": self.lib.grape_fr_mul,
+              "scale": self.lib.grape_fr_scale, "add_scalar": self.lib.grape_fr_add_scalar}[op]
+        self._check(fn(self.handle, _p(a), _p(b), _p(out), n))
+
+    def fp_binary(self, op: str, a, b, out, n):
+        self._check(self.lib.grape_fp_binary(self.handle, {"add": 0, "sub": 1, "mul": 2}[op], _p(a), _p(b), _p(out), n))
+
+    def fr_to_mont(self, t, n):
+        self._check(self.lib.grape_fr_to_mont(self.handle, _p(t), n))
+
+    def fr_from_mont(self, t, n):
+        self._check(self.lib.grape_fr_from_mont(self.handle, _p(t), n))
+
+    def fr_inverse(self, d_in, d_out, n, d_shift=None):
+        self._check(self.lib.grape_fr_inverse(self.handle, _p(d_in), _p(d_shift), _p(d_out), n))
+
+    def fr_sum(self, d_in, n, d_out):
+        self._check(self.lib.grape_fr_sum(self.handle, _p(d_in), n, _p(d_out)))
+
+    def fr_rowsum(self, d_in, d_out, rows, dim):
+        self._check(self.lib.grape_fr_rowsum(self.handle, _p(d_in), _p(d_out), rows, dim))
+
+    def fr_fold(self, d_t, ntot, d_x, c, gap, d_out):
+        self._check(self.lib.grape_fr_fold(self.handle, _p(d_t), ntot, _p(d_x), c, gap, _p(d_out)))
+
+    def fold_i32(self, d_t, ntot, d_x, c, gap, d_out):
+        self._check(self.lib.grape_fold_i32(self.handle, _p(d_t), ntot, _p(d_x), c, gap, _p(d_out)))
+
+    def fr_pad(self, d_in, d_out, n, pad_n, pad_size, d_pad_value):
+        self._check(self.lib.grape_fr_pad(self.handle, _p(d_in), _p(d_out), n, pad_n, pad_size, _p(d_pad_value)))
+
+    def pad_i32(self, d_in, d_out, n, pad_n, pad_size):
+        self._check(self.lib.grape_pad_i32(self.handle, _p(d_in), _p(d_out), n, pad_n, pad_size))
+
+
+def _p(x):
+    if x is None:
+        return None
+    if isinstance(x, DeviceBuffer):
+        return x.ptr
+    return int(x)
+
+
+# ----------------------------------------------------------------------------- commitments
+class GeneratorTable:
+    """Fixed-base table of the Hyrax generators (replaces ``precompute_generators``)."""
+
+    def __init__(self, ctx: Context, gens_jacobian: np.ndarray, window_bits: int = 8, n_windows: int = 1):
+        self.ctx = ctx
+        gens = np.ascontiguousarray(gens_jacobian, dtype=np.uint32).reshape(-1, 24)
+        self.n_gens = gens.shape[0]
+        self.window_bits = window_bits
+        self.n_windows = n_windows
+        self._gens_dev = ctx.upload(gens)
+        h = C.c_void_p()
+        ctx._check(ctx.lib.grape_table_create(ctx.handle, self._gens_dev.ptr, self.n_gens, window_bits,
+                                              n_windows, C.byref(h)))
+        self.handle = h.value
+
+    @property
+    def nbytes(self) -> int:
+        return int(self.ctx.lib.grape_table_bytes(self.handle))
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.ctx.sync()
+            self.ctx.lib.grape_table_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def commit_i32(ctx: Context, table: GeneratorTable, d_scalars, size: int, wd: int, d_out, max_bits: int = 32):
+    ctx._check(ctx.lib.grape_commit_i32(ctx.handle, table.handle, _p(d_scalars), size, wd, max_bits, _p(d_out)))
+
+
+def commit_fr(ctx: Context, table: GeneratorTable, d_scalars, size: int, wd: int, d_out):
+    ctx._check(ctx.lib.grape_commit_fr(ctx.handle, table.handle, _p(d_scalars), size, wd, _p(d_out)))
+
+
+def commit_i32_host(ctx: Context, table: GeneratorTable, scalars: np.ndarray, wd: int, max_bits: int = 32,
+                    out: np.ndarray | None = None) -> np.ndarray:
+    """Host int32 tensor in, host Jacobian records (uint32[rows, 24]) out; copies included."""
+    scalars = np.ascontiguousarray(scalars, dtype=np.int32).reshape(-1)
+    rows = scalars.size // wd
+    if out is None:
+        out = np.empty((rows, 24), dtype=np.uint32)
+    ctx._check(ctx.lib.grape_commit_i32_host(ctx.handle, table.handle, scalars.ctypes.data, scalars.size, wd,
+                                             max_bits, out.ctypes.data))
+    return out

@@ -1,0 +1,163 @@
+/*
+ * grape_b200 -- C ABI of the B200 (sm_100a) proving hot path.
+ *
+ * This is the boundary a caller written against the reference's static library binds instead of
+ * the reference's CUDA sources.  Every entry point names the reference interface it replaces
+ * (path:line inside the reference project).  All functions return a GRAPE_* status, never throw,
+ * never trap the device; grape_ctx_error() returns the text of the last failure on a context.
+ *
+ * Data formats (identical to the reference's device records):
+ *   Fr element    32 B  eight little-endian 32-bit limbs, Montgomery form (value * 2^256 mod r)
+ *   affine point  64 B  X|Y over Fp, Montgomery form, all-zero = point at infinity
+ *   Jacobian      96 B  X|Y|Z; outputs are always normalised to Z = 1 (or X=Y=1, Z=0 for
+ *                       infinity) so that equal group elements have equal bytes
+ * Pointers whose name starts with d_ are device pointers on the context's GPU, h_ are host.
+ * Calls on one context are issued on that context's stream and are asynchronous unless stated.
+ */
+#ifndef GRAPE_B200_H
+#define GRAPE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GRAPE_OK 0
+#define GRAPE_ERR_INVALID 1 /* bad argument / shape (reference: std::runtime_error) */
+#define GRAPE_ERR_CUDA 2    /* CUDA runtime failure, text in grape_ctx_error */
+#define GRAPE_ERR_CHECK 3   /* a prover-side round check p(0)+p(1)==claim failed */
+#define GRAPE_ERR_NOMEM 4
+#define GRAPE_ERR_LIMIT 5 /* size beyond a documented fixed limit */
+
+#define GRAPE_FR_BYTES 32
+#define GRAPE_AFFINE_BYTES 64
+#define GRAPE_JACOBIAN_BYTES 96
+#define GRAPE_COM_SCALE 16 /* reference: Hyrax::com_scale, src/Hyrax.cu:229 */
+
+typedef struct grape_ctx grape_ctx;
+typedef struct grape_table grape_table;
+
+/* ---- context ------------------------------------------------------------------------------ */
+/* One context = one GPU + one stream + a grow-only scratch arena + a seedable RNG.  The
+ * reference has no such object (single device, default stream, src/Hyrax.cu:312-333 allocates
+ * and frees scratch in every call). */
+int grape_ctx_create(int device, grape_ctx** out);
+int grape_ctx_destroy(grape_ctx* ctx);
+const char* grape_ctx_error(const grape_ctx* ctx);
+int grape_ctx_sync(grape_ctx* ctx);
+void* grape_ctx_stream(grape_ctx* ctx); /* cudaStream_t */
+int grape_version(void);
+
+/* Seeds the stream that replaces libff's Fr::random_element() inside the provers
+ * (reference draws: src/tlookup.cu:247,293,351,403; src/Hyrax.cu:253-256). */
+int grape_rng_seed(grape_ctx* ctx, uint64_t seed);
+/* Draws n Fr elements (Montgomery form) from that stream into host memory. */
+int grape_rng_fr(grape_ctx* ctx, void* h_out, uint64_t n);
+
+/* ---- raw device memory (so that FFI callers need not bind the CUDA runtime) ---------------- */
+int grape_dev_alloc(grape_ctx* ctx, size_t bytes, void** d_out);
+int grape_dev_free(grape_ctx* ctx, void* d_ptr);
+int grape_h2d(grape_ctx* ctx, void* d_dst, const void* h_src, size_t bytes); /* async */
+int grape_d2h(grape_ctx* ctx, void* h_dst, const void* d_src, size_t bytes); /* synchronises */
+int grape_d2d(grape_ctx* ctx, void* d_dst, const void* d_src, size_t bytes);
+int grape_dev_zero(grape_ctx* ctx, void* d_dst, size_t bytes);
+
+/* ---- generator table ---------------------------------------------------------------------- */
+/* Fixed-base table  T[w][d-1][i] = (2^(window_bits*w) * d) * G_i  for d in 1..2^(window_bits-1),
+ * w < n_windows, affine.  Replaces precompute_generators / naive_msm
+ * (src/ec_operation.cu:15-49), whose table is w*G_i for w < 256.  window_bits is 8 or 16.
+ * d_gens_jacobian: n_gens Jacobian records (the reference's cpu_points layout). */
+int grape_table_create(grape_ctx* ctx, const void* d_gens_jacobian, uint32_t n_gens,
+                       uint32_t window_bits, uint32_t n_windows, grape_table** out);
+/* Wraps a table laid out like the reference's points.bin: 256 rows of n_gens affine points,
+ * row w = w*G_i (src/ec_operation.cu:24).  Borrows d_points (no copy). */
+int grape_table_from_reference(grape_ctx* ctx, const void* d_points, uint32_t n_gens,
+                               grape_table** out);
+int grape_table_destroy(grape_table* t);
+uint64_t grape_table_bytes(const grape_table* t);
+const void* grape_table_data(const grape_table* t);
+
+/* ---- Hyrax row commitments ---------------------------------------------------------------- */
+/* C_r = sum_{i<wd} s[r*wd+i] * G_i for the rows of an int32 tensor.
+ * Replaces Hyrax::commit(int*, size, N) (src/Hyrax.cu:312-333, kernels :46-87) with wd = N*16.
+ * max_bits: bound on the magnitude of the scalars, |s| <= 2^(max_bits-1) (32 = any int32,
+ * 16 = int16-range data); it only trims windows that are known to be zero.
+ * d_out: size/wd Jacobian records. */
+int grape_commit_i32(grape_ctx* ctx, const grape_table* t, const int32_t* d_scalars, uint64_t size,
+                     uint32_t wd, uint32_t max_bits, void* d_out);
+/* Same for Fr scalars (Montgomery form, not modified).  Replaces Hyrax::commit(FrTensor&, size, N)
+ * (src/Hyrax.cu:335-359, kernels :128-167) and single_commit (src/Hyrax.cu:176-185) for one row. */
+int grape_commit_fr(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t size,
+                    uint32_t wd, void* d_out);
+/* Host-buffer form of grape_commit_i32: copies the scalars in, commits, copies the Jacobian
+ * records out and synchronises (reference flow: load_data + commit + savebin, test/commit.cu:60-72). */
+int grape_commit_i32_host(grape_ctx* ctx, const grape_table* t, const int32_t* h_scalars,
+                          uint64_t size, uint32_t wd, uint32_t max_bits, void* h_out);
+
+/* ---- field tensors over Fr ---------------------------------------------------------------- */
+/* Device arrays of 32-byte Montgomery residues; n counts elements.  These replace the FrTensor
+ * kernels of src/fr-tensor.cu; outputs may alias inputs unless stated. */
+int grape_fr_from_i32(grape_ctx* ctx, const int32_t* d_in, void* d_out, uint64_t n);   /* int_to_fr :30-39 */
+int grape_fr_from_u32(grape_ctx* ctx, const uint32_t* d_in, void* d_out, uint64_t n);  /* uint_to_fr :41-46 */
+int grape_fr_to_mont(grape_ctx* ctx, void* d_t, uint64_t n);                           /* to_kernel :116-120 */
+int grape_fr_from_mont(grape_ctx* ctx, void* d_t, uint64_t n);                         /* from_kernel :110-114 */
+int grape_fr_add(grape_ctx* ctx, const void* d_a, const void* d_b, void* d_out, uint64_t n); /* :74-79 */
+int grape_fr_sub(grape_ctx* ctx, const void* d_a, const void* d_b, void* d_out, uint64_t n); /* :81-86 */
+int grape_fr_mul(grape_ctx* ctx, const void* d_a, const void* d_b, void* d_out, uint64_t n); /* :96-101 */
+/* out = a * s / out = a + s with s one Fr element in device memory (Fr_broadcast_mul/add :88-108) */
+int grape_fr_scale(grape_ctx* ctx, const void* d_a, const void* d_scalar, void* d_out, uint64_t n);
+int grape_fr_add_scalar(grape_ctx* ctx, const void* d_a, const void* d_scalar, void* d_out, uint64_t n);
+/* out = a * s + b  (z = c*x + d of Hyrax::open, src/Hyrax.cu:281-284) */
+int grape_fr_axpy(grape_ctx* ctx, const void* d_a, const void* d_scalar, const void* d_b, void* d_out,
+                  uint64_t n);
+/* out[i] = 1 / (in[i] + shift) with shift one device Fr element or NULL; zero maps to zero.
+ * Replaces inverse_kernel (:122-126) and tlookup_inv_kernel (src/tlookup.cu:52-62); batched. */
+int grape_fr_inverse(grape_ctx* ctx, const void* d_in, const void* d_shift, void* d_out, uint64_t n);
+/* Row padding n -> pad_n over pad_size output elements (pad_int_kernel / pad_fr_kernel :18-28).
+ * d_out must not alias d_in. */
+int grape_pad_i32(grape_ctx* ctx, const int32_t* d_in, int32_t* d_out, uint32_t n, uint32_t pad_n,
+                  uint64_t pad_size);
+int grape_fr_pad(grape_ctx* ctx, const void* d_in, void* d_out, uint32_t n, uint32_t pad_n,
+                 uint64_t pad_size, const void* d_pad_value);
+/* d_out[0] = sum of the first n elements (FrTensor::sum(sz), :415-440). */
+int grape_fr_sum(grape_ctx* ctx, const void* d_in, uint64_t n, void* d_out);
+/* Every element of a row replaced by the row sum (FrTensor::sum(sz, N) / sum_by_dim_kernel :155-163). */
+int grape_fr_rowsum(grape_ctx* ctx, const void* d_in, void* d_out, uint64_t rows, uint32_t dim);
+/* Multilinear fold of one axis: the first ntot elements of d_t are viewed as [other][c][gap]; axis c
+ * is folded with the challenges d_x[0 .. ceil(log2 c)) (variable 0 = lowest index bit, odd tails
+ * paired with zero) into d_out = [other][gap].  Same values as FrTensor::partial_eval(N, x, c, id, gap)
+ * (:53-72,168-188,330-344) called with x + id; d_out must not alias d_t, which is left intact. */
+int grape_fr_fold(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* d_x, uint32_t c,
+                  uint64_t gap, void* d_out);
+/* The same fold reading an int32 tensor directly (skips the 8x larger Fr copy the reference
+ * materialises first, src/fr-tensor.cu:376-381). */
+int grape_fold_i32(grape_ctx* ctx, const int32_t* d_t, uint64_t ntot, const void* d_x, uint32_t c,
+                   uint64_t gap, void* d_out);
+
+/* ---- diagnostics and measurement ----------------------------------------------------------- */
+/* Element-wise add (0) / sub (1) / mul (2) over the base field Fp; test hook for the curve code. */
+int grape_fp_binary(grape_ctx* ctx, int op, const void* d_a, const void* d_b, void* d_out, uint64_t n);
+/* Device status word: bit 0 = a scalar exceeded max_bits, bit 1 = lookup query outside its table.
+ * Kernels set bits instead of trapping; reading synchronises and clears. */
+int grape_ctx_status(grape_ctx* ctx, uint32_t* flags);
+/* Kernels launched by this library on the context so far. */
+uint64_t grape_ctx_launches(const grape_ctx* ctx);
+/* Measured integer-pipe ceilings (operations per second): kind 0 mad.lo.u32, 1 mad.wide.u32,
+ * 2 mad.lo.cc/madc.hi pairs (counted as two), 3 Fp Montgomery multiplications. */
+int grape_measure_int_peak(grape_ctx* ctx, int kind, double* ops_per_second);
+/* CUDA-event stopwatch on the context's stream; grape_timer_end synchronises. */
+int grape_timer_begin(grape_ctx* ctx);
+int grape_timer_end(grape_ctx* ctx, float* ms);
+/* Per-kernel timing of the dominant kernel of each call (events around it while enabled). */
+int grape_prof_enable(grape_ctx* ctx, int on);
+int grape_prof_read(grape_ctx* ctx, float* total_ms, uint32_t* count);
+/* Page-locked host memory for the host-buffer entry points. */
+int grape_host_alloc_pinned(grape_ctx* ctx, size_t bytes, void** h_out);
+int grape_host_free_pinned(grape_ctx* ctx, void* h_ptr);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GRAPE_B200_H */

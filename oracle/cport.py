@@ -1,0 +1,105 @@
+"""ctypes loader for ``oracle/liboracle.so`` (the C restatement in ``grape_oracle.c``).
+
+TEST INFRASTRUCTURE ONLY: the checker for full-size parity cases and the host-core baseline the
+benchmark reports.  ``build()`` compiles it with gcc.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+LIB = HERE / "liboracle.so"
+
+
+def build(force: bool = False) -> Path:
+    src = HERE / "grape_oracle.c"
+    if force or not LIB.exists() or LIB.stat().st_mtime < src.stat().st_mtime:
+        # -march=native is avoided: the library is built here and run on another machine
+        subprocess.run(["gcc", "-O3", "-fopenmp", "-fPIC", "-std=c11", "-shared", "-o", str(LIB), str(src)],
+                       check=True)
+    return LIB
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB.exists():
+            build()
+        _lib = C.CDLL(str(LIB))
+        vp, u64, u32 = C.c_void_p, C.c_uint64, C.c_uint32
+        _lib.oracle_threads.restype = C.c_int
+        _lib.oracle_fe_binary.argtypes = [C.c_int, C.c_int, vp, vp, vp, u64]
+        _lib.oracle_fr_from_i32.argtypes = [vp, vp, u64]
+        _lib.oracle_table_build.argtypes = [vp, u64, vp]
+        _lib.oracle_commit_i32.argtypes = [vp, u64, u64, u64, vp, u64, vp]
+        _lib.oracle_commit_fr.argtypes = [vp, u64, u64, u64, vp, u64, vp]
+        _lib.oracle_fr_fold.argtypes = [vp, u64, vp, u32, u32, u64]
+    return _lib
+
+
+def threads() -> int:
+    return lib().oracle_threads()
+
+
+def fe_binary(field: str, op: str, a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    a = np.ascontiguousarray(a, dtype=np.uint32).reshape(-1, 8)
+    b = np.ascontiguousarray(b, dtype=np.uint32).reshape(-1, 8)
+    out = np.empty_like(a)
+    lib().oracle_fe_binary({"fr": 0, "fp": 1}[field], {"add": 0, "sub": 1, "mul": 2}[op],
+                           a.ctypes.data, b.ctypes.data, out.ctypes.data, a.shape[0])
+    return out
+
+
+def fr_from_i32(x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.int32).reshape(-1)
+    out = np.empty((x.size, 8), dtype=np.uint32)
+    lib().oracle_fr_from_i32(x.ctypes.data, out.ctypes.data, x.size)
+    return out
+
+
+def table_build(gens_jacobian: np.ndarray) -> np.ndarray:
+    """uint32[n, 24] generators -> uint32[256, n, 16] table, row w = w * G_i (reference layout)."""
+    g = np.ascontiguousarray(gens_jacobian, dtype=np.uint32).reshape(-1, 24)
+    n = g.shape[0]
+    table = np.empty((256, n, 16), dtype=np.uint32)
+    lib().oracle_table_build(g.ctypes.data, n, table.ctypes.data)
+    return table
+
+
+def commit_i32(scalars: np.ndarray, wd: int, table: np.ndarray, row_begin: int = 0, row_end: int | None = None):
+    s = np.ascontiguousarray(scalars, dtype=np.int32).reshape(-1)
+    rows = s.size // wd
+    row_end = rows if row_end is None else row_end
+    out = np.empty((row_end - row_begin, 24), dtype=np.uint32)
+    lib().oracle_commit_i32(s.ctypes.data, wd, row_begin, row_end, table.ctypes.data, table.shape[1],
+                            out.ctypes.data)
+    return out
+
+
+def commit_fr(scalars: np.ndarray, wd: int, table: np.ndarray, row_begin: int = 0, row_end: int | None = None):
+    s = np.ascontiguousarray(scalars, dtype=np.uint32).reshape(-1, 8)
+    rows = s.shape[0] // wd
+    row_end = rows if row_end is None else row_end
+    out = np.empty((row_end - row_begin, 24), dtype=np.uint32)
+    lib().oracle_commit_fr(s.ctypes.data, wd, row_begin, row_end, table.ctypes.data, table.shape[1],
+                           out.ctypes.data)
+    return out
+
+
+def fr_fold(t: np.ndarray, ntot: int, x: np.ndarray, c: int, idx: int, gap: int) -> np.ndarray:
+    """The reference's in-place fold; returns the compacted [other][gap] front of the buffer."""
+    t = np.array(t, dtype=np.uint32).reshape(-1, 8).copy()
+    x = np.ascontiguousarray(x, dtype=np.uint32).reshape(-1, 8)
+    lib().oracle_fr_fold(t.ctypes.data, ntot, x.ctypes.data, c, idx, gap)
+    return t[: ntot // c]
+
+
+if __name__ == "__main__":
+    print(build(force=True))

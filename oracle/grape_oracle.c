@@ -1,0 +1,444 @@
+/*
+ * CPU oracle, part 3: a plain-C restatement (4 x 64-bit limbs, unsigned __int128) of the
+ * reference's commitment and field-tensor algorithms, fast enough to check full-size cases and
+ * to serve as the timed host-core baseline.
+ *
+ * TEST INFRASTRUCTURE ONLY.  Nothing the product ships links or calls this file; only tests/,
+ * the smoke check and the benchmark's CPU-baseline leg load liboracle.so, as the checker / the
+ * baseline being reported.
+ *
+ * Parity status: pinned against oracle/bn254.py (Python big integers) by
+ * tests/test_oracle_c.py; the reference itself ships no known-answer vectors.
+ *
+ * What each function follows (paths inside the reference project):
+ *   fe_mul / fe_add / fe_sub          include/field/mont_t.cuh:225-427 (Montgomery residues, R = 2^256)
+ *   xyzz_madd / xyzz_add / xyzz_dbl   include/curve/xyzz_t.cuh:129-441 (same group law, EFD formulas)
+ *   oracle_table_build                naive_msm, src/ec_operation.cu:15-27: table[w*n + i] = w * G_i, w < 256
+ *   oracle_commit_i32                 Hyrax::commit(int*), src/Hyrax.cu:46-87,312-333: four byte windows
+ *                                     of |s|, sign by point negation, window sums doubled 8w times
+ *   oracle_commit_fr                  Hyrax::commit(FrTensor&), src/Hyrax.cu:128-167,335-359: 32 byte windows
+ *   oracle_fr_from_i32                int_to_fr, src/fr-tensor.cu:30-39
+ *   oracle_fr_fold                    Fr_partial_me / partial_eval, src/fr-tensor.cu:53-72,168-188,330-344
+ */
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+typedef unsigned __int128 u128;
+typedef struct { uint64_t w[4]; } fe;
+
+typedef struct {
+  uint64_t mod[4], r2[4], one[4], inv;
+} field_t;
+
+static const field_t FP = {
+    {0x3c208c16d87cfd47ull, 0x97816a916871ca8dull, 0xb85045b68181585dull, 0x30644e72e131a029ull},
+    {0xf32cfc5b538afa89ull, 0xb5e71911d44501fbull, 0x47ab1eff0a417ff6ull, 0x06d89f71cab8351full},
+    {0xd35d438dc58f0d9dull, 0x0a78eb28f5c70b3dull, 0x666ea36f7879462cull, 0x0e0a77c19a07df2full},
+    0x87d20782e4866389ull};
+static const field_t FR = {
+    {0x43e1f593f0000001ull, 0x2833e84879b97091ull, 0xb85045b68181585dull, 0x30644e72e131a029ull},
+    {0x1bb8e645ae216da7ull, 0x53fe3ab1e35c59e3ull, 0x8c49833d53bb8085ull, 0x0216d0b17f4e44a5ull},
+    {0xac96341c4ffffffbull, 0x36fc76959f60cd29ull, 0x666ea36f7879462eull, 0x0e0a77c19a07df2full},
+    0xc2e1f593efffffffull};
+
+static inline int fe_is_zero(const fe* a) { return (a->w[0] | a->w[1] | a->w[2] | a->w[3]) == 0; }
+static inline int fe_eq(const fe* a, const fe* b) { return memcmp(a, b, 32) == 0; }
+
+static inline int geq(const uint64_t* a, const uint64_t* m) {
+  for (int i = 3; i >= 0; i--) {
+    if (a[i] > m[i]) return 1;
+    if (a[i] < m[i]) return 0;
+  }
+  return 1;
+}
+static inline void sub_n(uint64_t* r, const uint64_t* a, const uint64_t* b) {
+  u128 borrow = 0;
+  for (int i = 0; i < 4; i++) {
+    u128 d = (u128)a[i] - b[i] - borrow;
+    r[i] = (uint64_t)d;
+    borrow = (d >> 64) & 1;
+  }
+}
+static inline void fe_add(const field_t* F, fe* r, const fe* a, const fe* b) {
+  u128 c = 0;
+  fe t;
+  for (int i = 0; i < 4; i++) {
+    c += (u128)a->w[i] + b->w[i];
+    t.w[i] = (uint64_t)c;
+    c >>= 64;
+  }
+  if (geq(t.w, F->mod)) sub_n(t.w, t.w, F->mod);
+  *r = t;
+}
+static inline void fe_neg(const field_t* F, fe* r, const fe* a) {
+  if (fe_is_zero(a)) { *r = *a; return; }
+  sub_n(r->w, F->mod, a->w);
+}
+static inline void fe_sub(const field_t* F, fe* r, const fe* a, const fe* b) {
+  fe n;
+  fe_neg(F, &n, b);
+  fe_add(F, r, a, &n);
+}
+static inline void fe_mul(const field_t* F, fe* r, const fe* a, const fe* b) {
+  uint64_t t[6] = {0, 0, 0, 0, 0, 0};
+  for (int i = 0; i < 4; i++) {
+    u128 c = 0;
+    for (int j = 0; j < 4; j++) {
+      c += (u128)a->w[j] * b->w[i] + t[j];
+      t[j] = (uint64_t)c;
+      c >>= 64;
+    }
+    c += t[4];
+    t[4] = (uint64_t)c;
+    t[5] = (uint64_t)(c >> 64);
+    uint64_t m = t[0] * F->inv;
+    c = (u128)m * F->mod[0] + t[0];
+    c >>= 64;
+    for (int j = 1; j < 4; j++) {
+      c += (u128)m * F->mod[j] + t[j];
+      t[j - 1] = (uint64_t)c;
+      c >>= 64;
+    }
+    c += t[4];
+    t[3] = (uint64_t)c;
+    t[4] = t[5] + (uint64_t)(c >> 64);
+  }
+  fe o = {{t[0], t[1], t[2], t[3]}};
+  if (t[4] || geq(o.w, F->mod)) sub_n(o.w, o.w, F->mod);
+  *r = o;
+}
+static inline void fe_sqr(const field_t* F, fe* r, const fe* a) { fe_mul(F, r, a, a); }
+static void fe_inv(const field_t* F, fe* r, const fe* a) {
+  uint64_t e[4] = {F->mod[0] - 2, F->mod[1], F->mod[2], F->mod[3]};
+  fe acc;
+  memcpy(&acc, F->one, 32);
+  for (int i = 3; i >= 0; i--)
+    for (int b = 63; b >= 0; b--) {
+      fe_sqr(F, &acc, &acc);
+      if ((e[i] >> b) & 1) fe_mul(F, &acc, &acc, a);
+    }
+  *r = acc;
+}
+static inline void fe_to_mont(const field_t* F, fe* r, const fe* a) {
+  fe r2;
+  memcpy(&r2, F->r2, 32);
+  fe_mul(F, r, a, &r2);
+}
+static inline void fe_from_mont(const field_t* F, fe* r, const fe* a) {
+  fe one = {{1, 0, 0, 0}};
+  fe_mul(F, r, a, &one);
+}
+
+/* ------------------------------------------------------------------------------------------ */
+/* curve: records as in the reference (affine X|Y, (0,0) = infinity; xyzz X|Y|ZZZ|ZZ, ZZ = 0)  */
+/* ------------------------------------------------------------------------------------------ */
+typedef struct { fe x, y; } affine;
+typedef struct { fe x, y, zzz, zz; } xyzz;
+typedef struct { fe x, y, z; } jac;
+
+static inline int aff_is_inf(const affine* p) { return fe_is_zero(&p->x) && fe_is_zero(&p->y); }
+static inline void xyzz_set_inf(xyzz* p) { memset(p, 0, sizeof(*p)); }
+static inline int xyzz_is_inf(const xyzz* p) { return fe_is_zero(&p->zz); }
+
+static void xyzz_dbl(xyzz* r, const xyzz* p) {
+  if (xyzz_is_inf(p)) { *r = *p; return; }
+  fe U, V, W, S, M, t, X3, Y3;
+  fe_add(&FP, &U, &p->y, &p->y);
+  fe_sqr(&FP, &V, &U);
+  fe_mul(&FP, &W, &U, &V);
+  fe_mul(&FP, &S, &p->x, &V);
+  fe_sqr(&FP, &t, &p->x);
+  fe_add(&FP, &M, &t, &t);
+  fe_add(&FP, &M, &M, &t);
+  fe_sqr(&FP, &X3, &M);
+  fe_sub(&FP, &X3, &X3, &S);
+  fe_sub(&FP, &X3, &X3, &S);
+  fe_sub(&FP, &t, &S, &X3);
+  fe_mul(&FP, &Y3, &M, &t);
+  fe_mul(&FP, &t, &W, &p->y);
+  fe_sub(&FP, &Y3, &Y3, &t);
+  xyzz o;
+  o.x = X3;
+  o.y = Y3;
+  fe_mul(&FP, &o.zz, &V, &p->zz);
+  fe_mul(&FP, &o.zzz, &W, &p->zzz);
+  *r = o;
+}
+
+static void xyzz_add(xyzz* acc, const xyzz* q) {
+  if (xyzz_is_inf(q)) return;
+  if (xyzz_is_inf(acc)) { *acc = *q; return; }
+  fe U1, U2, S1, S2, Pd, Rd, PP, PPP, Q, t, X3, Y3;
+  fe_mul(&FP, &U1, &acc->x, &q->zz);
+  fe_mul(&FP, &U2, &q->x, &acc->zz);
+  fe_mul(&FP, &S1, &acc->y, &q->zzz);
+  fe_mul(&FP, &S2, &q->y, &acc->zzz);
+  fe_sub(&FP, &Pd, &U2, &U1);
+  fe_sub(&FP, &Rd, &S2, &S1);
+  if (fe_is_zero(&Pd)) {
+    if (fe_is_zero(&Rd)) xyzz_dbl(acc, acc);
+    else xyzz_set_inf(acc);
+    return;
+  }
+  fe_sqr(&FP, &PP, &Pd);
+  fe_mul(&FP, &PPP, &Pd, &PP);
+  fe_mul(&FP, &Q, &U1, &PP);
+  fe_sqr(&FP, &X3, &Rd);
+  fe_sub(&FP, &X3, &X3, &PPP);
+  fe_sub(&FP, &X3, &X3, &Q);
+  fe_sub(&FP, &X3, &X3, &Q);
+  fe_sub(&FP, &t, &Q, &X3);
+  fe_mul(&FP, &Y3, &Rd, &t);
+  fe_mul(&FP, &t, &S1, &PPP);
+  fe_sub(&FP, &Y3, &Y3, &t);
+  acc->x = X3;
+  acc->y = Y3;
+  fe_mul(&FP, &t, &acc->zz, &q->zz);
+  fe_mul(&FP, &acc->zz, &t, &PP);
+  fe_mul(&FP, &t, &acc->zzz, &q->zzz);
+  fe_mul(&FP, &acc->zzz, &t, &PPP);
+}
+
+/* acc += (+/-) q with q affine: 8 multiplications + 2 squarings, as include/curve/xyzz_t.cuh:363-441 */
+static void xyzz_madd(xyzz* acc, const affine* q, int negate) {
+  if (aff_is_inf(q)) return;
+  affine p = *q;
+  if (negate) fe_neg(&FP, &p.y, &p.y);
+  if (xyzz_is_inf(acc)) {
+    acc->x = p.x;
+    acc->y = p.y;
+    memcpy(&acc->zz, FP.one, 32);
+    memcpy(&acc->zzz, FP.one, 32);
+    return;
+  }
+  fe U2, S2, Pd, Rd, PP, PPP, Q, t, X3, Y3;
+  fe_mul(&FP, &U2, &p.x, &acc->zz);
+  fe_mul(&FP, &S2, &p.y, &acc->zzz);
+  fe_sub(&FP, &Pd, &U2, &acc->x);
+  fe_sub(&FP, &Rd, &S2, &acc->y);
+  if (fe_is_zero(&Pd)) {
+    if (fe_is_zero(&Rd)) {
+      xyzz d;
+      d.x = p.x;
+      d.y = p.y;
+      memcpy(&d.zz, FP.one, 32);
+      memcpy(&d.zzz, FP.one, 32);
+      xyzz_dbl(acc, &d);
+    } else {
+      xyzz_set_inf(acc);
+    }
+    return;
+  }
+  fe_sqr(&FP, &PP, &Pd);
+  fe_mul(&FP, &PPP, &Pd, &PP);
+  fe_mul(&FP, &Q, &acc->x, &PP);
+  fe_sqr(&FP, &X3, &Rd);
+  fe_sub(&FP, &X3, &X3, &PPP);
+  fe_sub(&FP, &X3, &X3, &Q);
+  fe_sub(&FP, &X3, &X3, &Q);
+  fe_sub(&FP, &t, &Q, &X3);
+  fe_mul(&FP, &Y3, &Rd, &t);
+  fe_mul(&FP, &t, &acc->y, &PPP);
+  fe_sub(&FP, &Y3, &Y3, &t);
+  acc->x = X3;
+  acc->y = Y3;
+  fe_mul(&FP, &acc->zz, &acc->zz, &PP);
+  fe_mul(&FP, &acc->zzz, &acc->zzz, &PPP);
+}
+
+static void xyzz_to_affine(affine* r, const xyzz* p) {
+  if (xyzz_is_inf(p)) { memset(r, 0, sizeof(*r)); return; }
+  fe t, izz, izzz;
+  fe_mul(&FP, &t, &p->zz, &p->zzz);
+  fe_inv(&FP, &t, &t);
+  fe_mul(&FP, &izz, &t, &p->zzz);
+  fe_mul(&FP, &izzz, &t, &p->zz);
+  fe_mul(&FP, &r->x, &p->x, &izz);
+  fe_mul(&FP, &r->y, &p->y, &izzz);
+}
+
+static void jac_store_normalised(jac* out, const xyzz* p) {
+  if (xyzz_is_inf(p)) {
+    memcpy(&out->x, FP.one, 32);
+    memcpy(&out->y, FP.one, 32);
+    memset(&out->z, 0, 32);
+    return;
+  }
+  affine a;
+  xyzz_to_affine(&a, p);
+  out->x = a.x;
+  out->y = a.y;
+  memcpy(&out->z, FP.one, 32);
+}
+
+static void xyzz_from_jac(xyzz* r, const jac* j) {
+  if (fe_is_zero(&j->z)) { xyzz_set_inf(r); return; }
+  r->x = j->x;
+  r->y = j->y;
+  fe_sqr(&FP, &r->zz, &j->z);
+  fe_mul(&FP, &r->zzz, &r->zz, &j->z);
+}
+
+/* ------------------------------------------------------------------------------------------ */
+/* exported API (ctypes)                                                                       */
+/* ------------------------------------------------------------------------------------------ */
+int oracle_threads(void) {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
+
+/* field element-wise: op 0 add, 1 sub, 2 mul; field 0 = Fr, 1 = Fp */
+void oracle_fe_binary(int field, int op, const fe* a, const fe* b, fe* out, uint64_t n) {
+  const field_t* F = field ? &FP : &FR;
+#pragma omp parallel for
+  for (int64_t i = 0; i < (int64_t)n; i++) {
+    if (op == 0) fe_add(F, &out[i], &a[i], &b[i]);
+    else if (op == 1) fe_sub(F, &out[i], &a[i], &b[i]);
+    else fe_mul(F, &out[i], &a[i], &b[i]);
+  }
+}
+
+void oracle_fr_from_i32(const int32_t* in, fe* out, uint64_t n) {
+#pragma omp parallel for
+  for (int64_t i = 0; i < (int64_t)n; i++) {
+    int64_t v = in[i];
+    fe t = {{(uint64_t)(v < 0 ? -v : v), 0, 0, 0}};
+    fe_to_mont(&FR, &t, &t);
+    if (v < 0) fe_neg(&FR, &t, &t);
+    out[i] = t;
+  }
+}
+
+/* table[w * n + i] = w * G_i for w < 256 (row 0 = infinity), affine.  The 255 multiples of one
+ * generator are normalised together (one inversion per generator). */
+void oracle_table_build(const jac* gens, uint64_t n, affine* table) {
+#pragma omp parallel for
+  for (int64_t i = 0; i < (int64_t)n; i++) {
+    xyzz g, acc, pts[256];
+    fe pref[256], run, inv, zp, t;
+    xyzz_from_jac(&g, &gens[i]);
+    xyzz_set_inf(&acc);
+    memcpy(&run, FP.one, 32);
+    for (int w = 0; w < 256; w++) {
+      pts[w] = acc;
+      if (!xyzz_is_inf(&acc)) {
+        fe_mul(&FP, &zp, &acc.zz, &acc.zzz);
+        fe_mul(&FP, &run, &run, &zp);
+      }
+      pref[w] = run;
+      xyzz_add(&acc, &g);
+    }
+    fe_inv(&FP, &inv, &run);
+    for (int w = 255; w >= 0; w--) {
+      affine* out = &table[(uint64_t)w * n + i];
+      if (xyzz_is_inf(&pts[w])) { memset(out, 0, sizeof(*out)); continue; }
+      fe zinv;
+      if (w == 0) zinv = inv; else fe_mul(&FP, &zinv, &inv, &pref[w - 1]);
+      fe_mul(&FP, &zp, &pts[w].zz, &pts[w].zzz);
+      fe_mul(&FP, &inv, &inv, &zp);
+      fe_mul(&FP, &t, &zinv, &pts[w].zzz);
+      fe_mul(&FP, &out->x, &pts[w].x, &t);
+      fe_mul(&FP, &t, &zinv, &pts[w].zz);
+      fe_mul(&FP, &out->y, &pts[w].y, &t);
+    }
+  }
+}
+
+/* one commitment row with byte windows: scalars given as nbytes little-endian magnitude bytes */
+static void commit_row_bytes(const uint8_t* mags, const uint8_t* negs, int nbytes, uint64_t wd,
+                             const affine* table, uint64_t npoints, jac* out) {
+  xyzz total;
+  xyzz_set_inf(&total);
+  for (int w = nbytes - 1; w >= 0; w--) {
+    for (int k = 0; k < 8; k++) xyzz_dbl(&total, &total);
+    xyzz sum;
+    xyzz_set_inf(&sum);
+    for (uint64_t i = 0; i < wd; i++) {
+      uint8_t d = mags[i * nbytes + w];
+      if (d) xyzz_madd(&sum, &table[(uint64_t)d * npoints + i], negs ? negs[i] : 0);
+    }
+    xyzz_add(&total, &sum);
+  }
+  jac_store_normalised(out, &total);
+}
+
+/* C_r = sum_i s[r*wd + i] * G_i; rows [row_begin, row_end) only (for bounded samples) */
+void oracle_commit_i32(const int32_t* scalars, uint64_t wd, uint64_t row_begin, uint64_t row_end,
+                       const affine* table, uint64_t npoints, jac* out) {
+#pragma omp parallel
+  {
+    uint8_t* mags = (uint8_t*)malloc(wd * 4);
+    uint8_t* negs = (uint8_t*)malloc(wd);
+#pragma omp for schedule(dynamic, 1)
+    for (int64_t r = (int64_t)row_begin; r < (int64_t)row_end; r++) {
+      for (uint64_t i = 0; i < wd; i++) {
+        int64_t v = scalars[(uint64_t)r * wd + i];
+        uint32_t a = (uint32_t)(v < 0 ? -v : v);
+        negs[i] = v < 0;
+        memcpy(&mags[i * 4], &a, 4);
+      }
+      commit_row_bytes(mags, negs, 4, wd, table, npoints, &out[r - row_begin]);
+    }
+    free(mags);
+    free(negs);
+  }
+}
+
+void oracle_commit_fr(const fe* scalars, uint64_t wd, uint64_t row_begin, uint64_t row_end,
+                      const affine* table, uint64_t npoints, jac* out) {
+#pragma omp parallel
+  {
+    uint8_t* mags = (uint8_t*)malloc(wd * 32);
+#pragma omp for schedule(dynamic, 1)
+    for (int64_t r = (int64_t)row_begin; r < (int64_t)row_end; r++) {
+      for (uint64_t i = 0; i < wd; i++) {
+        fe s;
+        fe_from_mont(&FR, &s, &scalars[(uint64_t)r * wd + i]);
+        memcpy(&mags[i * 32], &s, 32);
+      }
+      commit_row_bytes(mags, NULL, 32, wd, table, npoints, &out[r - row_begin]);
+    }
+    free(mags);
+  }
+}
+
+/* In-place fold exactly as the reference does it: view [other][c][gap], log2ceil(c) passes pairing
+ * (2j, 2j+1) with challenge x[id + pass], then compaction to [other][gap]. */
+void oracle_fr_fold(fe* t, uint64_t ntot, const fe* x, uint32_t c, uint32_t id, uint64_t gap) {
+  uint64_t other = ntot / ((uint64_t)c * gap);
+  uint64_t dim = (uint64_t)c * gap;
+  uint32_t cin = c;
+  uint64_t g = gap;
+  uint32_t passes = 0;
+  for (uint32_t v = c - 1; c > 1 && v > 0; v >>= 1) passes++;
+  for (uint32_t p = 0; p < passes; p++) {
+    uint32_t cout = (cin + 1) / 2;
+    const fe* xv = &x[id + p];
+#pragma omp parallel for collapse(2)
+    for (int64_t o = 0; o < (int64_t)other; o++)
+      for (int64_t j = 0; j < (int64_t)cout; j++)
+        for (uint64_t k = 0; k < gap; k++) {
+          fe* lo = &t[o * dim + (2 * j) * g + k];
+          fe d, m;
+          if ((uint32_t)(2 * j + 1) < cin) {
+            fe* hi = &t[o * dim + (2 * j + 1) * g + k];
+            fe_sub(&FR, &d, hi, lo);
+            fe_mul(&FR, &m, xv, &d);
+            fe_add(&FR, lo, lo, &m);
+          } else {
+            fe_mul(&FR, &m, xv, lo);
+            fe_sub(&FR, lo, lo, &m);
+          }
+        }
+    g <<= 1;
+    cin = cout;
+  }
+  for (uint64_t o = 1; o < other; o++) memmove(&t[o * gap], &t[o * dim], gap * sizeof(fe));
+}
