@@ -229,6 +229,12 @@ k_fold_inner(const void* __restrict__ t, const uint32_t* __restrict__ w, uint32_
   if (threadIdx.x == 0) acc.store(out + o * 8);
 }
 
+void eq_weights_async(grape_ctx* ctx, const void* d_x, uint32_t nv, uint32_t c, void* d_w) {
+  if (c == 0) return;
+  k_eq_weights<<<ew_blocks(ctx, c), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_x, nv, c, (uint32_t*)d_w);
+  ctx->launches += 1;
+}
+
 // ---- host-side launch helpers shared with the provers ---------------------------------------
 // d_out = sum of n elements.  Uses its own arena allocation for the per-block partial sums.
 int fr_sum_async(grape_ctx* ctx, const void* d_in, uint64_t n, void* d_out) {
