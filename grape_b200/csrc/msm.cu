@@ -19,6 +19,8 @@
 //                       lane 0 writes the partial sum to scratch memory.
 //   commit_finalize:    one thread per row adds the chunk partials, normalises (one inversion)
 //                       and writes the canonical Jacobian record.
+#include <algorithm>
+
 #include "ctx.cuh"
 #include "curve.cuh"
 

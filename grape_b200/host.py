@@ -299,3 +299,54 @@ def commit_i32_host(ctx: Context, table: GeneratorTable, scalars: np.ndarray, wd
     ctx._check(ctx.lib.grape_commit_i32_host(ctx.handle, table.handle, scalars.ctypes.data, scalars.size, wd,
                                              max_bits, out.ctypes.data))
     return out
+
+
+# ----------------------------------------------------------------------------- sumcheck provers
+def _fr_host(values) -> np.ndarray:
+    return np.ascontiguousarray(encode_field(values))
+
+
+def prove_matmul(ctx: Context, d_A, d_B, L: int, N: int, M: int, K: int, u, v, claim: int):
+    """``prove_matmul``: returns (A_claim, B_claim, final_claim, transcript) as Python integers; the
+    transcript is a list of 4-coefficient round polynomials (degree-2 rounds end with a zero).
+    d_A and d_B are consumed."""
+    hu, hv = _fr_host(u), _fr_host(v)
+    hc = _fr_host([claim])
+    out = np.zeros((2, 8), dtype=np.uint32)
+    cap = len(u) + len(v) + 4
+    tr = np.zeros((cap, 4, 8), dtype=np.uint32)
+    nr = C.c_uint32()
+    ctx._check(ctx.lib.grape_prove_matmul(ctx.handle, _p(d_A), _p(d_B), L, N, M, K, hu.ctypes.data, len(u),
+                                          hv.ctypes.data, len(v), hc.ctypes.data, out.ctypes.data,
+                                          tr.ctypes.data, cap, C.byref(nr)))
+    a, b = decode_field(out)
+    polys = [decode_field(tr[i]) for i in range(nr.value)]
+    return a, b, decode_field(hc)[0], polys
+
+
+def prove_elemul(ctx: Context, d_A, d_B, L: int, M: int, N: int, u, v, claim: int):
+    hu, hv = _fr_host(u), _fr_host(v)
+    hc = _fr_host([claim])
+    out = np.zeros((2, 8), dtype=np.uint32)
+    cap = len(u) + 4
+    tr = np.zeros((cap, 4, 8), dtype=np.uint32)
+    nr = C.c_uint32()
+    ctx._check(ctx.lib.grape_prove_elemul(ctx.handle, _p(d_A), _p(d_B), L, M, N, hu.ctypes.data, len(u),
+                                          hv.ctypes.data, len(v), hc.ctypes.data, out.ctypes.data,
+                                          tr.ctypes.data, cap, C.byref(nr)))
+    a, b = decode_field(out)
+    return a, b, decode_field(hc)[0], [decode_field(tr[i]) for i in range(nr.value)]
+
+
+def combine_claims(ctx: Context, d_X, size: int, claims, us, v):
+    k, nv = len(claims), len(v)
+    hcl = _fr_host(claims)
+    hus = _fr_host([x for uj in us for x in uj])
+    hv = _fr_host(v)
+    out = np.zeros((1, 8), dtype=np.uint32)
+    tr = np.zeros((nv + 1, 4, 8), dtype=np.uint32)
+    nr = C.c_uint32()
+    ctx._check(ctx.lib.grape_combine_claims(ctx.handle, _p(d_X), size, hcl.ctypes.data, k, hus.ctypes.data,
+                                            hv.ctypes.data, nv, out.ctypes.data, tr.ctypes.data, nv + 1,
+                                            C.byref(nr)))
+    return decode_field(out)[0], [decode_field(tr[i]) for i in range(nr.value)]

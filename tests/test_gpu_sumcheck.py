@@ -1,0 +1,89 @@
+"""Parity of the sumcheck provers with the oracle: returned claims and every round polynomial."""
+import random
+
+import pytest
+
+from oracle import bn254
+from oracle import protocols as pr
+
+pytestmark = pytest.mark.gpu
+R = bn254.R
+
+
+def _mle(t, u):
+    n = 1 << len(u)
+    return pr.partial_eval(list(t) + [0] * (n - len(t)), n, u, n, 0, 1)[0]
+
+
+def _pad4(polys):
+    return [list(p) + [0] * (4 - len(p)) for p in polys]
+
+
+@pytest.mark.parametrize("L,N,M,K", [(1, 4, 8, 6), (2, 4, 2, 6), (4, 2, 4, 11), (1, 2, 2, 8), (1, 16, 8, 300), (2, 4, 8, 64), (1, 3, 8, 33)])
+def test_prove_matmul(gctx, L, N, M, K):
+    from grape_b200 import host
+    rng = random.Random(L * 1000 + N * 100 + M * 10 + K)
+    draw = bn254.SplitMix64(K, 5)
+    A = [rng.randrange(-2**15, 2**15) % R for _ in range(L * N * K)]
+    B = [rng.randrange(-2**15, 2**15) % R for _ in range(L * M * K)]
+    u = draw.fr_vec(pr.log2ceil(M) + pr.log2ceil(N) + pr.log2ceil(L))
+    v = draw.fr_vec(pr.log2ceil(K) + pr.log2ceil(L))
+    Mp, Np = 1 << pr.log2ceil(M), 1 << pr.log2ceil(N)
+    Y = [0] * (L * Np * Mp)
+    for l in range(L):
+        for n in range(N):
+            for m in range(M):
+                Y[(l * Np + n) * Mp + m] = sum(A[(l * N + n) * K + k] * B[(l * M + m) * K + k] for k in range(K)) % R
+    claim = _mle(Y, u)
+    want = pr.prove_matmul(A, B, L, N, M, K, u, v, claim)
+    dA, dB = gctx.fr_upload(A), gctx.fr_upload(B)
+    got = host.prove_matmul(gctx, dA, dB, L, N, M, K, u, v, claim)
+    assert got[0] == want[0] and got[1] == want[1] and got[2] == want[2]
+    assert got[3] == _pad4(want[3])
+
+
+def test_prove_matmul_rejects_wrong_claim(gctx):
+    import grape_b200 as g
+    from grape_b200 import host
+    rng = random.Random(5)
+    L, N, M, K = 1, 2, 2, 4
+    A = [rng.randrange(R) for _ in range(L * N * K)]
+    B = [rng.randrange(R) for _ in range(L * M * K)]
+    u = [rng.randrange(R) for _ in range(2)]
+    v = [rng.randrange(R) for _ in range(2)]
+    with pytest.raises(g.GrapeError) as e:
+        host.prove_matmul(gctx, gctx.fr_upload(A), gctx.fr_upload(B), L, N, M, K, u, v, 12345)
+    assert e.value.code == 3  # GRAPE_ERR_CHECK, the reference throws std::runtime_error here
+
+
+@pytest.mark.parametrize("L,M,N", [(2, 2, 6), (1, 4, 4), (2, 2, 11), (1, 1, 8), (4, 8, 37)])
+def test_prove_elemul(gctx, L, M, N):
+    from grape_b200 import host
+    rng = random.Random(L * 100 + M * 10 + N)
+    A = [rng.randrange(R) for _ in range(L * M * N)]
+    B = [rng.randrange(R) for _ in range(L * M * N)]
+    Np = 1 << pr.log2ceil(N)
+    pad = lambda X: [x for i in range(L * M) for x in X[i * N:(i + 1) * N] + [0] * (Np - N)]
+    nv = pr.log2ceil(L * M * N)
+    u = [rng.randrange(R) for _ in range(nv)]
+    v = [rng.randrange(R) for _ in range(nv)]
+    claim = _mle(pad([x * y % R for x, y in zip(A, B)]), u)
+    want = pr.prove_elemul(A, B, L, M, N, u, v, claim)
+    got = host.prove_elemul(gctx, gctx.fr_upload(A), gctx.fr_upload(B), L, M, N, u, v, claim)
+    assert got[:3] == want[:3]
+    assert got[3] == _pad4(want[3])
+
+
+@pytest.mark.parametrize("nv,k", [(4, 3), (1, 1), (7, 2), (10, 4)])
+def test_combine_claims(gctx, nv, k):
+    from grape_b200 import host
+    rng = random.Random(nv * 10 + k)
+    size = 1 << nv
+    X = [rng.randrange(R) for _ in range(size)]
+    us = [[rng.randrange(R) for _ in range(nv)] for _ in range(k)]
+    v = [rng.randrange(R) for _ in range(nv)]
+    claims = [_mle(X, uj) for uj in us]
+    want_ret, want_tr = pr.combine_claims(X, claims, us, v, size)
+    got_ret, got_tr = host.combine_claims(gctx, gctx.fr_upload(X), size, claims, us, v)
+    assert got_ret == want_ret == _mle(X, v)
+    assert got_tr == _pad4(want_tr)
