@@ -439,3 +439,144 @@ extern "C" int grape_commit_i32_host(grape_ctx* ctx, const grape_table* t, const
   GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
   return GRAPE_OK;
 }
+
+// ------------------------------------------------------------------------------------------
+// Commitment without any allocation
+// ------------------------------------------------------------------------------------------
+// For callers that must not allocate device memory at the moment they commit: code that runs
+// inside a memory-pool-managed framework where a stray cudaMalloc would synchronise the device
+// or fragment the pool, latency-critical serving loops, and hosts whose GPU memory is already
+// fully handed out to other buffers.  The per-(row, chunk) partial sums that the other entry
+// points keep in the context's scratch arena live here in a fixed array inside the library image.
+// Every GPU that loads the library holds that array (GRAPE_STATIC_SCRATCH_BYTES) until exit.
+constexpr uint64_t STATIC_MAX_UNITS = 65536;  // rows x chunks per call
+static __device__ __align__(256) unsigned char g_static_partials[STATIC_MAX_UNITS * sizeof(grape::Xyzz)];
+static __device__ __align__(256) uint32_t g_static_status[64];
+
+namespace {
+struct StaticDeviceState {
+  bool ready = false;
+  void* partials = nullptr;  // device address of g_static_partials on this device
+  uint32_t* status = nullptr;
+  int sm_count = 0;
+};
+StaticDeviceState g_static_state[64];
+char g_static_error[256] = "";
+
+// Resolves the device addresses of the static arrays for the CURRENT device, once per device.
+// In host code the array names are only stand-ins; the kernels must be given these addresses.
+int static_setup(int device, StaticDeviceState** out) {
+  if (device < 0 || device >= 64) {
+    snprintf(g_static_error, sizeof g_static_error, "device index %d out of range", device);
+    return GRAPE_ERR_LIMIT;
+  }
+  StaticDeviceState& st = g_static_state[device];
+  if (!st.ready) {
+    void* p = nullptr;
+    void* s = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_static_partials);
+    if (e == cudaSuccess) e = cudaGetSymbolAddress(&s, g_static_status);
+    int sms = 0;
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    if (e != cudaSuccess) {
+      snprintf(g_static_error, sizeof g_static_error, "static scratch set-up failed: %s", cudaGetErrorString(e));
+      return GRAPE_ERR_CUDA;
+    }
+    st.partials = p;
+    st.status = reinterpret_cast<uint32_t*>(s);
+    st.sm_count = sms;
+    st.ready = true;
+  }
+  *out = &st;
+  return GRAPE_OK;
+}
+}  // namespace
+
+extern "C" uint64_t grape_static_scratch_bytes(void) { return sizeof(g_static_partials); }
+extern "C" const char* grape_static_error(void) { return g_static_error; }
+
+// Same result as grape_commit_i32, for a table laid out as grape_table_create builds it
+// (d_table = grape_table_data, same n_gens / window_bits / n_windows), on the current device
+// and the given stream (NULL = default stream).  It calls no cudaMalloc, cudaFree or any routine
+// that allocates; inputs, outputs and the table are the caller's.
+//   * Limit: (size / wd) * chunks <= 65536 partial sums, where the number of chunks per row is
+//     what fills the GPU when there are few rows; more than 65536 rows is rejected with
+//     GRAPE_ERR_LIMIT (text in grape_static_error()).
+//   * The first call on a device resolves the address of the library's static scratch for that
+//     device (cudaGetSymbolAddress with that device current); make that first call outside any
+//     stream capture.
+//   * All calls on a device share the one static array, which keeps whatever the previous call
+//     left in it.  Each call overwrites every partial it later reads and clears the status word
+//     first, so back-to-back calls on one stream are fine; two calls whose kernels can overlap
+//     on the GPU (different streams, different threads) race on it.
+//   * h_status (may be NULL): if given, the call synchronises the stream and stores 1 there when
+//     some scalar exceeded max_bits (that scalar's out-of-range digit is skipped), else 0.
+extern "C" int grape_commit_i32_static(const void* d_table, uint32_t n_gens, uint32_t window_bits,
+                                       uint32_t n_windows, const int32_t* d_scalars, uint64_t size, uint32_t wd,
+                                       uint32_t max_bits, void* d_out, void* stream, uint32_t* h_status) {
+  if (!d_table || !d_scalars || !d_out) {
+    snprintf(g_static_error, sizeof g_static_error, "null argument");
+    return GRAPE_ERR_INVALID;
+  }
+  if ((window_bits != 8 && window_bits != 16) || n_windows == 0 || wd == 0 || wd > n_gens || size % wd != 0 ||
+      max_bits == 0 || max_bits > 32) {
+    snprintf(g_static_error, sizeof g_static_error, "bad geometry (window_bits 8|16, wd <= n_gens, size %% wd == 0, max_bits 1..32)");
+    return GRAPE_ERR_INVALID;
+  }
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) {
+    snprintf(g_static_error, sizeof g_static_error, "no current CUDA device");
+    return GRAPE_ERR_CUDA;
+  }
+  StaticDeviceState* st = nullptr;
+  int rc = static_setup(device, &st);
+  if (rc) return rc;
+  const uint64_t rows = size / wd;
+  if (rows == 0) return GRAPE_OK;
+  // chunks per row: as in the arena-backed path, but capped by the static array
+  uint64_t target_warps = (uint64_t)st->sm_count * 32;
+  uint64_t n_chunks = 1;
+  if (rows < target_warps) {
+    n_chunks = std::min<uint64_t>((target_warps + rows - 1) / rows, (wd + 63) / 64);
+    if (n_chunks < 1) n_chunks = 1;
+  }
+  while (n_chunks > 1 && rows * n_chunks > STATIC_MAX_UNITS) n_chunks--;
+  if (rows * n_chunks > STATIC_MAX_UNITS) {
+    snprintf(g_static_error, sizeof g_static_error, "%llu rows exceed the static scratch limit of %llu partial sums",
+             (unsigned long long)rows, (unsigned long long)STATIC_MAX_UNITS);
+    return GRAPE_ERR_LIMIT;
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  TableView view;
+  view.base = reinterpret_cast<const Affine*>(d_table);
+  view.n_gens = n_gens;
+  view.window_bits = window_bits;
+  view.n_windows = n_windows;
+  view.half = 1u << (window_bits - 1);
+  view.window_stride = (uint64_t)view.half * n_gens;
+  view.first_row = 0;
+  const uint32_t total_windows = (max_bits + window_bits - 1) / window_bits;
+  const uint32_t chunk_len = (uint32_t)((wd + n_chunks - 1) / n_chunks);
+  const uint64_t units = rows * n_chunks;
+  const uint64_t blocks = (units + MSM_THREADS / 32 - 1) / (MSM_THREADS / 32);
+  Xyzz* partials = reinterpret_cast<Xyzz*>(st->partials);
+  cudaError_t e = cudaMemsetAsync(st->status, 0, sizeof(uint32_t), s);  // must start at zero
+  if (e == cudaSuccess) {
+    commit_accumulate_kernel<false><<<(uint32_t)blocks, MSM_THREADS, 0, s>>>(
+        d_scalars, view, wd, total_windows, (uint32_t)n_chunks, chunk_len, units, partials, st->status);
+    commit_finalize_kernel<<<(uint32_t)((rows + 127) / 128), 128, 0, s>>>(partials, (uint32_t)n_chunks, rows,
+                                                                          reinterpret_cast<Jacobian*>(d_out));
+    e = cudaGetLastError();
+  }
+  if (e == cudaSuccess && h_status) {
+    uint32_t flag = 0;
+    e = cudaMemcpyAsync(&flag, st->status, sizeof(uint32_t), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    *h_status = flag ? 1u : 0u;
+  }
+  if (e != cudaSuccess) {
+    snprintf(g_static_error, sizeof g_static_error, "grape_commit_i32_static: %s", cudaGetErrorString(e));
+    return GRAPE_ERR_CUDA;
+  }
+  return GRAPE_OK;
+}

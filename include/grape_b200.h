@@ -136,6 +136,32 @@ int grape_fr_fold(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* d_
 int grape_fold_i32(grape_ctx* ctx, const int32_t* d_t, uint64_t ntot, const void* d_x, uint32_t c,
                    uint64_t gap, void* d_out);
 
+/* ---- allocation-free commitment ------------------------------------------------------------ */
+/* No counterpart in the reference (its commit allocates and frees scratch on every call,
+ * src/Hyrax.cu:312-333).  For embedders that may not allocate GPU memory when they commit --
+ * a framework that owns all device memory through its own pool, a serving loop that cannot
+ * afford cudaMalloc's implicit device synchronisation -- this variant of grape_commit_i32 keeps
+ * its per-(row, chunk) partial sums in a fixed 8 MiB array inside the library image instead of
+ * the context's arena.  It takes no context: d_table / n_gens / window_bits / n_windows describe
+ * a table as grape_table_create lays it out (grape_table_data returns the pointer), the work runs
+ * on the current CUDA device and on `stream` (a cudaStream_t, NULL = default stream).
+ *   - calls no cudaMalloc / cudaFree / allocating routine;
+ *   - at most 65536 partial sums per call: more than 65536 rows returns GRAPE_ERR_LIMIT
+ *     (message from grape_static_error());
+ *   - the first call on each device looks up the device address of the static array; issue that
+ *     first call outside any stream capture;
+ *   - all calls on a device share the array and it keeps the previous call's contents; each call
+ *     rewrites what it reads and clears its status word, so calls queued on one stream are safe,
+ *     calls that can overlap on the GPU race;
+ *   - h_status may be NULL; otherwise the call synchronises `stream` and stores 1 when a scalar
+ *     exceeded max_bits, else 0.
+ * Every GPU that loads the library holds the array until the process exits. */
+int grape_commit_i32_static(const void* d_table, uint32_t n_gens, uint32_t window_bits, uint32_t n_windows,
+                            const int32_t* d_scalars, uint64_t size, uint32_t wd, uint32_t max_bits,
+                            void* d_out, void* stream, uint32_t* h_status);
+uint64_t grape_static_scratch_bytes(void);
+const char* grape_static_error(void);
+
 /* ---- diagnostics and measurement ----------------------------------------------------------- */
 /* Element-wise add (0) / sub (1) / mul (2) over the base field Fp; test hook for the curve code. */
 int grape_fp_binary(grape_ctx* ctx, int op, const void* d_a, const void* d_b, void* d_out, uint64_t n);
