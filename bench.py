@@ -48,6 +48,8 @@ def parse_args():
     ap.add_argument("--window-bits", type=int, default=16, choices=[8, 16])
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target length of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--rows", type=int, default=0, help="commit only this many rows (reduced case for profiling)")
+    ap.add_argument("--gens", type=int, default=WD, help="generators = scalars per row (reduced case for profiling)")
     return ap.parse_args()
 
 
@@ -202,9 +204,10 @@ def run_own(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ctx = g.Context(local_rank)
 
-    n = wl.layer_weight_elements()
-    rows = n // WD
-    gens = wl.make_generators(ctx, WD, SEED)                  # same generators on every rank
+    wd = args.gens
+    n = wl.layer_weight_elements() if not args.rows else args.rows * wd
+    rows = n // wd
+    gens = wl.make_generators(ctx, wd, SEED)                  # same generators on every rank
     bits = 16
     n_windows = 1 if args.window_bits == 16 else 2
     table = g.GeneratorTable(ctx, gens, args.window_bits, n_windows)
@@ -218,10 +221,10 @@ def run_own(args):
     d_out = ctx.alloc(rows * 96)
 
     def step_device():
-        g.commit_i32(ctx, table, d_scalars, n, WD, d_out, max_bits=bits)
+        g.commit_i32(ctx, table, d_scalars, n, wd, d_out, max_bits=bits)
 
     def step_host():
-        g.commit_i32_host(ctx, table, h_scalars, WD, max_bits=bits, out=h_out)
+        g.commit_i32_host(ctx, table, h_scalars, wd, max_bits=bits, out=h_out)
 
     def barrier():
         ctx.sync()
@@ -300,14 +303,16 @@ def run_own(args):
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "u32 limbs (254-bit fields)", "data": "synthetic",
-            "config": workload_config(args.window_bits), "clocks": clocks,
+            "config": workload_config(args.window_bits) if not args.rows else
+            {"workload": f"reduced case for profiling: {rows} rows x {wd} generators", "window_bits": args.window_bits},
+            "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(n * 4),
                     "d2h_bytes_per_step": int(rows * 96), "ms_per_step": e2e_ms / args.steps,
                     "matches_device_path": host_path_matches},
             "gpu_launches": int(launches), "roofline": roofline, "device_status": status,
             "table_bytes": table.nbytes}
 
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and wd == WD:
         base, rows_used, rec = cpu_baseline(gens, np.asarray(h_scalars), args.cpu_seconds)
         base["matches_gpu_rows"] = bool(np.array_equal(rec, dev_records[:rows_used]))
         line["cpu_baseline"] = base
