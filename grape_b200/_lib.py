@@ -106,6 +106,15 @@ def _declare(lib):
     f("grape_prove_matmul", [vp, vp, vp, u32, u32, u32, u32, vp, u32, vp, u32, vp, vp, vp, u32, C.POINTER(u32)])
     f("grape_prove_elemul", [vp, vp, vp, u32, u32, u32, vp, u32, vp, u32, vp, vp, vp, u32, C.POINTER(u32)])
     f("grape_combine_claims", [vp, vp, u64, vp, u32, vp, vp, u32, vp, vp, u32, C.POINTER(u32)])
+    f("grape_lookup_range_create", [vp, C.c_int32, u32, C.POINTER(vp)])
+    f("grape_lookup_mapping_create", [vp, C.c_int32, u32, vp, C.POINTER(vp)])
+    f("grape_lookup_destroy", [vp])
+    f("grape_lookup_params", [vp, vp, vp, vp, C.POINTER(u32)])
+    f("grape_lookup_table", [vp, C.c_int], vp)
+    f("grape_lookup_prove_range", [vp, vp, vp, u64, vp, vp, u32, u32, u32, vp, u32, vp, vp, vp, vp, u32, C.POINTER(u32)])
+    f("grape_lookup_prove_mapping", [vp, vp, vp, vp, u64, vp, vp, vp, u32, u32, u32, vp, u32, vp, vp, vp, vp, u32,
+                                     C.POINTER(u32)])
+    f("grape_hyrax_open", [vp, vp, vp, u64, u32, u32, vp, u32, vp, vp, vp, vp, vp, vp])
     for name in _OPTIONAL:
         if hasattr(lib, name):
             f(name, _OPTIONAL[name])

@@ -377,10 +377,10 @@ extern "C" int grape_fr_axpy(grape_ctx* ctx, const void* d_a, const void* d_scal
   k_axpy<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_a, (const uint32_t*)d_scalar, (const uint32_t*)d_b, (uint32_t*)d_out, n);
   LAUNCH_DONE(ctx, 1);
 }
-extern "C" int grape_fr_inverse(grape_ctx* ctx, const void* d_in, const void* d_shift, void* d_out, uint64_t n) {
-  CHECK_CTX(ctx);
+namespace grape {
+// out[i] = 1 / (in[i] + shift); takes its prefix-product scratch from the arena without resetting it.
+int fr_inverse_async(grape_ctx* ctx, const void* d_in, const void* d_shift, void* d_out, uint64_t n) {
   if (n == 0) return GRAPE_OK;
-  arena_reset(ctx);
   void* scratch;
   int rc = arena_alloc(ctx, n * 32, &scratch);
   if (rc) return rc;
@@ -390,7 +390,15 @@ extern "C" int grape_fr_inverse(grape_ctx* ctx, const void* d_in, const void* d_
   if (threads < min_threads) threads = std::min<uint64_t>(n, min_threads);
   uint32_t blocks = (uint32_t)((threads + 127) / 128);
   k_batch_inverse<<<blocks, 128, 0, ctx->stream>>>((const uint32_t*)d_in, (const uint32_t*)d_shift, (uint32_t*)d_out, (uint32_t*)scratch, n);
-  LAUNCH_DONE(ctx, 1);
+  ctx->launches += 1;
+  GRAPE_CUDA_TRY(ctx, cudaGetLastError());
+  return GRAPE_OK;
+}
+}  // namespace grape
+extern "C" int grape_fr_inverse(grape_ctx* ctx, const void* d_in, const void* d_shift, void* d_out, uint64_t n) {
+  CHECK_CTX(ctx);
+  arena_reset(ctx);
+  return fr_inverse_async(ctx, d_in, d_shift, d_out, n);
 }
 extern "C" int grape_pad_i32(grape_ctx* ctx, const int32_t* d_in, int32_t* d_out, uint32_t n, uint32_t pad_n, uint64_t pad_size) {
   CHECK_CTX(ctx);

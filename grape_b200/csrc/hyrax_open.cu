@@ -1,0 +1,109 @@
+// Hyrax opening (the prover side of the evaluation proof).
+//
+// Replaces Hyrax::open (src/Hyrax.cu:237-305) and what it calls: single_commit (:176-185), the
+// row / layer / inner folds (FrTensor::partial_eval), z = c*x + d, and the host-side scalar
+// multiplication com_ad = <eq, d> * G (libff, :286-291), which here is one small kernel.
+// The input tensor is left intact (the reference folds it in place and destroys it).
+#include <vector>
+
+#include "ctx.cuh"
+#include "curve.cuh"
+#include "hostfr.hpp"
+
+namespace grape {
+
+template <bool FROM_I32>
+int fold_axis_async(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* d_x, uint32_t c,
+                    uint64_t gap, void* d_out);
+int commit_fr_async(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t size, uint32_t wd,
+                    void* d_out);
+
+// out = [s] * P for one Jacobian point and one Fr scalar (Montgomery form): double-and-add, one thread.
+__global__ void k_scalar_mul(const uint32_t* __restrict__ point_jac, const uint32_t* __restrict__ scalar,
+                             uint32_t* __restrict__ out_jac) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  Jacobian j;
+  j.x = Fp::load(point_jac);
+  j.y = Fp::load(point_jac + 8);
+  j.z = Fp::load(point_jac + 16);
+  Xyzz base = xyzz_from_jacobian(j);
+  Fr s = fe_from_mont(Fr::load(scalar));
+  Xyzz acc = Xyzz::inf();
+  for (int w = 7; w >= 0; w--) {
+    for (int b = 31; b >= 0; b--) {
+      acc = xyzz_dbl(acc);
+      if ((s.v[w] >> b) & 1u) xyzz_add(acc, base);
+    }
+  }
+  bool inf = acc.is_inf();
+  Affine a = xyzz_to_affine(acc);
+  store_jacobian_normalised(out_jac, a, inf);
+}
+
+}  // namespace grape
+
+using namespace grape;
+
+extern "C" int grape_hyrax_open(grape_ctx* ctx, const grape_table* table, const void* d_tensor, uint64_t size,
+                                uint32_t N, uint32_t layer_num, const void* h_eval_point, uint32_t n_e,
+                                const void* h_c, const void* h_G_jacobian, void* h_result, void* h_z,
+                                void* h_com_d, void* h_com_ad) {
+  if (!ctx || !table || !d_tensor || !h_eval_point || !h_c || !h_G_jacobian || !h_result || !h_z || !h_com_d || !h_com_ad)
+    return fail(ctx, GRAPE_ERR_INVALID, "null argument");
+  if (N == 0 || layer_num == 0) return fail(ctx, GRAPE_ERR_INVALID, "open: zero dimension");
+  if (size / N / GRAPE_COM_SCALE < layer_num)
+    return fail(ctx, GRAPE_ERR_INVALID, "Size too small: size < N * com_scale * layer_num");
+  const uint32_t pad_n = 1u << log2ceil(N);
+  const uint32_t new_n = pad_n * GRAPE_COM_SCALE;
+  const uint32_t wd = N * GRAPE_COM_SCALE;
+  if (n_e != log2ceil(size)) return fail(ctx, GRAPE_ERR_INVALID, "open: eval_point.size() != Log2(size)");
+  if (size % ((uint64_t)layer_num * wd) != 0) return fail(ctx, GRAPE_ERR_INVALID, "open: size is not layer_num * rows * N * 16");
+  if (new_n > table->n_gens) return fail(ctx, GRAPE_ERR_INVALID, "open: the table has fewer generators than the padded row length");
+  const uint32_t rows_per_layer = (uint32_t)(size / layer_num / wd);
+  const HostFr* e = reinterpret_cast<const HostFr*>(h_eval_point);
+  arena_reset(ctx);
+  int rc;
+  uint32_t *d_e, *d_cG, *d_d, *d_x1, *d_x, *d_xpad, *d_z, *d_small, *d_pts;
+  if ((rc = arena_alloc_t(ctx, (size_t)n_e * 8 + 8, &d_e))) return rc;
+  if ((rc = arena_alloc_t(ctx, 8 + 24 + 8, &d_cG))) return rc;       // c | G
+  if ((rc = arena_alloc_t(ctx, (size_t)new_n * 8, &d_d))) return rc;
+  if ((rc = arena_alloc_t(ctx, (size_t)layer_num * wd * 8, &d_x1))) return rc;
+  if ((rc = arena_alloc_t(ctx, (size_t)new_n * 8, &d_x))) return rc;
+  if ((rc = arena_alloc_t(ctx, (size_t)new_n * 8, &d_xpad))) return rc;
+  if ((rc = arena_alloc_t(ctx, (size_t)new_n * 8, &d_z))) return rc;
+  if ((rc = arena_alloc_t(ctx, 4 * 8, &d_small))) return rc;          // result | sum_ad | zero
+  if ((rc = arena_alloc_t(ctx, 2 * 24 + 8, &d_pts))) return rc;       // com_d | com_ad
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_e, e, (size_t)n_e * 32, cudaMemcpyHostToDevice, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_cG, h_c, 32, cudaMemcpyHostToDevice, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_cG + 8, h_G_jacobian, 96, cudaMemcpyHostToDevice, ctx->stream));
+  // blinding vector d from the context's random stream (reference: src/Hyrax.cu:253-256)
+  std::vector<HostFr> hd(new_n);
+  for (auto& x : hd) x = rng_next_fr(ctx->rng_state);
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_d, hd.data(), (size_t)new_n * 32, cudaMemcpyHostToDevice, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));  // hd goes out of scope only after the copy
+  // com_d = sum_i d_i G_i
+  if ((rc = commit_fr_async(ctx, table, d_d, new_n, new_n, d_pts))) return rc;
+  // x = tensor folded over the row variables, then over the layer variables
+  if ((rc = fold_axis_async<false>(ctx, d_tensor, size, d_e + (size_t)log2ceil(wd) * 8, rows_per_layer, wd, d_x1))) return rc;
+  if ((rc = fold_axis_async<false>(ctx, d_x1, (uint64_t)wd * layer_num, d_e + (size_t)log2ceil(size / layer_num) * 8,
+                                   layer_num, wd, d_x))) return rc;
+  const uint32_t* xp = d_x;
+  if (pad_n != N) {
+    GRAPE_CUDA_TRY(ctx, cudaMemsetAsync(d_small + 16, 0, 32, ctx->stream));
+    if ((rc = grape_fr_pad(ctx, d_x, d_xpad, N, pad_n, new_n, d_small + 16))) return rc;
+    xp = d_xpad;
+  }
+  // result = x~(e[0..log2 new_n)),  z = c*x + d,  sum_ad = d~(e[0..))
+  if ((rc = fold_axis_async<false>(ctx, xp, new_n, d_e, new_n, 1, d_small))) return rc;
+  if ((rc = grape_fr_axpy(ctx, xp, d_cG, d_d, d_z, new_n))) return rc;
+  if ((rc = fold_axis_async<false>(ctx, d_d, new_n, d_e, new_n, 1, d_small + 8))) return rc;
+  k_scalar_mul<<<1, 32, 0, ctx->stream>>>(d_cG + 8, d_small + 8, d_pts + 24);
+  ctx->launches += 1;
+  GRAPE_CUDA_TRY(ctx, cudaGetLastError());
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(h_result, d_small, 32, cudaMemcpyDeviceToHost, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(h_z, d_z, (size_t)new_n * 32, cudaMemcpyDeviceToHost, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(h_com_d, d_pts, 96, cudaMemcpyDeviceToHost, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(h_com_ad, d_pts + 24, 96, cudaMemcpyDeviceToHost, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  return GRAPE_OK;
+}

@@ -388,8 +388,11 @@ extern "C" int grape_commit_i32(grape_ctx* ctx, const grape_table* t, const int3
   return launch_commit<false>(ctx, t, d_scalars, rows, wd, total_windows, partials, n_chunks, d_out);
 }
 
-extern "C" int grape_commit_fr(grape_ctx* ctx, const grape_table* t, const void* d_scalars,
-                               uint64_t size, uint32_t wd, void* d_out) {
+namespace grape {
+// Fr-scalar commitment that takes its scratch from the arena without resetting it (used inside the
+// lookup prover, which holds other arena regions at that point).
+int commit_fr_async(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t size, uint32_t wd,
+                    void* d_out) {
   int rc = check_table(ctx, t, wd);
   if (rc) return rc;
   if (size % wd != 0) return fail(ctx, GRAPE_ERR_INVALID, "size is not a multiple of the row length");
@@ -398,7 +401,6 @@ extern "C" int grape_commit_fr(grape_ctx* ctx, const grape_table* t, const void*
   uint64_t rows = size / wd;
   uint32_t total_windows = (254 + t->window_bits - 1) / t->window_bits;
   uint32_t n_chunks = pick_chunks(ctx, rows, wd);
-  arena_reset(ctx);
   Xyzz* partials = nullptr;
   uint32_t* biased = nullptr;
   rc = arena_alloc_t(ctx, rows * n_chunks, &partials);
@@ -409,6 +411,14 @@ extern "C" int grape_commit_fr(grape_ctx* ctx, const grape_table* t, const void*
       reinterpret_cast<const uint32_t*>(d_scalars), biased, size, t->window_bits, total_windows);
   ctx->launches += 1;
   return launch_commit<true>(ctx, t, biased, rows, wd, total_windows, partials, n_chunks, d_out);
+}
+}  // namespace grape
+
+extern "C" int grape_commit_fr(grape_ctx* ctx, const grape_table* t, const void* d_scalars,
+                               uint64_t size, uint32_t wd, void* d_out) {
+  if (!ctx) return GRAPE_ERR_INVALID;
+  arena_reset(ctx);
+  return commit_fr_async(ctx, t, d_scalars, size, wd, d_out);
 }
 
 extern "C" int grape_commit_i32_host(grape_ctx* ctx, const grape_table* t, const int32_t* h_scalars,

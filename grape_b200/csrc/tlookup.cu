@@ -37,6 +37,9 @@ namespace grape {
 
 void eq_weights_async(grape_ctx* ctx, const void* d_x, uint32_t nv, uint32_t c, void* d_w);
 int fr_sum_async(grape_ctx* ctx, const void* d_in, uint64_t n, void* d_out);
+int fr_inverse_async(grape_ctx* ctx, const void* d_in, const void* d_shift, void* d_out, uint64_t n);
+int commit_fr_async(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t size, uint32_t wd,
+                    void* d_out);
 
 constexpr int LT = 128;
 
@@ -238,7 +241,6 @@ static P4 mul_eq(const HostFr q[3], const HostFr& u) {
 
 using namespace grape;
 
-int grape_fr_inverse(grape_ctx* ctx, const void* d_in, const void* d_shift, void* d_out, uint64_t n);
 
 static int lookup_create(grape_ctx* ctx, int32_t low, uint32_t len, const int32_t* d_map, grape_lookup** out) {
   if (!ctx || !out) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
@@ -273,13 +275,8 @@ static int lookup_create(grape_ctx* ctx, int32_t low, uint32_t len, const int32_
   cudaMemsetAsync(lk->m, 0, bytes, ctx->stream);
   k_table_init<<<lk_blocks(ctx, n), LT, 0, ctx->stream>>>(lk->T, d_c, lk->mapped, d_c + 16, n);
   ctx->launches += 1;
-  // B = 1 / (T + beta), batched (uses its own arena allocation; d_c stays valid: no reset in between)
-  {
-    void* scratch;
-    rc = arena_alloc(ctx, bytes, &scratch);
-    if (rc) return rc;
-  }
-  rc = grape_lookup_fill_inverse(ctx, lk->T, d_c + 8, lk->B, n);
+  // B = 1 / (T + beta), batched
+  rc = fr_inverse_async(ctx, lk->T, d_c + 8, lk->B, n);
   if (rc) return rc;
   GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
   *out = lk;
@@ -367,7 +364,7 @@ static int lookup_prove(grape_ctx* ctx, grape_lookup* lk, uint32_t* d_S, uint64_
     GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_S, d_A, Dp * 32, cudaMemcpyDeviceToDevice, ctx->stream));
   }
   // A = 1 / (S + beta)
-  if ((rc = grape_lookup_fill_inverse(ctx, d_S, d_c + 8, d_A, Dp))) return rc;
+  if ((rc = fr_inverse_async(ctx, d_S, d_c + 8, d_A, Dp))) return rc;
   // commitments to A and m (reference: src/tlookup.cu:319-323); optional here
   if (table) {
     if (msm_size == 0 || Dp % ((uint64_t)msm_size * GRAPE_COM_SCALE) != 0)
@@ -383,8 +380,8 @@ static int lookup_prove(grape_ctx* ctx, grape_lookup* lk, uint32_t* d_S, uint64_
       if ((rc = arena_alloc(ctx, (size_t)(N / m_wd) * 96, &tmp))) return rc;
       d_com_m = tmp;
     }
-    if ((rc = grape_commit_fr_noreset(ctx, table, d_A, Dp, msm_size * GRAPE_COM_SCALE, d_com_A))) return rc;
-    if ((rc = grape_commit_fr_noreset(ctx, table, lk->m, N, m_wd, d_com_m))) return rc;
+    if ((rc = commit_fr_async(ctx, table, d_A, Dp, msm_size * GRAPE_COM_SCALE, d_com_A))) return rc;
+    if ((rc = commit_fr_async(ctx, table, lk->m, N, m_wd, d_com_m))) return rc;
   }
   // working copies of B, T, m (the rounds fold in place), sum_j B_j m_j
   uint32_t *Bw, *Tw, *Mw, *partial, *sums, *whi, *wlo, *d_bm;

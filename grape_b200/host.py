@@ -350,3 +350,88 @@ def combine_claims(ctx: Context, d_X, size: int, claims, us, v):
                                             hv.ctypes.data, nv, out.ctypes.data, tr.ctypes.data, nv + 1,
                                             C.byref(nr)))
     return decode_field(out)[0], [decode_field(tr[i]) for i in range(nr.value)]
+
+
+# ----------------------------------------------------------------------------- lookup argument
+class Lookup:
+    """``tLookupRange`` (``mapped=None``) or ``tLookupRangeMapping`` (``mapped`` = int32 table)."""
+
+    def __init__(self, ctx: Context, low: int, length: int, mapped: np.ndarray | None = None):
+        self.ctx = ctx
+        h = C.c_void_p()
+        if mapped is None:
+            ctx._check(ctx.lib.grape_lookup_range_create(ctx.handle, low, length, C.byref(h)))
+        else:
+            self._map_dev = ctx.upload(np.ascontiguousarray(mapped, dtype=np.int32))
+            ctx._check(ctx.lib.grape_lookup_mapping_create(ctx.handle, low, length, self._map_dev.ptr, C.byref(h)))
+        self.handle = h.value
+        a, b, r = (np.zeros((1, 8), dtype=np.uint32) for _ in range(3))
+        n = C.c_uint32()
+        ctx.lib.grape_lookup_params(self.handle, a.ctypes.data, b.ctypes.data, r.ctypes.data, C.byref(n))
+        self.alpha, self.beta, self.r = decode_field(a)[0], decode_field(b)[0], decode_field(r)[0]
+        self.n = n.value
+        self.low = low
+
+    def table(self, which: str) -> list[int]:
+        idx = {"T": 0, "B": 1, "m": 2, "mapped": 3}[which]
+        ptr = self.ctx.lib.grape_lookup_table(self.handle, idx)
+        return self.ctx.fr_download(ptr, self.n)
+
+    def prove(self, d_S, D: int, d_A, v, inner: int = 11008, inner_pad: int = 16384, table: "GeneratorTable | None" = None,
+              msm_size: int = 0, d_com_A=None, d_com_m=None):
+        """``tLookupRange::prove``: returns (S_claim, transcript)."""
+        hv = _fr_host(v)
+        out = np.zeros((1, 8), dtype=np.uint32)
+        cap = len(v) + 2
+        tr = np.zeros((cap, 4, 8), dtype=np.uint32)
+        nr = C.c_uint32()
+        ctx = self.ctx
+        ctx._check(ctx.lib.grape_lookup_prove_range(ctx.handle, self.handle, _p(d_S), D, _p(d_A), hv.ctypes.data, len(v),
+                                                    inner, inner_pad, table.handle if table else None, msm_size,
+                                                    _p(d_com_A), _p(d_com_m), out.ctypes.data, tr.ctypes.data, cap,
+                                                    C.byref(nr)))
+        return decode_field(out)[0], [decode_field(tr[i]) for i in range(nr.value)]
+
+    def prove_pairs(self, d_S_in, d_S_out, D: int, d_S_work, d_A, v, inner: int = 11008, inner_pad: int = 16384,
+                    table: "GeneratorTable | None" = None, msm_size: int = 0, d_com_A=None, d_com_m=None):
+        """``tLookupRangeMapping::prove``: returns (S_claim, transcript)."""
+        hv = _fr_host(v)
+        out = np.zeros((1, 8), dtype=np.uint32)
+        cap = len(v) + 2
+        tr = np.zeros((cap, 4, 8), dtype=np.uint32)
+        nr = C.c_uint32()
+        ctx = self.ctx
+        ctx._check(ctx.lib.grape_lookup_prove_mapping(ctx.handle, self.handle, _p(d_S_in), _p(d_S_out), D, _p(d_S_work),
+                                                      _p(d_A), hv.ctypes.data, len(v), inner, inner_pad,
+                                                      table.handle if table else None, msm_size, _p(d_com_A),
+                                                      _p(d_com_m), out.ctypes.data, tr.ctypes.data, cap, C.byref(nr)))
+        return decode_field(out)[0], [decode_field(tr[i]) for i in range(nr.value)]
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.ctx.lib.grape_lookup_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+# ----------------------------------------------------------------------------- Hyrax opening
+def hyrax_open(ctx: Context, table: GeneratorTable, d_tensor, size: int, N: int, layer_num: int, eval_point, c: int,
+               G_jacobian: np.ndarray):
+    """``Hyrax::open``: returns dict(result, z, com_d, com_ad) with points as affine tuples / None."""
+    he, hc = _fr_host(eval_point), _fr_host([c])
+    G = np.ascontiguousarray(G_jacobian, dtype=np.uint32).reshape(24)
+    new_n = (1 << max(N - 1, 0).bit_length()) * COM_SCALE
+    res = np.zeros((1, 8), dtype=np.uint32)
+    z = np.zeros((new_n, 8), dtype=np.uint32)
+    com = np.zeros((2, 24), dtype=np.uint32)
+    ctx._check(ctx.lib.grape_hyrax_open(ctx.handle, table.handle, _p(d_tensor), size, N, layer_num, he.ctypes.data,
+                                        len(eval_point), hc.ctypes.data, G.ctypes.data, res.ctypes.data, z.ctypes.data,
+                                        com[0].ctypes.data, com[1].ctypes.data))
+    pts = decode_jacobian(com)
+    return {"result": decode_field(res)[0], "z": decode_field(z), "com_d": pts[0], "com_ad": pts[1],
+            "com_bytes": com.tobytes()}

@@ -38,6 +38,7 @@ extern "C" {
 
 typedef struct grape_ctx grape_ctx;
 typedef struct grape_table grape_table;
+typedef struct grape_lookup grape_lookup;
 
 /* ---- context ------------------------------------------------------------------------------ */
 /* One context = one GPU + one stream + a grow-only scratch arena + a seedable RNG.  The
@@ -135,6 +136,75 @@ int grape_fr_fold(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* d_
  * materialises first, src/fr-tensor.cu:376-381). */
 int grape_fold_i32(grape_ctx* ctx, const int32_t* d_t, uint64_t ntot, const void* d_x, uint32_t c,
                    uint64_t gap, void* d_out);
+
+/* ---- sumcheck provers ----------------------------------------------------------------------- */
+/* Challenge vectors and claims are host arrays of 32-byte Fr elements (the reference's
+ * std::vector<Fr> / Fr).  h_claim is read (claimed value) and overwritten with the final running
+ * claim; a failed round check p(0)+p(1)==claim returns GRAPE_ERR_CHECK where the reference throws.
+ * h_transcript (may be NULL) receives up to transcript_capacity round polynomials of four
+ * coefficients each, lowest degree first (degree-2 rounds end with a zero); *n_rounds the count.
+ * Tensor arguments are consumed (left folded), as in the reference. */
+
+/* prove_matmul (src/prove.cu:175-210; phases :49-117).  d_A = [L][N][K], d_B = [L][M][K];
+ * u = u_M | u_N | u_L, v = v_K | v_L.  h_out_claims[0..1] = A~(v_K,u_N,v_L), B~(v_K,u_M,v_L). */
+int grape_prove_matmul(grape_ctx* ctx, void* d_A, void* d_B, uint32_t L, uint32_t N, uint32_t M, uint32_t K,
+                       const void* h_u, uint32_t n_u, const void* h_v, uint32_t n_v, void* h_claim,
+                       void* h_out_claims, void* h_transcript, uint32_t transcript_capacity,
+                       uint32_t* n_rounds);
+/* prove_eleMul (src/prove.cu:212-241; eleMul_sumcheck :119-172).  d_A, d_B = [L*M][N]. */
+int grape_prove_elemul(grape_ctx* ctx, void* d_A, void* d_B, uint32_t L, uint32_t M, uint32_t N,
+                       const void* h_u, uint32_t n_u, const void* h_v, uint32_t n_v, void* h_claim,
+                       void* h_out_claims, void* h_transcript, uint32_t transcript_capacity,
+                       uint32_t* n_rounds);
+/* combine_claims (src/prove.cu:243-301): k <= 4 claims X~(u_j) = c_j -> h_result = X~(v).
+ * h_us: the k challenge vectors back to back (k * n_vars elements); size = 2^n_vars. */
+int grape_combine_claims(grape_ctx* ctx, void* d_X, uint64_t size, const void* h_claims, uint32_t k,
+                         const void* h_us, const void* h_v, uint32_t n_vars, void* h_result,
+                         void* h_transcript, uint32_t transcript_capacity, uint32_t* n_rounds);
+
+/* ---- lookup argument ------------------------------------------------------------------------ */
+/* tLookupRange(low, len) (src/tlookup.cu:251-263): table low .. low+2^ceil(log2 len)-1, beta = table
+ * size, alpha drawn from the context's random stream. */
+int grape_lookup_range_create(grape_ctx* ctx, int32_t low, uint32_t len, grape_lookup** out);
+/* tLookupRangeMapping(low, len, file) (src/tlookup.cu:350-371) with the int32 table f already in
+ * device memory (len a power of two); draws alpha then r. */
+int grape_lookup_mapping_create(grape_ctx* ctx, int32_t low, uint32_t len, const int32_t* d_map,
+                                grape_lookup** out);
+int grape_lookup_destroy(grape_lookup* lk);
+/* alpha, beta, r (32 bytes each, any may be NULL) and the table size. */
+int grape_lookup_params(const grape_lookup* lk, void* h_alpha, void* h_beta, void* h_r, uint32_t* n);
+/* Device tensors of the object: 0 = T, 1 = B = 1/(T+beta), 2 = m (multiplicities of the last
+ * prove), 3 = mapped values. */
+const void* grape_lookup_table(const grape_lookup* lk, int which);
+/* tLookupRange::prove (src/tlookup.cu:288-343).  d_S: D queries; when D is not a power of two the
+ * rows of length `inner` are padded to `inner_pad` (the reference hard-codes 11008 -> 16384) and
+ * d_S, d_A must hold 2^ceil(log2 D) elements.  d_A receives 1/(S+beta); both are consumed.
+ * table / msm_size: commit A (rows of msm_size*16) and the multiplicities as the reference does
+ * (pass table = NULL to skip); d_com_A / d_com_m (may be NULL) receive those commitments.
+ * h_claim = S~(v).  Draws ceil(log2 D) elements from the random stream (the reference's u). */
+int grape_lookup_prove_range(grape_ctx* ctx, grape_lookup* lk, void* d_S, uint64_t D, void* d_A,
+                             const void* h_v, uint32_t n_v, uint32_t inner, uint32_t inner_pad,
+                             const grape_table* table, uint32_t msm_size, void* d_com_A, void* d_com_m,
+                             void* h_claim, void* h_transcript, uint32_t transcript_capacity,
+                             uint32_t* n_rounds);
+/* tLookupRangeMapping::prove (src/tlookup.cu:398-456): pairs (S_in, S_out = f(S_in)); d_S_work
+ * (2^ceil(log2 D) elements) receives S_in + r*S_out. */
+int grape_lookup_prove_mapping(grape_ctx* ctx, grape_lookup* lk, const void* d_S_in, const void* d_S_out,
+                               uint64_t D, void* d_S_work, void* d_A, const void* h_v, uint32_t n_v,
+                               uint32_t inner, uint32_t inner_pad, const grape_table* table,
+                               uint32_t msm_size, void* d_com_A, void* d_com_m, void* h_claim,
+                               void* h_transcript, uint32_t transcript_capacity, uint32_t* n_rounds);
+
+/* ---- Hyrax opening -------------------------------------------------------------------------- */
+/* Hyrax::open (src/Hyrax.cu:237-305).  d_tensor = [layer_num][rows][N*16] Fr (left intact here; the
+ * reference destroys it), size its element count, h_eval_point = ceil(log2 size) challenges, h_c the
+ * verifier's scalar, h_G_jacobian the base point (the reference passes cpu_points[0]).  The blinding
+ * vector d (16 * 2^ceil(log2 N) elements) is drawn from the context's random stream.  Outputs (host):
+ * h_result = tensor~(eval_point), h_z = c*x + d (16 * 2^ceil(log2 N) elements), h_com_d = sum d_i G_i,
+ * h_com_ad = <eq(eval_point), d> * G, both as normalised Jacobian records (Hyrax_proof, include/Hyrax.cuh:57-69). */
+int grape_hyrax_open(grape_ctx* ctx, const grape_table* table, const void* d_tensor, uint64_t size, uint32_t N,
+                     uint32_t layer_num, const void* h_eval_point, uint32_t n_e, const void* h_c,
+                     const void* h_G_jacobian, void* h_result, void* h_z, void* h_com_d, void* h_com_ad);
 
 /* ---- allocation-free commitment ------------------------------------------------------------ */
 /* No counterpart in the reference (its commit allocates and frees scratch on every call,

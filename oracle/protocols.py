@@ -427,12 +427,12 @@ class LookupRange:
             out.append(S[(g // inner_pad) * inner + g % inner_pad] if g % inner_pad < inner else pad_value)
         return out
 
-    def prove(self, S, v, u, pad_value=0):
+    def prove(self, S, v, u, pad_value=0, inner=11008, inner_pad=16384):
         """Returns a dict with the multiplicities, A, the round transcript and the final claims.
         ``u`` holds the ceil(log2 D) field elements the reference draws inside ``prove``
         (src/tlookup.cu:293)."""
         self.prep(S)
-        S = self.padded(S, pad_value=pad_value)
+        S = self.padded(S, inner, inner_pad, pad_value)
         D = len(S)
         if len(v) != log2ceil(D):
             raise RuntimeError("u.size() != ceilLog2(D)")
@@ -464,11 +464,11 @@ class LookupRangeMapping(LookupRange):
         self.B = [inv((t + self.beta) % R) for t in self.T]
         self.m = [0] * self.N
 
-    def prove_pairs(self, S_in, S_out, v, u):
+    def prove_pairs(self, S_in, S_out, v, u, inner=11008, inner_pad=16384):
         self.prep(S_in)
         S = [(a + self.r * b) % R for a, b in zip(S_in, S_out)]
         pad_value = self.mapped[-self.low] * self.r % R
-        S = self.padded(S, pad_value=pad_value)
+        S = self.padded(S, inner, inner_pad, pad_value)
         D = len(S)
         if len(v) != log2ceil(D):
             raise RuntimeError("v.size() != ceilLog2(D)")

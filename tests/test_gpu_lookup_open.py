@@ -1,0 +1,167 @@
+"""Parity of the lookup argument and of the Hyrax opening with the oracle (claims, round
+polynomials, multiplicities, tables, proof elements), with the prover randomness seeded identically."""
+import random
+
+import numpy as np
+import pytest
+
+from oracle import bn254, cport
+from oracle import protocols as pr
+
+pytestmark = pytest.mark.gpu
+R = bn254.R
+
+
+def _mle(t, u):
+    n = 1 << len(u)
+    return pr.partial_eval(list(t) + [0] * (n - len(t)), n, u, n, 0, 1)[0]
+
+
+def test_lookup_range_power_of_two(gctx):
+    from grape_b200 import host
+    rng = random.Random(1)
+    gctx.seed(77)
+    draw = bn254.SplitMix64(77)
+    lk = host.Lookup(gctx, -8, 16)
+    ref = pr.LookupRange(-8, 16, draw.next_fr())
+    assert lk.alpha == ref.alpha and lk.beta == ref.beta and lk.n == 16
+    assert lk.table("T") == ref.T and lk.table("B") == ref.B
+    D = 256
+    S = [rng.randrange(-8, 8) % R for _ in range(D)]
+    v = [rng.randrange(R) for _ in range(8)]
+    u = draw.fr_vec(8)
+    want = ref.prove(S, v, u)
+    dS, dA = gctx.fr_upload(S), gctx.alloc(D * 32)
+    claim, tr = lk.prove(dS, D, dA, v)
+    assert claim == want["claim"] == _mle(S, v)
+    assert tr == want["transcript"]
+    assert lk.table("m") == want["m"]
+    lk.close()
+
+
+def test_lookup_range_padded_rows(gctx):
+    """D is not a power of two: rows of 6 padded to 8, pad count lands in the bin of value zero."""
+    from grape_b200 import host
+    rng = random.Random(2)
+    gctx.seed(5)
+    draw = bn254.SplitMix64(5)
+    lk = host.Lookup(gctx, -4, 8)
+    ref = pr.LookupRange(-4, 8, draw.next_fr())
+    rows, inner, inner_pad = 4, 6, 8
+    D = rows * inner
+    S = [rng.randrange(-4, 4) % R for _ in range(D)]
+    v = [rng.randrange(R) for _ in range(5)]
+    u = draw.fr_vec(5)
+    want = ref.prove(S, v, u, inner=inner, inner_pad=inner_pad)
+    dS = gctx.alloc(32 * 32)
+    gctx._check(gctx.lib.grape_h2d(gctx.handle, dS.ptr, host.encode_field(S).ctypes.data, D * 32))
+    gctx.sync()
+    dA = gctx.alloc(32 * 32)
+    claim, tr = lk.prove(dS, D, dA, v, inner=inner, inner_pad=inner_pad)
+    assert claim == want["claim"] and tr == want["transcript"]
+    assert lk.table("m") == want["m"] and sum(want["m"]) == 32
+    lk.close()
+
+
+def test_lookup_with_commitments(gctx):
+    """The commitments to A = 1/(S+beta) and to the multiplicities, as the reference forms them."""
+    import grape_b200 as g
+    from grape_b200 import host, workloads as wl
+    rng = random.Random(3)
+    gens = wl.make_generators(gctx, 512, seed=31)
+    table = g.GeneratorTable(gctx, gens, 8, 1)
+    ctable = cport.table_build(gens)
+    gctx.seed(9)
+    draw = bn254.SplitMix64(9)
+    lk = host.Lookup(gctx, -512, 1024)
+    ref = pr.LookupRange(-512, 1024, draw.next_fr())
+    D, msm = 4096, 16
+    S = [rng.randrange(-512, 512) % R for _ in range(D)]
+    v = [rng.randrange(R) for _ in range(12)]
+    u = draw.fr_vec(12)
+    want = ref.prove(S, v, u)
+    dS, dA = gctx.fr_upload(S), gctx.alloc(D * 32)
+    comA, comm = gctx.alloc(D // (msm * 16) * 96), gctx.alloc(1024 // 512 * 96)
+    claim, tr = lk.prove(dS, D, dA, v, table=table, msm_size=msm, d_com_A=comA, d_com_m=comm)
+    assert claim == want["claim"] and tr == want["transcript"]
+    wantA = cport.commit_fr(host.encode_field(want["A"]), msm * 16, ctable)
+    wantm = cport.commit_fr(host.encode_field(want["m"]), 512, ctable)
+    assert gctx.download(comA, wantA.nbytes).tobytes() == wantA.tobytes()
+    assert gctx.download(comm, wantm.nbytes).tobytes() == wantm.tobytes()
+    lk.close()
+    table.close()
+
+
+def test_lookup_mapping(gctx):
+    from grape_b200 import host
+    rng = random.Random(4)
+    gctx.seed(13)
+    draw = bn254.SplitMix64(13)
+    mp = [rng.randrange(-1000, 1000) for _ in range(32)]
+    lk = host.Lookup(gctx, -16, 32, np.array(mp, dtype=np.int32))
+    ref = pr.LookupRangeMapping(-16, 32, mp, draw.next_fr(), draw.next_fr())
+    assert lk.r == ref.r and lk.table("T") == ref.T and lk.table("B") == ref.B
+    D = 128
+    s_in = [rng.randrange(-16, 16) for _ in range(D)]
+    s_out = [mp[s + 16] for s in s_in]
+    v = [rng.randrange(R) for _ in range(7)]
+    u = draw.fr_vec(7)
+    want = ref.prove_pairs([s % R for s in s_in], [s % R for s in s_out], v, u)
+    d_in, d_out = gctx.fr_upload(s_in), gctx.fr_upload(s_out)
+    work, dA = gctx.alloc(D * 32), gctx.alloc(D * 32)
+    claim, tr = lk.prove_pairs(d_in, d_out, D, work, dA, v)
+    assert claim == want["claim"] and tr == want["transcript"] and lk.table("m") == want["m"]
+    lk.close()
+
+
+def test_lookup_rejects_query_outside_table(gctx):
+    import grape_b200 as g
+    from grape_b200 import host
+    lk = host.Lookup(gctx, -8, 16)
+    S = [3 % R] * 63 + [100]
+    with pytest.raises(g.GrapeError) as e:
+        lk.prove(gctx.fr_upload(S), 64, gctx.alloc(64 * 32), [5, 6, 7, 8, 9, 10])
+    assert e.value.code == 3
+    lk.close()
+
+
+@pytest.mark.parametrize("layer_num,N,rows", [(2, 2, 2), (1, 3, 4), (4, 1, 1)])
+def test_hyrax_open_and_verify(gctx, layer_num, N, rows):
+    import grape_b200 as g
+    from grape_b200 import host
+    rng = random.Random(layer_num * 10 + N)
+    wd = N * 16
+    new_n = (1 << pr.log2ceil(N)) * 16
+    gens = bn254.make_generators(new_n, seed=41)
+    gj = g.encode_jacobian(gens)
+    table = g.GeneratorTable(gctx, gj, 8, 1)
+    size = layer_num * rows * wd
+    t = [rng.randrange(-2**15, 2**15) for _ in range(size)]
+    # the tensor is committed in its padded layout (every N-chunk padded to a power of two), which is
+    # what the reference does before commit (pad_int, test/commit.cu:63-64)
+    pad_n = new_n // 16
+    d_int = gctx.upload(np.array(t, dtype=np.int32))
+    n_pad = (size // N) * pad_n
+    d_pad = gctx.alloc(n_pad * 4)
+    gctx.pad_i32(d_int, d_pad, N, pad_n, n_pad)
+    t_pad = [int(x) for x in gctx.download(d_pad, n_pad * 4, dtype=np.int32)]
+    assert t_pad == [t[(i // pad_n) * N + i % pad_n] if i % pad_n < N else 0 for i in range(n_pad)]
+    com = gctx.alloc((n_pad // new_n) * 96)
+    g.commit_i32(gctx, table, d_pad, n_pad, new_n, com)
+    commitments = g.decode_jacobian(gctx.download(com, (n_pad // new_n) * 96).reshape(-1, 24))
+    assert commitments == pr.commit_rows(t_pad, new_n, gens)
+    e = [rng.randrange(R) for _ in range(pr.log2ceil(size))]
+    c = rng.randrange(R)
+    gctx.seed(1234)
+    d = bn254.SplitMix64(1234).fr_vec(new_n)
+    tf = [x % R for x in t]
+    want = pr.hyrax_open(tf, e, c, size, N, layer_num, gens, gens[0], d)
+    d_t = gctx.fr_upload(tf)
+    got = host.hyrax_open(gctx, table, d_t, size, N, layer_num, e, c, gj[0])
+    assert got["result"] == want["result"]
+    assert got["z"] == want["z"]
+    assert got["com_d"] == want["com_d"] and got["com_ad"] == want["com_ad"]
+    assert gctx.fr_download(d_t, size) == tf  # the tensor is left intact
+    proof = {"result": got["result"], "z": got["z"], "com_d": got["com_d"], "com_ad": got["com_ad"]}
+    assert pr.hyrax_verify(commitments, proof, e, c, size, N, layer_num, gens, gens[0])
+    table.close()
