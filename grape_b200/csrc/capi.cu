@@ -43,6 +43,8 @@ extern "C" int grape_ctx_destroy(grape_ctx* ctx) {
   if (ctx->dstage) cudaFree(ctx->dstage);
   if (ctx->pinned) cudaFreeHost(ctx->pinned);
   if (ctx->d_status) cudaFree(ctx->d_status);
+  if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
+  for (auto e : ctx->copy_events) cudaEventDestroy(e);
   if (ctx->t0) { cudaEventDestroy(ctx->t0); cudaEventDestroy(ctx->t1); }
   for (auto& pr : ctx->prof_events) { cudaEventDestroy(pr.first); cudaEventDestroy(pr.second); }
   cudaStreamDestroy(ctx->stream);

@@ -11,6 +11,9 @@
 struct grape_ctx {
   int device = 0;
   cudaStream_t stream = nullptr;
+  // second stream + events: host-to-device copies of the host-buffer entry points overlap compute
+  cudaStream_t copy_stream = nullptr;
+  std::vector<cudaEvent_t> copy_events;
   // scratch arena: a bump allocator over a few device blocks.  A top-level call resets it,
   // carves what its kernels need, and the next call on the stream reuses the same memory.
   struct ArenaBlock { void* ptr; size_t size; size_t off; };

@@ -55,6 +55,25 @@ __global__ void __launch_bounds__(256) k_int_peak(uint32_t* sink, uint32_t seed)
 #pragma unroll
     for (int k = 0; k < PEAK_CHAINS; k++) s ^= lo[k] ^ hi[k];
     if (s == 0x12345) sink[0] = s;
+  } else if (KIND == 4) {
+    // the same multiplications with a loop body of 16 inlined products (about 3 000 instructions),
+    // the footprint of one mixed point addition: exposes instruction-fetch limits
+    Fp x[4], y;
+#pragma unroll
+    for (int i = 0; i < 8; i++) { x[0].v[i] = a + i; x[1].v[i] = b + i; x[2].v[i] = a * 3 + i; x[3].v[i] = b * 5 + i; y.v[i] = (a ^ b) + i; }
+#pragma unroll
+    for (int k = 0; k < 4; k++) x[k].v[7] &= 0x0fffffffu;
+    y.v[7] &= 0x0fffffffu;
+    for (int it = 0; it < PEAK_ITERS / 64; it++) {
+#pragma unroll
+      for (int r = 0; r < 4; r++) {
+        x[0] = fe_mul(x[0], y);
+        x[1] = fe_mul(x[1], x[0]);
+        x[2] = fe_mul(x[2], y);
+        x[3] = fe_mul(x[3], x[2]);
+      }
+    }
+    if (x[0].v[0] == 0x12345 && x[1].v[3] == 7 && x[3].v[2] == 9) sink[0] = x[0].v[1];
   } else {
     Fp x[2], y;
 #pragma unroll
@@ -75,7 +94,7 @@ using namespace grape;
 // Writes operations per second: kinds 0-2 count multiply-add instructions (a lo/hi pair counts 2),
 // kind 3 counts field multiplications.
 extern "C" int grape_measure_int_peak(grape_ctx* ctx, int kind, double* ops_per_second) {
-  if (!ctx || !ops_per_second || kind < 0 || kind > 3) return GRAPE_ERR_INVALID;
+  if (!ctx || !ops_per_second || kind < 0 || kind > 4) return GRAPE_ERR_INVALID;
   arena_reset(ctx);
   uint32_t* sink = nullptr;
   int rc = arena_alloc_t(ctx, 64, &sink);
@@ -90,7 +109,8 @@ extern "C" int grape_measure_int_peak(grape_ctx* ctx, int kind, double* ops_per_
     if (kind == 0) k_int_peak<0><<<blocks, threads, 0, ctx->stream>>>(sink, rep + 1);
     else if (kind == 1) k_int_peak<1><<<blocks, threads, 0, ctx->stream>>>(sink, rep + 1);
     else if (kind == 2) k_int_peak<2><<<blocks, threads, 0, ctx->stream>>>(sink, rep + 1);
-    else k_int_peak<3><<<blocks, threads, 0, ctx->stream>>>(sink, rep + 1);
+    else if (kind == 3) k_int_peak<3><<<blocks, threads, 0, ctx->stream>>>(sink, rep + 1);
+    else k_int_peak<4><<<blocks, threads, 0, ctx->stream>>>(sink, rep + 1);
     cudaEventRecord(e1, ctx->stream);
     ctx->launches += 1;
     GRAPE_CUDA_TRY(ctx, cudaEventSynchronize(e1));
@@ -104,7 +124,8 @@ extern "C" int grape_measure_int_peak(grape_ctx* ctx, int kind, double* ops_per_
   double per_thread;
   if (kind == 0 || kind == 1) per_thread = (double)PEAK_ITERS * PEAK_CHAINS;
   else if (kind == 2) per_thread = 2.0 * PEAK_ITERS * PEAK_CHAINS;
-  else per_thread = 2.0 * (PEAK_ITERS / 8);
+  else if (kind == 3) per_thread = 2.0 * (PEAK_ITERS / 8);
+  else per_thread = 16.0 * (PEAK_ITERS / 64);
   *ops_per_second = per_thread * blocks * threads / (best * 1e-3);
   return GRAPE_OK;
 }

@@ -13,6 +13,10 @@
 #include <cstdint>
 #include <cuda_runtime.h>
 
+#ifndef GRAPE_MUL_ATTR
+#define GRAPE_MUL_ATTR __forceinline__
+#endif
+
 namespace grape {
 
 // ---------------------------------------------------------------------------------------------
@@ -319,7 +323,7 @@ __device__ __forceinline__ Fe<P> mont_finish(const uint32_t (&E)[8], const uint3
 
 // r = a * b / 2^256 mod m
 template <class P>
-__device__ __forceinline__ Fe<P> fe_mul(const Fe<P>& a, const Fe<P>& b) {
+__device__ GRAPE_MUL_ATTR Fe<P> fe_mul(const Fe<P>& a, const Fe<P>& b) {
   uint32_t E[8], O[8];
   mul4(E, a.v[0], a.v[2], a.v[4], a.v[6], b.v[0]);
   mul4(O, a.v[1], a.v[3], a.v[5], a.v[7], b.v[0]);

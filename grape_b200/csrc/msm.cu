@@ -442,9 +442,34 @@ extern "C" int grape_commit_i32_host(grape_ctx* ctx, const grape_table* t, const
   }
   int32_t* d_in = reinterpret_cast<int32_t*>(ctx->dstage);
   char* d_out = reinterpret_cast<char*>(ctx->dstage) + ((in_bytes + 255) & ~size_t(255));
-  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_in, h_scalars, in_bytes, cudaMemcpyHostToDevice, ctx->stream));
-  rc = grape_commit_i32(ctx, t, d_in, size, wd, max_bits, d_out);
-  if (rc) return rc;
+  // Row slices: slice i+1 is copied in on the copy stream while slice i is being committed.
+  const uint32_t n_slices = rows >= 4096 ? 8 : 1;
+  if (!ctx->copy_stream) GRAPE_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+  while (ctx->copy_events.size() < n_slices + 1) {
+    cudaEvent_t e;
+    GRAPE_CUDA_TRY(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    ctx->copy_events.push_back(e);
+  }
+  // the copy stream must not overwrite the staging buffer while earlier work still reads it
+  GRAPE_CUDA_TRY(ctx, cudaEventRecord(ctx->copy_events[n_slices], ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->copy_events[n_slices], 0));
+  const uint64_t rows_per_slice = (rows + n_slices - 1) / n_slices;
+  for (uint32_t sidx = 0; sidx < n_slices; sidx++) {
+    const uint64_t r0 = (uint64_t)sidx * rows_per_slice;
+    if (r0 >= rows) break;
+    const uint64_t r1 = std::min<uint64_t>(rows, r0 + rows_per_slice);
+    GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_in + r0 * wd, h_scalars + r0 * wd, (r1 - r0) * wd * sizeof(int32_t),
+                                        cudaMemcpyHostToDevice, ctx->copy_stream));
+    GRAPE_CUDA_TRY(ctx, cudaEventRecord(ctx->copy_events[sidx], ctx->copy_stream));
+  }
+  for (uint32_t sidx = 0; sidx < n_slices; sidx++) {
+    const uint64_t r0 = (uint64_t)sidx * rows_per_slice;
+    if (r0 >= rows) break;
+    const uint64_t r1 = std::min<uint64_t>(rows, r0 + rows_per_slice);
+    GRAPE_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->copy_events[sidx], 0));
+    rc = grape_commit_i32(ctx, t, d_in + r0 * wd, (r1 - r0) * wd, wd, max_bits, d_out + r0 * GRAPE_JACOBIAN_BYTES);
+    if (rc) return rc;
+  }
   GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(h_out, d_out, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
   GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
   return GRAPE_OK;
