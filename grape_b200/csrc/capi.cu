@@ -192,3 +192,20 @@ extern "C" int grape_prof_read(grape_ctx* ctx, float* total_ms, uint32_t* count)
   ctx->prof_events.clear();
   return GRAPE_OK;
 }
+
+// ---- host-side Fr arithmetic for callers that used libff's Fr --------------------------------
+// (the reference does its claim algebra on the host with libff; these keep a drop-in veneer free
+// of any arithmetic of its own).  All pointers are host pointers to 32-byte Montgomery elements.
+extern "C" void grape_hfr_add(const void* a, const void* b, void* out) {
+  *reinterpret_cast<HostFr*>(out) = fr_add(*reinterpret_cast<const HostFr*>(a), *reinterpret_cast<const HostFr*>(b));
+}
+extern "C" void grape_hfr_sub(const void* a, const void* b, void* out) {
+  *reinterpret_cast<HostFr*>(out) = fr_sub(*reinterpret_cast<const HostFr*>(a), *reinterpret_cast<const HostFr*>(b));
+}
+extern "C" void grape_hfr_mul(const void* a, const void* b, void* out) {
+  *reinterpret_cast<HostFr*>(out) = fr_mul(*reinterpret_cast<const HostFr*>(a), *reinterpret_cast<const HostFr*>(b));
+}
+extern "C" void grape_hfr_inv(const void* a, void* out) {
+  *reinterpret_cast<HostFr*>(out) = fr_inv(*reinterpret_cast<const HostFr*>(a));
+}
+extern "C" void grape_hfr_from_i64(int64_t v, void* out) { *reinterpret_cast<HostFr*>(out) = fr_from_i64(v); }

@@ -206,6 +206,15 @@ int grape_hyrax_open(grape_ctx* ctx, const grape_table* table, const void* d_ten
                      uint32_t layer_num, const void* h_eval_point, uint32_t n_e, const void* h_c,
                      const void* h_G_jacobian, void* h_result, void* h_z, void* h_com_d, void* h_com_ad);
 
+/* ---- host-side Fr arithmetic ---------------------------------------------------------------- */
+/* What the reference does with libff's Fr on the host (claim algebra, src/prove.cu:55-82,
+ * test/llm.cu:98-108).  Host pointers to 32-byte Montgomery elements; outputs may alias inputs. */
+void grape_hfr_add(const void* a, const void* b, void* out);
+void grape_hfr_sub(const void* a, const void* b, void* out);
+void grape_hfr_mul(const void* a, const void* b, void* out);
+void grape_hfr_inv(const void* a, void* out);
+void grape_hfr_from_i64(int64_t v, void* out);
+
 /* ---- allocation-free commitment ------------------------------------------------------------ */
 /* No counterpart in the reference (its commit allocates and frees scratch on every call,
  * src/Hyrax.cu:312-333).  For embedders that may not allocate GPU memory when they commit --
