@@ -132,6 +132,13 @@ class Context:
         self._check(self.lib.grape_d2h(self.handle, out.ctypes.data, ptr, nbytes))
         return out
 
+    def clone(self, src, nbytes: int) -> DeviceBuffer:
+        """Device-to-device copy into a fresh buffer."""
+        buf = DeviceBuffer(self, max(nbytes, 1))
+        if nbytes:
+            self._check(self.lib.grape_d2d(self.handle, buf.ptr, _p(src), nbytes))
+        return buf
+
     def sync(self):
         self._check(self.lib.grape_ctx_sync(self.handle))
 
@@ -230,6 +237,22 @@ class Context:
     def fr_fold(self, d_t, ntot, d_x, c, gap, d_out):
         self._check(self.lib.grape_fr_fold(self.handle, _p(d_t), ntot, _p(d_x), c, gap, _p(d_out)))
 
+    def fr_eval(self, d_t, size: int, u, inner: int | None = None) -> int:
+        """Multilinear evaluation of a tensor at u (``FrTensor::operator()(vector<Fr>)``); the tensor is
+        left intact.  ``inner``: row length when the size is not a power of two (rows are padded to a
+        power of two with zeros; the reference hard-codes 11008)."""
+        du = self.fr_upload(u)
+        out = self.alloc(32)
+        if size == 1 << len(u):
+            self.fr_fold(d_t, size, du, size, 1, out)
+        else:
+            assert inner and size % inner == 0
+            lin = max(inner - 1, 0).bit_length()
+            tmp = self.alloc(inner * 32)
+            self.fr_fold(d_t, size, du.at(lin * 32), size // inner, inner, tmp)
+            self.fr_fold(tmp, inner, du, inner, 1, out)
+        return self.fr_download(out, 1)[0]
+
     def fold_i32(self, d_t, ntot, d_x, c, gap, d_out):
         self._check(self.lib.grape_fold_i32(self.handle, _p(d_t), ntot, _p(d_x), c, gap, _p(d_out)))
 
@@ -299,6 +322,14 @@ def commit_i32_host(ctx: Context, table: GeneratorTable, scalars: np.ndarray, wd
     ctx._check(ctx.lib.grape_commit_i32_host(ctx.handle, table.handle, scalars.ctypes.data, scalars.size, wd,
                                              max_bits, out.ctypes.data))
     return out
+
+
+def reassemble_vectors(first, second, first_size: int, same_size: int, last_size: int):
+    """``ReassembleVectors`` (src/ec_operation.cu:74-122): the two points at which prove_matmul's
+    returned claims hold; returns the new (first, second)."""
+    r1 = list(second[:same_size]) + list(first[last_size:last_size + first_size]) + list(second[same_size:])
+    r2 = list(second[:same_size]) + list(first[:last_size]) + list(second[same_size:])
+    return r1, r2
 
 
 # ----------------------------------------------------------------------------- sumcheck provers

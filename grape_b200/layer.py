@@ -1,0 +1,241 @@
+"""Proof of the feed-forward half of one (batch of) LLaMA-2 decoder layer(s): the call sequence of
+the reference's end-to-end driver, test/llm.cu:73-262, on top of this package's provers.
+
+Tensors are the quantised intermediates the reference's data producer dumps (zzllama/llama/model.py):
+for every matmul Y = X W^T the quotient q = round(Y / s) and remainder rem = Y - q s are stored and
+the prover (i) range-checks rem with a lookup, (ii) opens it, (iii) continues with the claim
+q~(e) s + rem~(e) (test/llm.cu:98-108).  `synthesize_ffn` produces self-consistent tensors of any
+shape from a seed; the reference reads them from files that are not distributable.
+
+The walk is backwards from the block output, exactly in the reference's order:
+  open(output) -> down_out (value, remainder lookup) -> matmul down (+ open W_down)
+  -> upSilu remainder -> Hadamard up_out * silu_out -> SwiGLU mapping lookup on (gate_out, silu_out)
+  -> up_out remainder -> matmul up (+ open W_up) -> gate_out remainder (scale 2) -> matmul gate
+  (+ open W_gate) -> combine the two claims on the block input.
+Every junction the reference asserts is checked here and raises `ProofError`.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+
+from . import host
+from .host import Context, GeneratorTable, Lookup, decode_field, reassemble_vectors
+
+R = host.FR_MODULUS
+
+
+class ProofError(RuntimeError):
+    pass
+
+
+def log2ceil(n: int) -> int:
+    return max(n - 1, 0).bit_length()
+
+
+@dataclass
+class FFNShape:
+    layer_num: int
+    tokens: int
+    dim: int
+    ffn: int
+    scale1: int = 1 << 16          # matmul rescale (reference SCALE1)
+    scale2: int = 1 << 20          # SwiGLU gate rescale (reference SCALE2)
+    swiglu_low: int = -(1 << 18)   # mapping table range (reference: tLookupRangeMapping(-(1<<18), 1<<19, ...))
+    swiglu_len: int = 1 << 19
+    npoints: int = 16384           # reference global `npoints`: msm_size of the wide lookups
+
+    @property
+    def ffn_pad(self) -> int:
+        return 1 << log2ceil(self.ffn)
+
+
+def round_div(x: np.ndarray, s: int):
+    q = np.floor_divide(x + s // 2, s)
+    return q, x - q * s
+
+
+def synthesize_ffn(shape: FFNShape, seed: int, x_range: int = 1 << 13, w_std: float = 0.02 * 65536,
+                   matmul=None):
+    """Self-consistent integer tensors of the FFN block.  `matmul(a, b)` multiplies int64 arrays
+    [..., n, k] x [..., m, k]^T exactly (default: numpy int64)."""
+    rng = np.random.default_rng(seed)
+    L, T, d, F = shape.layer_num, shape.tokens, shape.dim, shape.ffn
+    if matmul is None:
+        matmul = lambda a, b: np.einsum("lnk,lmk->lnm", a, b)
+    x = rng.integers(-x_range, x_range, size=(L, T, d)).astype(np.int64)
+    wgen = lambda *s: np.clip(np.rint(rng.normal(0, w_std, size=s)), -(1 << 15), (1 << 15) - 1).astype(np.int64)
+    W_up, W_gate, W_down = wgen(L, F, d), wgen(L, F, d), wgen(L, d, F)
+    table = np.clip(np.rint(rng.normal(0, shape.scale1, size=shape.swiglu_len)), -(1 << 30), (1 << 30)).astype(np.int64)
+    table[-shape.swiglu_low] = 0  # f(0) = 0, as for SiLU: zero padding of the ffn axis stays inside the relation
+    up_q, up_rem = round_div(matmul(x, W_up), shape.scale1)
+    gate_q, gate_rem = round_div(matmul(x, W_gate), shape.scale2)
+    if gate_q.min() < shape.swiglu_low or gate_q.max() >= shape.swiglu_low + shape.swiglu_len:
+        raise ValueError("gate values leave the SwiGLU table; lower x_range / w_std")
+    silu = table[gate_q - shape.swiglu_low]
+    upsilu_q, upsilu_rem = round_div(up_q * silu, shape.scale1)
+    down_q, down_rem = round_div(matmul(upsilu_q, W_down), shape.scale1)
+    skip = rng.integers(-x_range, x_range, size=(L, T, d)).astype(np.int64)
+    t = {"x": x, "W_up": W_up, "W_gate": W_gate, "W_down": W_down, "up_q": up_q, "up_rem": up_rem, "gate_q": gate_q,
+         "gate_rem": gate_rem, "silu": silu, "upsilu_q": upsilu_q, "upsilu_rem": upsilu_rem, "down_q": down_q,
+         "down_rem": down_rem, "output": down_q + skip, "swiglu_table": table}
+    for k, v in t.items():
+        if np.abs(v).max() >= 1 << 31:
+            raise ValueError(f"{k} does not fit int32")
+    return {k: v.astype(np.int32) for k, v in t.items()}
+
+
+@dataclass
+class FFNTrace:
+    """Values at the junctions of the walk (what a verifier would receive besides the openings)."""
+    values: dict = field(default_factory=dict)
+    opens: int = 0
+    lookups: int = 0
+    matmuls: int = 0
+
+
+class FFNProver:
+    """Holds the lookup tables and the generator table; `prove` walks one block."""
+
+    def __init__(self, ctx: Context, shape: FFNShape, table: GeneratorTable, G_jacobian: np.ndarray,
+                 swiglu_table: np.ndarray):
+        self.ctx, self.shape, self.table, self.G = ctx, shape, table, G_jacobian
+        s = shape
+        # draw order of the reference: the opening scalar c first (test/llm.cu:52), then the lookup
+        # objects' alpha / r in construction order (test/llm.cu:54-64)
+        self.c = decode_field(ctx.random_fr(1))[0]
+        self.rs = Lookup(ctx, -(s.scale1 // 2), s.scale1)
+        self.swiglu_rs = Lookup(ctx, -(s.scale2 // 2), s.scale2)
+        self.swiglu = Lookup(ctx, s.swiglu_low, s.swiglu_len, swiglu_table)
+
+    # -- helpers ---------------------------------------------------------------------------------
+    def _fr(self, ints: np.ndarray):
+        """int32 host tensor -> Fr tensor on the device, sized for row padding of the ffn axis."""
+        flat = np.ascontiguousarray(ints, dtype=np.int32).reshape(-1)
+        d_int = self.ctx.upload(flat)
+        cap = flat.size
+        if flat.size % self.shape.ffn == 0 and self.shape.ffn != self.shape.ffn_pad:
+            cap = flat.size // self.shape.ffn * self.shape.ffn_pad
+        buf = self.ctx.alloc(cap * 32)
+        self.ctx.fr_from_i32(d_int, flat.size, buf)
+        d_int.free()
+        return buf, flat.size
+
+    def _draw(self, n: int):
+        return decode_field(self.ctx.random_fr(n))
+
+    def _open(self, buf, size: int, e, N: int, trace: FFNTrace):
+        trace.opens += 1
+        return host.hyrax_open(self.ctx, self.table, buf, size, N, self.shape.layer_num, e, self.c, self.G)
+
+    def _rescale(self, lk: Lookup, rem_ints, e, msm: int, open_N: int, q_claim: int, scale: int, trace, name):
+        """Remainder lookup + opening + claim algebra (test/llm.cu:98-108 pattern)."""
+        s = self.shape
+        rem, size = self._fr(rem_ints)
+        keep = self.ctx.clone(rem, size * 32)
+        cap = (1 << log2ceil(size))
+        A = self.ctx.alloc(cap * 32)
+        trace.lookups += 1
+        lookup_value, _ = lk.prove(rem, size, A, e, inner=s.ffn, inner_pad=s.ffn_pad, table=self.table, msm_size=msm)
+        proof = self._open(keep, size, e, open_N, trace)
+        if proof["result"] != lookup_value:
+            raise ProofError(f"{name}: opening of the remainder disagrees with the lookup claim")
+        for b in (rem, keep, A):
+            b.free()
+        value = (q_claim * scale + lookup_value) % R
+        trace.values[name] = value
+        return value
+
+    # -- the walk ----------------------------------------------------------------------------------
+    def prove(self, t: dict) -> FFNTrace:
+        ctx, s = self.ctx, self.shape
+        L, T, d, F = s.layer_num, s.tokens, s.dim, s.ffn
+        lT, ld, lF = log2ceil(T), log2ceil(d), log2ceil(F)
+        trace = FFNTrace()
+        # output opening and the skip split (test/llm.cu:75-92)
+        out, size = self._fr(t["output"])
+        e1 = self._draw(log2ceil(size))
+        proof = self._open(out, size, e1, size // L // T, trace)
+        out.free()
+        dq, _ = self._fr(t["down_q"])
+        down_out_value = ctx.fr_eval(dq, size, e1)
+        dq.free()
+        trace.values["skip"] = (proof["result"] - down_out_value) % R
+        skip_eval_point = list(e1)
+        down_out_value = self._rescale(self.rs, t["down_rem"], e1, d, size // L // T, down_out_value, s.scale1, trace, "down_out")
+        # matmul down (test/llm.cu:111-125)
+        A, _ = self._fr(t["upsilu_q"])
+        W, wsize = self._fr(t["W_down"])
+        Wkeep = ctx.clone(W, wsize * 32)
+        e2 = self._draw(log2ceil(F * L))
+        trace.matmuls += 1
+        a_cl, b_cl, _, _ = host.prove_matmul(ctx, A, W, L, T, d, F, e1, e2, down_out_value)
+        e1, e2 = reassemble_vectors(e1, e2, lT, lF, ld)
+        proof = self._open(Wkeep, wsize, e2, F, trace)
+        if proof["result"] != b_cl:
+            raise ProofError("down: opening of W_down disagrees with the sumcheck claim")
+        for b in (A, W, Wkeep):
+            b.free()
+        # upSilu remainder (test/llm.cu:128-138)
+        upsilu_value = self._rescale(self.rs, t["upsilu_rem"], e1, s.npoints, F, a_cl, s.scale1, trace, "upSilu")
+        # Hadamard product up_out * silu_out (test/llm.cu:140-150)
+        up, esize = self._fr(t["up_q"])
+        silu, _ = self._fr(t["silu"])
+        silu_keep = ctx.clone(silu, esize * 32)
+        e2 = self._draw(log2ceil(esize))
+        up_cl, silu_cl, _, _ = host.prove_elemul(ctx, up, silu, L, T, F, e1, e2, upsilu_value)
+        trace.values["silu_at_e2"] = silu_cl
+        up.free()
+        silu.free()
+        # SwiGLU mapping lookup on (gate_out, silu_out) (test/llm.cu:153-166)
+        gate, gsize = self._fr(t["gate_q"])
+        e1 = self._draw(log2ceil(gsize))
+        cap = 1 << log2ceil(gsize)
+        work, Abuf = ctx.alloc(cap * 32), ctx.alloc(cap * 32)
+        trace.lookups += 1
+        lookup_value, _ = self.swiglu.prove_pairs(gate, silu_keep, gsize, work, Abuf, e1, inner=F, inner_pad=s.ffn_pad,
+                                                  table=self.table, msm_size=s.npoints)
+        gate_out_value = self._open(gate, gsize, e1, F, trace)["result"]
+        silu_open = self._open(silu_keep, gsize, e1, F, trace)["result"]
+        if lookup_value != (gate_out_value + silu_open * self.swiglu.r) % R:
+            raise ProofError("swiglu: lookup claim disagrees with the two openings")
+        for b in (gate, silu_keep, work, Abuf):
+            b.free()
+        # up_out remainder (test/llm.cu:169-178)
+        up_out_value = self._rescale(self.rs, t["up_rem"], e2, s.npoints, F, up_cl, s.scale1, trace, "up_out")
+        # matmul up (test/llm.cu:181-198)
+        x, xsize = self._fr(t["x"])
+        x_keep = ctx.clone(x, xsize * 32)
+        W, wsize = self._fr(t["W_up"])
+        Wkeep = ctx.clone(W, wsize * 32)
+        e3 = self._draw(log2ceil(d * L))
+        trace.matmuls += 1
+        n1, w_cl, _, _ = host.prove_matmul(ctx, x, W, L, T, F, d, e2, e3, up_out_value)
+        e2, e3 = reassemble_vectors(e2, e3, lT, ld, lF)
+        if self._open(Wkeep, wsize, e3, d, trace)["result"] != w_cl:
+            raise ProofError("up: opening of W_up disagrees with the sumcheck claim")
+        for b in (x, W, Wkeep):
+            b.free()
+        # gate_out remainder at the second scale (test/llm.cu:204-213)
+        gate_out_value = self._rescale(self.swiglu_rs, t["gate_rem"], e1, s.npoints, F, gate_out_value, s.scale2, trace, "gate_out")
+        # matmul gate (test/llm.cu:216-231)
+        x2 = ctx.clone(x_keep, xsize * 32)
+        W, wsize = self._fr(t["W_gate"])
+        Wkeep = ctx.clone(W, wsize * 32)
+        e3 = self._draw(log2ceil(d * L))
+        trace.matmuls += 1
+        n2, w_cl, _, _ = host.prove_matmul(ctx, x2, W, L, T, F, d, e1, e3, gate_out_value)
+        e1, e3 = reassemble_vectors(e1, e3, lT, ld, lF)
+        if self._open(Wkeep, wsize, e3, d, trace)["result"] != w_cl:
+            raise ProofError("gate: opening of W_gate disagrees with the sumcheck claim")
+        for b in (x2, W, Wkeep):
+            b.free()
+        # both claims on the block input become one (test/llm.cu:234-239)
+        e3 = self._draw(log2ceil(d * L * T))
+        value, _ = host.combine_claims(ctx, x_keep, d * L * T, [n1, n2], [e2, e1], e3)
+        x_keep.free()
+        trace.values["normOutSecond"] = value
+        trace.values["normOutSecond_point"] = e3
+        trace.values["skip_point"] = skip_eval_point
+        return trace

@@ -491,7 +491,7 @@ def commit_rows(scalars, wd, gens):
     return [bn254.msm(scalars[r * wd:(r + 1) * wd], gens[:wd]) for r in range(len(scalars) // wd)]
 
 
-def hyrax_open(t, e, c, size, N, layer_num, gens, G, d):
+def hyrax_open(t, e, c, size, N, layer_num, gens, G, d, msm_fn=None):
     """``Hyrax::open`` (src/Hyrax.cu:237-305).  ``d`` is the injected blinding vector of
     16 * 2^ceil(log2 N) field elements (the reference draws it at src/Hyrax.cu:253-256).
     Returns dict(result, z, com_d, com_ad)."""
@@ -502,7 +502,7 @@ def hyrax_open(t, e, c, size, N, layer_num, gens, G, d):
     assert len(e) == log2ceil(size)
     assert len(d) == new_n
     wd = N * COM_SCALE
-    com_d = bn254.msm(d, gens[:new_n])
+    com_d = (msm_fn or bn254.msm)(d, gens[:new_n])
     t = list(t[:size])
     t = partial_eval(t, size, e, (size // layer_num) // wd, log2ceil(wd), wd)
     t = partial_eval(t, wd * layer_num, e, layer_num, log2ceil(size // layer_num), wd)
