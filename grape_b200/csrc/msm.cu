@@ -118,30 +118,34 @@ __global__ void __launch_bounds__(128) table_build_kernel(const Jacobian* __rest
 
 // ------------------------------------------------------------------------------------------
 // Scalar preparation for Fr scalars: leave Montgomery form and add the signed-digit bias, so the
-// accumulate kernel can read window e_w = (v + bias) >> (c w) and use digit e_w - 2^(c-1).
+// accumulate kernel can read window e_w = bits [c w, c w + c) of (v + bias) and use digit e_w - 2^(c-1).
 // ------------------------------------------------------------------------------------------
+struct Bias256 {
+  uint32_t v[8];
+};
+
 __global__ void fr_bias_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out,
-                               uint64_t n, uint32_t window_bits, uint32_t total_windows) {
+                               uint64_t n, Bias256 bias) {
   uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= n) return;
   Fr s = Fr::load_nc(in + gid * 8);
   s = fe_from_mont(s);
-  uint32_t bias[8];
-#pragma unroll
-  for (int k = 0; k < 8; k++) bias[k] = (window_bits == 8) ? 0x80808080u : 0x80008000u;
-  // the top window keeps its unsigned value: clear the bias of windows >= total_windows - 1
-  uint32_t top_bit = window_bits * (total_windows - 1);
-#pragma unroll
-  for (int k = 0; k < 8; k++) {
-    uint32_t lo = 32u * k;
-    if (lo >= top_bit) bias[k] = 0;
-    else if (lo + 32 > top_bit) bias[k] &= (1u << (top_bit - lo)) - 1u;
-  }
   uint32_t r[8];
-  add8(r, s.v, bias);
+  add8(r, s.v, bias.v);  // value < 2^254 and bias < 2^254: no carry out
   uint4* o = reinterpret_cast<uint4*>(out + gid * 8);
   o[0] = make_uint4(r[0], r[1], r[2], r[3]);
   o[1] = make_uint4(r[4], r[5], r[6], r[7]);
+}
+
+// 2^(c-1) at the bottom of every window below the top one
+static Bias256 make_bias(uint32_t c, uint32_t total_windows) {
+  Bias256 b;
+  for (int k = 0; k < 8; k++) b.v[k] = 0;
+  for (uint32_t w = 0; w + 1 < total_windows; w++) {
+    uint32_t bit = c * w + c - 1;
+    b.v[bit >> 5] |= 1u << (bit & 31);
+  }
+  return b;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -197,8 +201,9 @@ commit_accumulate_kernel(const void* __restrict__ scalars, TableView tab, uint32
       if (FR) {
         const uint32_t* sp = reinterpret_cast<const uint32_t*>(scalars) + idx * 8;
         for (uint32_t w = w_lo; w < w_hi; w++) {
-          uint32_t bit = c * w;
-          uint32_t e = (__ldg(sp + (bit >> 5)) >> (bit & 31)) & mask;
+          uint32_t bit = c * w, word = bit >> 5;
+          uint32_t lo = __ldg(sp + word), hi = word < 7 ? __ldg(sp + word + 1) : 0u;
+          uint32_t e = __funnelshift_r(lo, hi, bit & 31) & mask;
           int32_t d = (w + 1 == total_windows) ? (int32_t)e : (int32_t)e - (int32_t)half;
           if (d == 0) continue;
           uint32_t mag = d < 0 ? (uint32_t)(-d) : (uint32_t)d;
@@ -300,8 +305,8 @@ using namespace grape;
 extern "C" int grape_table_create(grape_ctx* ctx, const void* d_gens_jacobian, uint32_t n_gens,
                                   uint32_t window_bits, uint32_t n_windows, grape_table** out) {
   if (!ctx || !out || !d_gens_jacobian) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
-  if (window_bits != 8 && window_bits != 16)
-    return fail(ctx, GRAPE_ERR_INVALID, "window_bits must be 8 or 16");
+  if (window_bits < 5 || window_bits > 16)
+    return fail(ctx, GRAPE_ERR_INVALID, "window_bits must be between 5 and 16");
   if (n_gens == 0 || n_windows == 0 || n_windows * window_bits > 256)
     return fail(ctx, GRAPE_ERR_INVALID, "bad table geometry");
   uint32_t half = 1u << (window_bits - 1);
@@ -408,7 +413,7 @@ int commit_fr_async(grape_ctx* ctx, const grape_table* t, const void* d_scalars,
   rc = arena_alloc_t(ctx, size * 8, &biased);
   if (rc) return rc;
   fr_bias_kernel<<<(uint32_t)((size + 255) / 256), 256, 0, ctx->stream>>>(
-      reinterpret_cast<const uint32_t*>(d_scalars), biased, size, t->window_bits, total_windows);
+      reinterpret_cast<const uint32_t*>(d_scalars), biased, size, make_bias(t->window_bits, total_windows));
   ctx->launches += 1;
   return launch_commit<true>(ctx, t, biased, rows, wd, total_windows, partials, n_chunks, d_out);
 }
@@ -553,9 +558,9 @@ extern "C" int grape_commit_i32_static(const void* d_table, uint32_t n_gens, uin
     snprintf(g_static_error, sizeof g_static_error, "null argument");
     return GRAPE_ERR_INVALID;
   }
-  if ((window_bits != 8 && window_bits != 16) || n_windows == 0 || wd == 0 || wd > n_gens || size % wd != 0 ||
+  if (window_bits < 5 || window_bits > 16 || n_windows == 0 || wd == 0 || wd > n_gens || size % wd != 0 ||
       max_bits == 0 || max_bits > 32) {
-    snprintf(g_static_error, sizeof g_static_error, "bad geometry (window_bits 8|16, wd <= n_gens, size %% wd == 0, max_bits 1..32)");
+    snprintf(g_static_error, sizeof g_static_error, "bad geometry (window_bits 5..16, wd <= n_gens, size %% wd == 0, max_bits 1..32)");
     return GRAPE_ERR_INVALID;
   }
   int device = 0;

@@ -463,6 +463,28 @@ def hyrax_open(ctx: Context, table: GeneratorTable, d_tensor, size: int, N: int,
     ctx._check(ctx.lib.grape_hyrax_open(ctx.handle, table.handle, _p(d_tensor), size, N, layer_num, he.ctypes.data,
                                         len(eval_point), hc.ctypes.data, G.ctypes.data, res.ctypes.data, z.ctypes.data,
                                         com[0].ctypes.data, com[1].ctypes.data))
-    pts = decode_jacobian(com)
-    return {"result": decode_field(res)[0], "z": decode_field(z), "com_d": pts[0], "com_ad": pts[1],
-            "com_bytes": com.tobytes()}
+    return OpenProof(res, z, com)
+
+
+class OpenProof:
+    """Result of ``hyrax_open`` (the reference's ``Hyrax_proof``).  Holds the raw records; the Python
+    integers / affine tuples are decoded on first use (decoding a long z vector is slow)."""
+
+    def __init__(self, res: np.ndarray, z: np.ndarray, com: np.ndarray):
+        self.result_raw, self.z_raw, self.com_raw = res, z, com
+        self._cache = {}
+
+    def __getitem__(self, key: str):
+        if key not in self._cache:
+            if key == "result":
+                self._cache[key] = decode_field(self.result_raw)[0]
+            elif key == "z":
+                self._cache[key] = decode_field(self.z_raw)
+            elif key in ("com_d", "com_ad"):
+                pts = decode_jacobian(self.com_raw)
+                self._cache["com_d"], self._cache["com_ad"] = pts
+            elif key == "com_bytes":
+                self._cache[key] = self.com_raw.tobytes()
+            else:
+                raise KeyError(key)
+        return self._cache[key]

@@ -16,6 +16,8 @@ Every junction the reference asserts is checked here and raises `ProofError`.
 """
 from __future__ import annotations
 
+import contextlib
+import time
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -93,6 +95,7 @@ class FFNTrace:
     opens: int = 0
     lookups: int = 0
     matmuls: int = 0
+    seconds: dict = field(default_factory=dict)  # wall time per kind of step (filled when timing is on)
 
 
 class FFNProver:
@@ -109,17 +112,59 @@ class FFNProver:
         self.swiglu_rs = Lookup(ctx, -(s.scale2 // 2), s.scale2)
         self.swiglu = Lookup(ctx, s.swiglu_low, s.swiglu_len, swiglu_table)
 
+    timing = False  # set to True to synchronise around every step and fill FFNTrace.seconds
+
+    @contextlib.contextmanager
+    def _phase(self, trace, name):
+        if not self.timing:
+            yield
+            return
+        self.ctx.sync()
+        t0 = time.perf_counter()
+        yield
+        self.ctx.sync()
+        trace.seconds[name] = trace.seconds.get(name, 0.0) + time.perf_counter() - t0
+
     # -- helpers ---------------------------------------------------------------------------------
+    # Device buffers are recycled between steps (the reference keeps three preallocated tensors for
+    # the same reason: allocating and freeing multi-gigabyte buffers per step costs more than the proof).
+    def _alloc(self, nbytes: int):
+        pool = self.__dict__.setdefault("_pool", [])
+        best = None
+        for b in pool:
+            if nbytes <= b.nbytes <= 2 * max(nbytes, 1) and (best is None or b.nbytes < best.nbytes):
+                best = b
+        if best is not None:
+            pool.remove(best)
+            return best
+        return self.ctx.alloc(nbytes)
+
+    def _release(self, *bufs):
+        self.__dict__.setdefault("_pool", []).extend(bufs)
+
+    def _clone(self, src, nbytes: int):
+        buf = self._alloc(nbytes)
+        self.ctx._check(self.ctx.lib.grape_d2d(self.ctx.handle, buf.ptr, src.ptr, nbytes))
+        return buf
+
+    def release_pool(self):
+        for b in self.__dict__.pop("_pool", []):
+            b.free()
+
     def _fr(self, ints: np.ndarray):
         """int32 host tensor -> Fr tensor on the device, sized for row padding of the ffn axis."""
         flat = np.ascontiguousarray(ints, dtype=np.int32).reshape(-1)
-        d_int = self.ctx.upload(flat)
+        t0 = time.perf_counter()
+        d_int = self._alloc(flat.nbytes)
+        self.ctx._check(self.ctx.lib.grape_h2d(self.ctx.handle, d_int.ptr, flat.ctypes.data, flat.nbytes))
+        self.ctx.sync()
+        self.upload_seconds = getattr(self, "upload_seconds", 0.0) + time.perf_counter() - t0
         cap = flat.size
         if flat.size % self.shape.ffn == 0 and self.shape.ffn != self.shape.ffn_pad:
             cap = flat.size // self.shape.ffn * self.shape.ffn_pad
-        buf = self.ctx.alloc(cap * 32)
+        buf = self._alloc(cap * 32)
         self.ctx.fr_from_i32(d_int, flat.size, buf)
-        d_int.free()
+        self._release(d_int)
         return buf, flat.size
 
     def _draw(self, n: int):
@@ -127,22 +172,23 @@ class FFNProver:
 
     def _open(self, buf, size: int, e, N: int, trace: FFNTrace):
         trace.opens += 1
-        return host.hyrax_open(self.ctx, self.table, buf, size, N, self.shape.layer_num, e, self.c, self.G)
+        with self._phase(trace, "open"):
+            return host.hyrax_open(self.ctx, self.table, buf, size, N, self.shape.layer_num, e, self.c, self.G)
 
     def _rescale(self, lk: Lookup, rem_ints, e, msm: int, open_N: int, q_claim: int, scale: int, trace, name):
         """Remainder lookup + opening + claim algebra (test/llm.cu:98-108 pattern)."""
         s = self.shape
         rem, size = self._fr(rem_ints)
-        keep = self.ctx.clone(rem, size * 32)
+        keep = self._clone(rem, size * 32)
         cap = (1 << log2ceil(size))
-        A = self.ctx.alloc(cap * 32)
+        A = self._alloc(cap * 32)
         trace.lookups += 1
-        lookup_value, _ = lk.prove(rem, size, A, e, inner=s.ffn, inner_pad=s.ffn_pad, table=self.table, msm_size=msm)
+        with self._phase(trace, "lookup"):
+            lookup_value, _ = lk.prove(rem, size, A, e, inner=s.ffn, inner_pad=s.ffn_pad, table=self.table, msm_size=msm)
         proof = self._open(keep, size, e, open_N, trace)
         if proof["result"] != lookup_value:
             raise ProofError(f"{name}: opening of the remainder disagrees with the lookup claim")
-        for b in (rem, keep, A):
-            b.free()
+        self._release(rem, keep, A)
         value = (q_claim * scale + lookup_value) % R
         trace.values[name] = value
         return value
@@ -157,84 +203,85 @@ class FFNProver:
         out, size = self._fr(t["output"])
         e1 = self._draw(log2ceil(size))
         proof = self._open(out, size, e1, size // L // T, trace)
-        out.free()
+        self._release(out)
         dq, _ = self._fr(t["down_q"])
         down_out_value = ctx.fr_eval(dq, size, e1)
-        dq.free()
+        self._release(dq)
         trace.values["skip"] = (proof["result"] - down_out_value) % R
         skip_eval_point = list(e1)
         down_out_value = self._rescale(self.rs, t["down_rem"], e1, d, size // L // T, down_out_value, s.scale1, trace, "down_out")
         # matmul down (test/llm.cu:111-125)
         A, _ = self._fr(t["upsilu_q"])
         W, wsize = self._fr(t["W_down"])
-        Wkeep = ctx.clone(W, wsize * 32)
+        Wkeep = self._clone(W, wsize * 32)
         e2 = self._draw(log2ceil(F * L))
         trace.matmuls += 1
-        a_cl, b_cl, _, _ = host.prove_matmul(ctx, A, W, L, T, d, F, e1, e2, down_out_value)
+        with self._phase(trace, "matmul"):
+            a_cl, b_cl, _, _ = host.prove_matmul(ctx, A, W, L, T, d, F, e1, e2, down_out_value)
         e1, e2 = reassemble_vectors(e1, e2, lT, lF, ld)
         proof = self._open(Wkeep, wsize, e2, F, trace)
         if proof["result"] != b_cl:
             raise ProofError("down: opening of W_down disagrees with the sumcheck claim")
-        for b in (A, W, Wkeep):
-            b.free()
+        self._release(A, W, Wkeep)
         # upSilu remainder (test/llm.cu:128-138)
         upsilu_value = self._rescale(self.rs, t["upsilu_rem"], e1, s.npoints, F, a_cl, s.scale1, trace, "upSilu")
         # Hadamard product up_out * silu_out (test/llm.cu:140-150)
         up, esize = self._fr(t["up_q"])
         silu, _ = self._fr(t["silu"])
-        silu_keep = ctx.clone(silu, esize * 32)
+        silu_keep = self._clone(silu, esize * 32)
         e2 = self._draw(log2ceil(esize))
-        up_cl, silu_cl, _, _ = host.prove_elemul(ctx, up, silu, L, T, F, e1, e2, upsilu_value)
+        with self._phase(trace, "elemul"):
+            up_cl, silu_cl, _, _ = host.prove_elemul(ctx, up, silu, L, T, F, e1, e2, upsilu_value)
         trace.values["silu_at_e2"] = silu_cl
-        up.free()
-        silu.free()
+        self._release(up, silu)
         # SwiGLU mapping lookup on (gate_out, silu_out) (test/llm.cu:153-166)
         gate, gsize = self._fr(t["gate_q"])
         e1 = self._draw(log2ceil(gsize))
         cap = 1 << log2ceil(gsize)
-        work, Abuf = ctx.alloc(cap * 32), ctx.alloc(cap * 32)
+        work, Abuf = self._alloc(cap * 32), self._alloc(cap * 32)
         trace.lookups += 1
-        lookup_value, _ = self.swiglu.prove_pairs(gate, silu_keep, gsize, work, Abuf, e1, inner=F, inner_pad=s.ffn_pad,
-                                                  table=self.table, msm_size=s.npoints)
+        with self._phase(trace, "lookup"):
+            lookup_value, _ = self.swiglu.prove_pairs(gate, silu_keep, gsize, work, Abuf, e1, inner=F, inner_pad=s.ffn_pad,
+                                                      table=self.table, msm_size=s.npoints)
         gate_out_value = self._open(gate, gsize, e1, F, trace)["result"]
         silu_open = self._open(silu_keep, gsize, e1, F, trace)["result"]
         if lookup_value != (gate_out_value + silu_open * self.swiglu.r) % R:
             raise ProofError("swiglu: lookup claim disagrees with the two openings")
-        for b in (gate, silu_keep, work, Abuf):
-            b.free()
+        self._release(gate, silu_keep, work, Abuf)
         # up_out remainder (test/llm.cu:169-178)
         up_out_value = self._rescale(self.rs, t["up_rem"], e2, s.npoints, F, up_cl, s.scale1, trace, "up_out")
         # matmul up (test/llm.cu:181-198)
         x, xsize = self._fr(t["x"])
-        x_keep = ctx.clone(x, xsize * 32)
+        x_keep = self._clone(x, xsize * 32)
         W, wsize = self._fr(t["W_up"])
-        Wkeep = ctx.clone(W, wsize * 32)
+        Wkeep = self._clone(W, wsize * 32)
         e3 = self._draw(log2ceil(d * L))
         trace.matmuls += 1
-        n1, w_cl, _, _ = host.prove_matmul(ctx, x, W, L, T, F, d, e2, e3, up_out_value)
+        with self._phase(trace, "matmul"):
+            n1, w_cl, _, _ = host.prove_matmul(ctx, x, W, L, T, F, d, e2, e3, up_out_value)
         e2, e3 = reassemble_vectors(e2, e3, lT, ld, lF)
         if self._open(Wkeep, wsize, e3, d, trace)["result"] != w_cl:
             raise ProofError("up: opening of W_up disagrees with the sumcheck claim")
-        for b in (x, W, Wkeep):
-            b.free()
+        self._release(x, W, Wkeep)
         # gate_out remainder at the second scale (test/llm.cu:204-213)
         gate_out_value = self._rescale(self.swiglu_rs, t["gate_rem"], e1, s.npoints, F, gate_out_value, s.scale2, trace, "gate_out")
         # matmul gate (test/llm.cu:216-231)
-        x2 = ctx.clone(x_keep, xsize * 32)
+        x2 = self._clone(x_keep, xsize * 32)
         W, wsize = self._fr(t["W_gate"])
-        Wkeep = ctx.clone(W, wsize * 32)
+        Wkeep = self._clone(W, wsize * 32)
         e3 = self._draw(log2ceil(d * L))
         trace.matmuls += 1
-        n2, w_cl, _, _ = host.prove_matmul(ctx, x2, W, L, T, F, d, e1, e3, gate_out_value)
+        with self._phase(trace, "matmul"):
+            n2, w_cl, _, _ = host.prove_matmul(ctx, x2, W, L, T, F, d, e1, e3, gate_out_value)
         e1, e3 = reassemble_vectors(e1, e3, lT, ld, lF)
         if self._open(Wkeep, wsize, e3, d, trace)["result"] != w_cl:
             raise ProofError("gate: opening of W_gate disagrees with the sumcheck claim")
-        for b in (x2, W, Wkeep):
-            b.free()
+        self._release(x2, W, Wkeep)
         # both claims on the block input become one (test/llm.cu:234-239)
         e3 = self._draw(log2ceil(d * L * T))
-        value, _ = host.combine_claims(ctx, x_keep, d * L * T, [n1, n2], [e2, e1], e3)
-        x_keep.free()
+        with self._phase(trace, "combine"):
+            value, _ = host.combine_claims(ctx, x_keep, d * L * T, [n1, n2], [e2, e1], e3)
+        self._release(x_keep)
         trace.values["normOutSecond"] = value
         trace.values["normOutSecond_point"] = e3
         trace.values["skip_point"] = skip_eval_point

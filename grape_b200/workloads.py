@@ -51,3 +51,16 @@ def make_generators(ctx: Context, n: int, seed: int) -> np.ndarray:
     d_rho.free()
     d_out.free()
     return gens
+
+
+def exact_matmul_cuda(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """[l, n, k] x [l, m, k]^T for int64 arrays, computed exactly on the GPU in float64 (all
+    partial sums of the synthetic tensors stay far below 2^53).  Data preparation only: this is
+    the stand-in for the model's forward pass that produced the reference's dumps."""
+    import torch
+    ta = torch.from_numpy(np.ascontiguousarray(a)).cuda().double()
+    tb = torch.from_numpy(np.ascontiguousarray(b)).cuda().double()
+    r = torch.matmul(ta, tb.transpose(1, 2)).round().long().cpu().numpy()
+    del ta, tb
+    torch.cuda.empty_cache()
+    return r

@@ -68,7 +68,8 @@ int grape_dev_zero(grape_ctx* ctx, void* d_dst, size_t bytes);
 /* ---- generator table ---------------------------------------------------------------------- */
 /* Fixed-base table  T[w][d-1][i] = (2^(window_bits*w) * d) * G_i  for d in 1..2^(window_bits-1),
  * w < n_windows, affine.  Replaces precompute_generators / naive_msm
- * (src/ec_operation.cu:15-49), whose table is w*G_i for w < 256.  window_bits is 8 or 16.
+ * (src/ec_operation.cu:15-49), whose table is w*G_i for w < 256.  window_bits is 5..16: wider
+ * windows mean fewer additions per scalar and a table of 2^(window_bits-1) * n_gens * 64 bytes per window.
  * d_gens_jacobian: n_gens Jacobian records (the reference's cpu_points layout). */
 int grape_table_create(grape_ctx* ctx, const void* d_gens_jacobian, uint32_t n_gens,
                        uint32_t window_bits, uint32_t n_windows, grape_table** out);

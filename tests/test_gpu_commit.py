@@ -28,7 +28,7 @@ def _commit(gctx, table, scalars, wd, max_bits):
     return raw
 
 
-@pytest.mark.parametrize("window_bits,n_windows", [(8, 1), (8, 4), (16, 1), (16, 2)])
+@pytest.mark.parametrize("window_bits,n_windows", [(8, 1), (8, 4), (16, 1), (16, 2), (12, 1), (13, 3), (7, 2), (10, 1)])
 def test_commit_i32_full_range(gctx, gens64, window_bits, n_windows):
     import grape_b200 as g
     rng = random.Random(window_bits * 10 + n_windows)
@@ -83,7 +83,7 @@ def test_commit_degenerate_generators(gctx):
     table.close()
 
 
-@pytest.mark.parametrize("window_bits,n_windows", [(8, 1), (16, 1), (8, 32)])
+@pytest.mark.parametrize("window_bits,n_windows", [(8, 1), (16, 1), (8, 32), (13, 1), (11, 2), (5, 1)])
 def test_commit_fr(gctx, gens64, window_bits, n_windows):
     import grape_b200 as g
     rng = random.Random(99)
