@@ -59,14 +59,17 @@ def round_div(x: np.ndarray, s: int):
 
 
 def synthesize_ffn(shape: FFNShape, seed: int, x_range: int = 1 << 13, w_std: float = 0.02 * 65536,
-                   matmul=None):
+                   matmul=None, x=None, skip=None):
     """Self-consistent integer tensors of the FFN block.  `matmul(a, b)` multiplies int64 arrays
-    [..., n, k] x [..., m, k]^T exactly (default: numpy int64)."""
+    [..., n, k] x [..., m, k]^T exactly (default: numpy int64).  `x` (block input) and `skip`
+    (residual added to the block output) are drawn at random unless given."""
     rng = np.random.default_rng(seed)
     L, T, d, F = shape.layer_num, shape.tokens, shape.dim, shape.ffn
     if matmul is None:
         matmul = lambda a, b: np.einsum("lnk,lmk->lnm", a, b)
-    x = rng.integers(-x_range, x_range, size=(L, T, d)).astype(np.int64)
+    if x is None:
+        x = rng.integers(-x_range, x_range, size=(L, T, d)).astype(np.int64)
+    x = np.asarray(x, dtype=np.int64)
     wgen = lambda *s: np.clip(np.rint(rng.normal(0, w_std, size=s)), -(1 << 15), (1 << 15) - 1).astype(np.int64)
     W_up, W_gate, W_down = wgen(L, F, d), wgen(L, F, d), wgen(L, d, F)
     table = np.clip(np.rint(rng.normal(0, shape.scale1, size=shape.swiglu_len)), -(1 << 30), (1 << 30)).astype(np.int64)
@@ -78,7 +81,9 @@ def synthesize_ffn(shape: FFNShape, seed: int, x_range: int = 1 << 13, w_std: fl
     silu = table[gate_q - shape.swiglu_low]
     upsilu_q, upsilu_rem = round_div(up_q * silu, shape.scale1)
     down_q, down_rem = round_div(matmul(upsilu_q, W_down), shape.scale1)
-    skip = rng.integers(-x_range, x_range, size=(L, T, d)).astype(np.int64)
+    if skip is None:
+        skip = rng.integers(-x_range, x_range, size=(L, T, d)).astype(np.int64)
+    skip = np.asarray(skip, dtype=np.int64)
     t = {"x": x, "W_up": W_up, "W_gate": W_gate, "W_down": W_down, "up_q": up_q, "up_rem": up_rem, "gate_q": gate_q,
          "gate_rem": gate_rem, "silu": silu, "upsilu_q": upsilu_q, "upsilu_rem": upsilu_rem, "down_q": down_q,
          "down_rem": down_rem, "output": down_q + skip, "swiglu_table": table}

@@ -56,3 +56,34 @@ def test_ffn_block_rejects_inconsistent_remainder(gctx):
     with pytest.raises(g.GrapeError):
         prover.prove(t)
     table.close()
+
+
+def test_whole_layer_matches_oracle(gctx):
+    """FFN half, both RMSNorms, attention (softmax relation, exp lookup, score / Q / K / V matmuls)."""
+    import grape_b200 as g
+    from grape_b200 import layer_full, workloads as wl
+    shape = layer_full.LayerShape(layer_num=2, tokens=16, dim=32, ffn=48, scale1=256, scale2=512, swiglu_low=-256,
+                                  swiglu_len=512, npoints=64, scale3=1 << 9, exp_low=-511, exp_len=512,
+                                  softmax_len=512)
+    t = layer_full.synthesize_layer(shape, seed=5, x_range=512, w_std=24.0)
+    assert np.abs(t["xq_q"]).max() > 0 and np.abs(t["qkv_q"]).max() > 0 and t["exp_in"].min() < 0
+    gens_j = wl.make_generators(gctx, shape.ffn_pad * 16, seed=79)
+    table = g.GeneratorTable(gctx, gens_j, 8, 1)
+    gctx.seed(31337)
+    prover = layer_full.LayerProver(gctx, shape, table, gens_j[0], t["swiglu_table"], t["exp_table"])
+    trace = prover.prove_layer(t)
+    assert trace.matmuls == 11 and trace.lookups == 16  # the reference's 11 matmul sumchecks, 14 range + 2 mapping lookups
+    gens = g.decode_jacobian(gens_j)
+    ctable = cport.table_build(gens_j)
+
+    def msm_fn(scalars, points):
+        enc = np.frombuffer(bn254.fr_vec_to_bytes(scalars), dtype=np.uint32).reshape(-1, 8)
+        rec = cport.commit_fr(enc, len(scalars), ctable[:, :len(scalars)].copy())
+        return bn254.jacobian_from_bytes(rec[0].tobytes())
+
+    flat = {k: v.reshape(-1).tolist() for k, v in t.items()}
+    want = olayer.prove_layer(flat, shape, gens, bn254.SplitMix64(31337), msm_fn)
+    for key in want:
+        assert trace.values[key] == want[key], key
+    prover.release_pool()
+    table.close()
