@@ -49,8 +49,9 @@ def parse_args():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target length of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--proof-layers", type=int, default=0,
-                    help="also time the proof of the feed-forward half of this many layers (one batch, seq 2048)")
+                    help="also time the proof of this many decoder layers (one batch, seq 2048)")
     ap.add_argument("--proof-window-bits", type=int, default=13)
+    ap.add_argument("--proof-scope", default="layer", choices=["layer", "ffn"])
     ap.add_argument("--rows", type=int, default=0, help="commit only this many rows (reduced case for profiling)")
     ap.add_argument("--gens", type=int, default=WD, help="generators = scalars per row (reduced case for profiling)")
     return ap.parse_args()
@@ -192,31 +193,43 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def ffn_half_proof(ctx, layers: int, window_bits: int):
-    """Proof of the feed-forward half of `layers` LLaMA-2-7B-shaped layers in one batch (the call
-    sequence of the reference's end-to-end driver, test/llm.cu:73-262): 3 matmul sumchecks, 1 Hadamard
-    sumcheck, 4 remainder lookups, 1 SwiGLU mapping lookup, 10 openings, 1 claim batching."""
+def layer_proof(ctx, layers: int, window_bits: int, scope: str):
+    """Proof of `layers` LLaMA-2-7B-shaped decoder layers in one batch (seq 2048, dim 4096, ffn 11008) in
+    the call order of the reference's end-to-end driver test/llm.cu:73-611.  scope "layer": everything
+    (11 matmul sumchecks, 3 Hadamard sumchecks, 14 range and 2 mapping lookups, 3 claim batchings and the
+    openings); scope "ffn": the feed-forward half only (test/llm.cu:73-239)."""
     import grape_b200 as g
-    from grape_b200 import layer, workloads as wl
-    shape = layer.FFNShape(layer_num=layers, tokens=2048, dim=4096, ffn=11008)
-    t = layer.synthesize_ffn(shape, seed=0xC5, x_range=1 << 13, matmul=wl.exact_matmul_cuda)
+    from grape_b200 import layer, layer_full, workloads as wl
+    if scope == "ffn":
+        shape = layer.FFNShape(layer_num=layers, tokens=2048, dim=4096, ffn=11008)
+        t = layer.synthesize_ffn(shape, seed=0xC5, x_range=1 << 13, matmul=wl.exact_matmul_cuda)
+    else:
+        shape = layer_full.LayerShape(layer_num=layers, tokens=2048, dim=4096, ffn=11008)
+        t = layer_full.synthesize_layer(shape, seed=0xC5, x_range=1 << 13, matmul=wl.exact_matmul_cuda)
     gens = wl.make_generators(ctx, shape.ffn_pad * 16, 0xC5)
     t0 = time.perf_counter()
     table = g.GeneratorTable(ctx, gens, window_bits, 1)
     ctx.sync()
     table_s = time.perf_counter() - t0
     ctx.seed(1)
-    prover = layer.FFNProver(ctx, shape, table, gens[0], t["swiglu_table"])
-    prover.prove(t)  # warm-up (allocations)
+    if scope == "ffn":
+        prover = layer.FFNProver(ctx, shape, table, gens[0], t["swiglu_table"])
+        run = prover.prove
+    else:
+        prover = layer_full.LayerProver(ctx, shape, table, gens[0], t["swiglu_table"], t["exp_table"])
+        run = prover.prove_layer
+    run(t)  # warm-up (allocations)
     ctx.sync()
-    prover.timing = True
     t0 = time.perf_counter()
-    trace = prover.prove(t)
+    run(t)
     ctx.sync()
     dt = time.perf_counter() - t0
-    out = {"layers": layers, "seconds": dt, "seconds_per_layer": dt / layers, "by_step": trace.seconds,
-           "window_bits": window_bits, "table_gib": table.nbytes / 2**30, "table_build_s": table_s,
-           "opens": trace.opens, "lookups": trace.lookups, "matmul_sumchecks": trace.matmuls,
+    prover.timing = True
+    trace = run(t)
+    out = {"scope": scope, "layers": layers, "seconds": dt, "seconds_per_layer": dt / layers,
+           "by_step_with_syncs": trace.seconds, "window_bits": window_bits, "table_gib": table.nbytes / 2**30,
+           "table_build_s": table_s, "opens": trace.opens, "lookups": trace.lookups,
+           "matmul_sumchecks": trace.matmuls,
            "note": "host int32 tensors are uploaded inside the timed region, as the reference's driver loads them"}
     prover.release_pool()
     table.close()
@@ -347,7 +360,7 @@ def run_own(args):
             "table_bytes": table.nbytes}
 
     if args.proof_layers:
-        line["ffn_half_proof"] = ffn_half_proof(ctx, args.proof_layers, args.proof_window_bits)
+        line["layer_proof"] = layer_proof(ctx, args.proof_layers, args.proof_window_bits, args.proof_scope)
     if not args.no_cpu_baseline and wd == WD:
         base, rows_used, rec = cpu_baseline(gens, np.asarray(h_scalars), args.cpu_seconds)
         base["matches_gpu_rows"] = bool(np.array_equal(rec, dev_records[:rows_used]))
