@@ -52,6 +52,9 @@ def parse_args():
                     help="also time the proof of this many decoder layers (one batch, seq 2048)")
     ap.add_argument("--proof-window-bits", type=int, default=13)
     ap.add_argument("--proof-scope", default="layer", choices=["layer", "ffn"])
+    ap.add_argument("--workload", default="commit", choices=["commit", "matmul", "lookup"],
+                    help="commit = C4 (the headline); matmul = C2 prove_matmul; lookup = C3 range lookup")
+    ap.add_argument("--shrink", type=int, default=1, help="divide the matmul / lookup sizes (profiling cases)")
     ap.add_argument("--rows", type=int, default=0, help="commit only this many rows (reduced case for profiling)")
     ap.add_argument("--gens", type=int, default=WD, help="generators = scalars per row (reduced case for profiling)")
     return ap.parse_args()
@@ -370,10 +373,96 @@ def run_own(args):
         dist.destroy_process_group()
 
 
+def run_secondary(args):
+    """C2 (matmul sumcheck) and C3 (range lookup) as stand-alone timings with the roofline of their
+    dominant kernel; single GPU."""
+    import grape_b200 as g
+    from grape_b200 import host, workloads as wl
+    ctx = g.Context(int(os.environ.get("LOCAL_RANK", "0")))
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    hbm_peak = json.loads(peaks_file.read_text())["hbm_gbs"] if peaks_file.exists() else 6650.0
+    rng = np.random.default_rng(0xC2)
+    times = []
+    if args.workload == "matmul":
+        L, N, M, K = 1, 2048 // args.shrink, 4096 // args.shrink, 4096
+        A = wl.quantised_normal(rng, N * K, lo=-2**31, hi=2**31 - 1)
+        B = wl.quantised_normal(rng, M * K, lo=-2**31, hi=2**31 - 1)
+        dAi, dBi = ctx.upload(A), ctx.upload(B)
+        dA, dB = ctx.alloc(N * K * 32), ctx.alloc(M * K * 32)
+        ctx.seed(0xC2)
+        lM, lN, lK = (M - 1).bit_length(), (N - 1).bit_length(), (K - 1).bit_length()
+        u = host.decode_field(ctx.random_fr(lM + lN))
+        v = host.decode_field(ctx.random_fr(lK))
+        du = ctx.fr_upload(u)
+        a_, b_, one = ctx.alloc(K * 32), ctx.alloc(K * 32), ctx.alloc(32)
+        ctx.fr_from_i32(dAi, N * K, dA)
+        ctx.fr_from_i32(dBi, M * K, dB)
+        ctx.fr_fold(dA, N * K, du.at(lM * 32), N, K, a_)
+        ctx.fr_fold(dB, M * K, du, M, K, b_)
+        ctx.fr_binary("mul", a_, b_, a_, K)
+        ctx.fr_sum(a_, K, one)
+        claim = ctx.fr_download(one, 1)[0]
+        launches = 0
+        for it in range(args.warmup + args.steps):
+            ctx.fr_from_i32(dAi, N * K, dA)
+            ctx.fr_from_i32(dBi, M * K, dB)
+            if it == args.warmup:
+                ctx.prof_enable(True)
+            l0 = ctx.launches
+            ctx.timer_begin()
+            host.prove_matmul(ctx, dA, dB, L, N, M, K, u, v, claim)
+            ms = ctx.timer_end()
+            if it >= args.warmup:
+                times.append(ms)
+                launches += ctx.launches - l0
+        k_ms, k_n = ctx.prof_read()
+        algo_bytes = 32.0 * (N * K + M * K)   # the two axis folds read every element once
+        per_launch = k_ms / max(k_n, 1)
+        achieved = algo_bytes / 2 / (per_launch * 1e-3) / 1e9 if k_n else 0.0  # two launches (A and B) per proof
+        line = {"metric": "prove_matmul_ms", "value": float(np.mean(times)), "unit": "ms", "higher_is_better": False,
+                "config": {"workload": f"C2: prove_matmul A {N}x{K} . B {M}x{K}^T, Fr tensors resident in HBM"},
+                "roofline": {"bound": "hbm", "kernel": "k_fold_axis", "achieved": achieved, "peak": hbm_peak,
+                             "unit": "GB/s", "frac": achieved / hbm_peak, "traffic": None,
+                             "note": "mean over the A-fold and B-fold launches; 32 B read and one field "
+                                     "multiplication per element, so the integer pipe caps it near 2.2 TB/s"},
+                "gpu_launches": int(launches)}
+    else:
+        D, Nt = (1 << 22) // args.shrink, 1 << 16
+        gens = wl.make_generators(ctx, 4096, 0xC3)
+        table = g.GeneratorTable(ctx, gens, args.window_bits if args.window_bits != 16 else 13, 1)
+        ctx.seed(0xC3)
+        lk = host.Lookup(ctx, -(1 << 15), Nt)
+        q = rng.integers(-(1 << 15), 1 << 15, size=D).astype(np.int32)
+        dqi, dS, dAq = ctx.upload(q), ctx.alloc(D * 32), ctx.alloc(D * 32)
+        vv = host.decode_field(ctx.random_fr((D - 1).bit_length()))
+        launches = 0
+        res = {}
+        for label, tab in (("without_commitments", None), ("with_commitments", table)):
+            ts = []
+            for it in range(args.warmup + args.steps):
+                ctx.fr_from_i32(dqi, D, dS)
+                l0 = ctx.launches
+                ctx.timer_begin()
+                lk.prove(dS, D, dAq, vv, table=tab, msm_size=256 if tab else 0)
+                ms = ctx.timer_end()
+                if it >= args.warmup:
+                    ts.append(ms)
+                    launches += ctx.launches - l0
+            res[label] = float(np.mean(ts))
+        line = {"metric": "lookup_prove_ms", "value": res["with_commitments"], "unit": "ms", "higher_is_better": False,
+                "config": {"workload": f"C3: range lookup, {D} queries into a 2^16 table, commitments of A and m over 4096 generators"},
+                "without_commitments_ms": res["without_commitments"], "gpu_launches": int(launches)}
+    line.update({"n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "data": "synthetic",
+                 "dtype": "u32 limbs (254-bit fields)", "vs_baseline": None})
+    print(json.dumps(line))
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "commit":
+        run_secondary(args)
     else:
         run_own(args)
 

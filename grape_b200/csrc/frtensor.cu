@@ -284,8 +284,11 @@ int fold_axis_async(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* 
   } else {
     uint32_t slice_len = (c + n_slices - 1) / n_slices;
     dim3 grid((uint32_t)((n_out + FOLD_THREADS - 1) / FOLD_THREADS), n_slices);
-    k_fold_axis<FROM_I32><<<grid, FOLD_THREADS, 0, ctx->stream>>>(
-        d_t, w, c, gap, n_out, slice_len, n_slices > 1 ? partial : (uint32_t*)d_out);
+    {
+      ProfScope prof(ctx);
+      k_fold_axis<FROM_I32><<<grid, FOLD_THREADS, 0, ctx->stream>>>(
+          d_t, w, c, gap, n_out, slice_len, n_slices > 1 ? partial : (uint32_t*)d_out);
+    }
     ctx->launches += 1;
     if (n_slices > 1) {
       k_sum_slices<<<ew_blocks(ctx, n_out), EW_THREADS, 0, ctx->stream>>>(partial, n_slices, n_out, (uint32_t*)d_out);
