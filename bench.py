@@ -35,6 +35,7 @@ MUL_INSTR_PER_FIELD_MUL = 264  # 8-limb Montgomery product in 32-bit lo/hi multi
 FIELD_MUL_PER_ADD = 10         # mixed XYZZ += affine addition
 ADDS_PER_PAIR_INT16 = 2        # byte windows of a 16-bit magnitude (the reference's cost model)
 ALGO_MUL_INSTR_PER_PAIR = MUL_INSTR_PER_FIELD_MUL * FIELD_MUL_PER_ADD * ADDS_PER_PAIR_INT16  # 5280
+NCU_DRAM_BYTES_PER_PAIR = 69.8  # profiles/commit_accumulate_c4_int16_w16.md
 METRIC = "hyrax_msm_points_per_s"
 UNIT = "points/s"
 
@@ -334,6 +335,7 @@ def run_own(args):
     # ---- roofline of the dominant kernel (commit_accumulate) ----------------------------------
     peak_instr = ctx.measure_int_peak(2)        # lo/hi multiply-add instructions per second, measured now
     peak_fmul = ctx.measure_int_peak(3)
+    peak_madd = ctx.measure_madd_peak()         # mixed additions/s on register-resident operands
     k_ms = kernel_ms / max(kernel_launches, 1)
     achieved = n * ALGO_MUL_INSTR_PER_PAIR / (k_ms * 1e-3)
     peaks_file = ROOT / "MEASURED_PEAKS.json"
@@ -345,10 +347,18 @@ def run_own(args):
                 "peak_source": "measured in this run: dependent-free mad.lo.cc/madc.hi loop at full occupancy",
                 "algorithmic_instr_per_pair": ALGO_MUL_INSTR_PER_PAIR,
                 "kernel_ms": k_ms, "field_mul_peak_per_s": peak_fmul,
+                "executed": {"adds_per_pair": 1 if args.window_bits == 16 else 2,
+                             "adds_per_s": n * (1 if args.window_bits == 16 else 2) / (k_ms * 1e-3),
+                             "register_resident_add_peak_per_s": peak_madd,
+                             "frac_of_add_peak": n * (1 if args.window_bits == 16 else 2) / (k_ms * 1e-3) / peak_madd,
+                             "note": "the same mixed addition looped on registers, no table or scalar traffic: "
+                                     "what the kernel could reach if memory were free"},
+                "traffic": int(n * NCU_DRAM_BYTES_PER_PAIR), "traffic_source": "ncu dram bytes of a reduced case "
+                "(8.4 M pairs: 585 MB read+write = 69.8 B/pair) scaled by pairs; algorithmic 68 B/pair",
                 "hbm": {"achieved_gbs": algo_bytes / (k_ms * 1e-3) / 1e9, "peak_gbs": hbm_peak,
                         "frac": algo_bytes / (k_ms * 1e-3) / 1e9 / hbm_peak,
                         "peak_source": "MEASURED_PEAKS.json" if peaks_file.exists() else "fallback"},
-                "traffic": None}
+                }
 
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",

@@ -99,6 +99,7 @@ def _declare(lib):
     f("grape_fr_fold", [vp, vp, u64, vp, u32, u64, vp])
     f("grape_fold_i32", [vp, vp, u64, vp, u32, u64, vp])
     f("grape_measure_int_peak", [vp, C.c_int, C.POINTER(C.c_double)])
+    f("grape_measure_madd_peak", [vp, C.POINTER(C.c_double)])
     f("grape_timer_begin", [vp])
     f("grape_timer_end", [vp, C.POINTER(C.c_float)])
     f("grape_prof_enable", [vp, C.c_int])

@@ -5,9 +5,21 @@
 //   kind 2: mad.lo.cc + madc.hi  (the lo/hi pair form the field arithmetic is written in)
 //   kind 3: Montgomery multiplications in Fp (field muls per second)
 #include "ctx.cuh"
-#include "field.cuh"
+#include "curve.cuh"
 
 namespace grape {
+
+// Mixed additions on register-resident data (no table, no scalars): the arithmetic ceiling of the
+// commitment inner loop at its own register budget.
+__global__ void __launch_bounds__(128, 4) k_madd_peak(const uint32_t* __restrict__ seed_pts, uint32_t* sink, int iters) {
+  Affine q = Affine::load(seed_pts + (threadIdx.x & 7) * 16);
+  Xyzz acc = Xyzz::from_affine(Affine::load(seed_pts + 8 * 16 + (threadIdx.x & 7) * 16));
+  for (int it = 0; it < iters; it++) {
+    xyzz_madd(acc, q);
+    q.x = acc.zz;  // keep the operands changing; values need not be curve points for timing
+  }
+  if (acc.x.v[0] == 0x12345 && acc.y.v[1] == 7) sink[0] = acc.zz.v[2];
+}
 
 constexpr int PEAK_ITERS = 2048;
 constexpr int PEAK_CHAINS = 8;
@@ -127,5 +139,38 @@ extern "C" int grape_measure_int_peak(grape_ctx* ctx, int kind, double* ops_per_
   else if (kind == 3) per_thread = 2.0 * (PEAK_ITERS / 8);
   else per_thread = 16.0 * (PEAK_ITERS / 64);
   *ops_per_second = per_thread * blocks * threads / (best * 1e-3);
+  return GRAPE_OK;
+}
+
+// Mixed XYZZ additions per second on register-resident operands (kind of ceiling for the
+// commitment kernel: same code, same launch bounds, no memory traffic).
+extern "C" int grape_measure_madd_peak(grape_ctx* ctx, double* adds_per_second) {
+  if (!ctx || !adds_per_second) return GRAPE_ERR_INVALID;
+  arena_reset(ctx);
+  uint32_t* buf = nullptr;
+  int rc = arena_alloc_t(ctx, 16 * 16 + 64, &buf);
+  if (rc) return rc;
+  uint32_t h[16 * 16];
+  for (int i = 0; i < 16 * 16; i++) h[i] = (0x9E3779B9u * (i + 1)) & ((i % 8 == 7) ? 0x0fffffffu : 0xffffffffu);
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(buf, h, sizeof h, cudaMemcpyHostToDevice, ctx->stream));
+  const int blocks = ctx->sm_count * 4, threads = 128, iters = 512;
+  cudaEvent_t e0, e1;
+  GRAPE_CUDA_TRY(ctx, cudaEventCreate(&e0));
+  GRAPE_CUDA_TRY(ctx, cudaEventCreate(&e1));
+  float best = 1e30f;
+  for (int rep = 0; rep < 4; rep++) {
+    cudaEventRecord(e0, ctx->stream);
+    k_madd_peak<<<blocks, threads, 0, ctx->stream>>>(buf, buf + 16 * 16, iters);
+    cudaEventRecord(e1, ctx->stream);
+    ctx->launches += 1;
+    GRAPE_CUDA_TRY(ctx, cudaEventSynchronize(e1));
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    if (rep > 0 && ms < best) best = ms;
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  GRAPE_CUDA_TRY(ctx, cudaGetLastError());
+  *adds_per_second = (double)iters * blocks * threads / (best * 1e-3);
   return GRAPE_OK;
 }

@@ -4,6 +4,7 @@
 // row / layer / inner folds (FrTensor::partial_eval), z = c*x + d, and the host-side scalar
 // multiplication com_ad = <eq, d> * G (libff, :286-291), which here is one small kernel.
 // The input tensor is left intact (the reference folds it in place and destroys it).
+#include <algorithm>
 #include <vector>
 
 #include "ctx.cuh"
@@ -17,6 +18,40 @@ int fold_axis_async(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* 
                     uint64_t gap, void* d_out);
 int commit_fr_async(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t size, uint32_t wd,
                     void* d_out);
+
+// The context's SplitMix64 stream evaluated in parallel: the state after k steps is
+// state0 + k * GOLDEN, so draw i (eight 64-bit outputs: four low words, four high words, reduced
+// mod r as lo + hi * 2^256) needs no sequential dependency.  Same values as rng_next_fr on the host.
+__device__ __forceinline__ uint64_t splitmix_at(uint64_t state0, uint64_t k) {
+  uint64_t z = state0 + k * 0x9E3779B97F4A7C15ull;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+__global__ void k_rng_fr(uint64_t state0, uint64_t n, uint32_t* __restrict__ out) {
+  // 2^128 in Montgomery form; the 512 random bits are folded in four 128-bit pieces so that every
+  // value entering a multiplication is far below the modulus' size limit
+  const uint32_t t128[8] = {0xef8cfeb9u, 0xb075da81u, 0xa5b6cd8cu, 0xa7f12accu,
+                            0x7957bf7bu, 0x32c47504u, 0x48ffa25eu, 0x03d581d7u};
+  Fr T;
+#pragma unroll
+  for (int k = 0; k < 8; k++) T.v[k] = t128[k];
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+    Fr acc = Fr::zero();
+#pragma unroll
+    for (int piece = 3; piece >= 0; piece--) {   // most significant 128 bits first
+      uint64_t a = splitmix_at(state0, 8 * i + 1 + 2 * piece), b = splitmix_at(state0, 8 * i + 2 + 2 * piece);
+      Fr c = Fr::zero();
+      c.v[0] = (uint32_t)a;
+      c.v[1] = (uint32_t)(a >> 32);
+      c.v[2] = (uint32_t)b;
+      c.v[3] = (uint32_t)(b >> 32);
+      acc = fe_add(fe_mul(acc, T), fe_to_mont(c));
+    }
+    acc.store(out + i * 8);
+  }
+}
 
 // out = [s] * P for one Jacobian point and one Fr scalar (Montgomery form): double-and-add, one thread.
 __global__ void k_scalar_mul(const uint32_t* __restrict__ point_jac, const uint32_t* __restrict__ scalar,
@@ -76,11 +111,11 @@ extern "C" int grape_hyrax_open(grape_ctx* ctx, const grape_table* table, const 
   GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_e, e, (size_t)n_e * 32, cudaMemcpyHostToDevice, ctx->stream));
   GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_cG, h_c, 32, cudaMemcpyHostToDevice, ctx->stream));
   GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_cG + 8, h_G_jacobian, 96, cudaMemcpyHostToDevice, ctx->stream));
-  // blinding vector d from the context's random stream (reference: src/Hyrax.cu:253-256)
-  std::vector<HostFr> hd(new_n);
-  for (auto& x : hd) x = rng_next_fr(ctx->rng_state);
-  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_d, hd.data(), (size_t)new_n * 32, cudaMemcpyHostToDevice, ctx->stream));
-  GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));  // hd goes out of scope only after the copy
+  // blinding vector d from the context's random stream (reference: src/Hyrax.cu:253-256), generated on
+  // the device; the host stream is advanced past the 8 words per element it consumed
+  k_rng_fr<<<std::min<uint32_t>((new_n + 127) / 128, (uint32_t)ctx->sm_count * 8), 128, 0, ctx->stream>>>(ctx->rng_state, new_n, d_d);
+  ctx->launches += 1;
+  ctx->rng_state += (uint64_t)new_n * 8 * 0x9E3779B97F4A7C15ull;
   // com_d = sum_i d_i G_i
   if ((rc = commit_fr_async(ctx, table, d_d, new_n, new_n, d_pts))) return rc;
   // x = tensor folded over the row variables, then over the layer variables

@@ -189,6 +189,12 @@ class Context:
         self._check(self.lib.grape_measure_int_peak(self.handle, kind, C.byref(v)))
         return v.value
 
+    def measure_madd_peak(self) -> float:
+        """Mixed point additions per second with register-resident operands."""
+        v = C.c_double()
+        self._check(self.lib.grape_measure_madd_peak(self.handle, C.byref(v)))
+        return v.value
+
     # -- randomness seam
     def seed(self, seed: int):
         self._check(self.lib.grape_rng_seed(self.handle, seed))

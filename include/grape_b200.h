@@ -251,8 +251,12 @@ int grape_ctx_status(grape_ctx* ctx, uint32_t* flags);
 /* Kernels launched by this library on the context so far. */
 uint64_t grape_ctx_launches(const grape_ctx* ctx);
 /* Measured integer-pipe ceilings (operations per second): kind 0 mad.lo.u32, 1 mad.wide.u32,
- * 2 mad.lo.cc/madc.hi pairs (counted as two), 3 Fp Montgomery multiplications. */
+ * 2 mad.lo.cc/madc.hi pairs (counted as two), 3 Fp Montgomery multiplications, 4 the same with a
+ * loop body of 16 inlined multiplications (instruction-fetch probe). */
 int grape_measure_int_peak(grape_ctx* ctx, int kind, double* ops_per_second);
+/* Mixed point additions per second on register-resident operands: the commitment kernel's
+ * arithmetic with no memory traffic, at the same register budget. */
+int grape_measure_madd_peak(grape_ctx* ctx, double* adds_per_second);
 /* CUDA-event stopwatch on the context's stream; grape_timer_end synchronises. */
 int grape_timer_begin(grape_ctx* ctx);
 int grape_timer_end(grape_ctx* ctx, float* ms);
