@@ -116,6 +116,7 @@ def _declare(lib):
     f("grape_lookup_prove_mapping", [vp, vp, vp, vp, u64, vp, vp, vp, u32, u32, u32, vp, u32, vp, vp, vp, vp, u32,
                                      C.POINTER(u32)])
     f("grape_hyrax_open", [vp, vp, vp, u64, u32, u32, vp, u32, vp, vp, vp, vp, vp, vp])
+    f("grape_g1_lincomb", [vp, vp, vp, u64, vp])
     for name in _OPTIONAL:
         if hasattr(lib, name):
             f(name, _OPTIONAL[name])

@@ -142,3 +142,61 @@ extern "C" int grape_hyrax_open(grape_ctx* ctx, const grape_table* table, const 
   GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
   return GRAPE_OK;
 }
+
+// ---- variable-base linear combination (verifier side) ------------------------------------------
+namespace grape {
+// partial[warp] = sum over the warp's points of s_i * P_i (double-and-add per point, shuffle tree)
+__global__ void __launch_bounds__(128) k_lincomb(const uint32_t* __restrict__ points_jac, const uint32_t* __restrict__ scalars,
+                                                  uint64_t n, Xyzz* __restrict__ partial) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  Xyzz acc = Xyzz::inf();
+  if (i < n) {
+    Jacobian j;
+    j.x = Fp::load(points_jac + i * 24);
+    j.y = Fp::load(points_jac + i * 24 + 8);
+    j.z = Fp::load(points_jac + i * 24 + 16);
+    Xyzz base = xyzz_from_jacobian(j);
+    Fr s = fe_from_mont(Fr::load(scalars + i * 8));
+    for (int w = 7; w >= 0; w--) {
+      for (int b = 31; b >= 0; b--) {
+        acc = xyzz_dbl(acc);
+        if ((s.v[w] >> b) & 1u) xyzz_add(acc, base);
+      }
+    }
+  }
+#pragma unroll 1
+  for (int off = 16; off > 0; off >>= 1) {
+    Xyzz other = xyzz_shfl_down(acc, off);
+    if ((threadIdx.x & 31) < off) xyzz_add(acc, other);
+  }
+  if ((threadIdx.x & 31) == 0) acc.store(partial + (i >> 5));
+}
+
+__global__ void k_lincomb_finish(const Xyzz* __restrict__ partial, uint32_t n_partial, uint32_t* __restrict__ out_jac) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  Xyzz acc = Xyzz::inf();
+  for (uint32_t k = 0; k < n_partial; k++) xyzz_add(acc, Xyzz::load(partial + k));
+  bool inf = acc.is_inf();
+  Affine a = xyzz_to_affine(acc);
+  store_jacobian_normalised(out_jac, a, inf);
+}
+}  // namespace grape
+
+// out = sum_i s_i * P_i for arbitrary Jacobian points and Fr scalars in device memory (what the
+// reference's verifier code does on the host with libff: host_partial_me<G1> and Fr * G1,
+// include/ec_operation.cuh:37-55, test/HyraxTest.cu:96-125).  d_out: one normalised Jacobian record.
+extern "C" int grape_g1_lincomb(grape_ctx* ctx, const void* d_points_jacobian, const void* d_scalars, uint64_t n,
+                                void* d_out) {
+  if (!ctx || !d_out || (n && (!d_points_jacobian || !d_scalars))) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
+  if (n > (uint64_t(1) << 24)) return fail(ctx, GRAPE_ERR_LIMIT, "lincomb: at most 2^24 points");
+  arena_reset(ctx);
+  const uint32_t blocks = (uint32_t)std::max<uint64_t>((n + 127) / 128, 1);
+  Xyzz* partial = nullptr;
+  int rc = arena_alloc_t(ctx, (size_t)blocks * 4, &partial);
+  if (rc) return rc;
+  k_lincomb<<<blocks, 128, 0, ctx->stream>>>((const uint32_t*)d_points_jacobian, (const uint32_t*)d_scalars, n, partial);
+  k_lincomb_finish<<<1, 32, 0, ctx->stream>>>(partial, blocks * 4, (uint32_t*)d_out);
+  ctx->launches += 2;
+  GRAPE_CUDA_TRY(ctx, cudaGetLastError());
+  return GRAPE_OK;
+}

@@ -216,6 +216,13 @@ void grape_hfr_mul(const void* a, const void* b, void* out);
 void grape_hfr_inv(const void* a, void* out);
 void grape_hfr_from_i64(int64_t v, void* out);
 
+/* ---- verifier-side group arithmetic ---------------------------------------------------------- */
+/* out = sum_i s_i * P_i over n arbitrary Jacobian points and Fr scalars (device memory); d_out is one
+ * normalised Jacobian record.  Replaces the libff host code of the reference's only verifier
+ * (host_partial_me<G1>, Fr * G1: include/ec_operation.cuh:37-55, test/HyraxTest.cu:96-125). */
+int grape_g1_lincomb(grape_ctx* ctx, const void* d_points_jacobian, const void* d_scalars, uint64_t n,
+                     void* d_out);
+
 /* ---- allocation-free commitment ------------------------------------------------------------ */
 /* No counterpart in the reference (its commit allocates and frees scratch on every call,
  * src/Hyrax.cu:312-333).  For embedders that may not allocate GPU memory when they commit --
