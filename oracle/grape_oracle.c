@@ -442,3 +442,77 @@ void oracle_fr_fold(fe* t, uint64_t ntot, const fe* x, uint32_t c, uint32_t id, 
   }
   for (uint64_t o = 1; o < other; o++) memmove(&t[o * gap], &t[o * dim], gap * sizeof(fe));
 }
+
+/* ------------------------------------------------------------------------------------------ */
+/* Host scalar / group operations and the seeded random stream, exported for the libff stand-in */
+/* that lets the reference's own sources compile (oracle/ref_shim).                              */
+/* ------------------------------------------------------------------------------------------ */
+void oracle_fr_add(const fe* a, const fe* b, fe* out) { fe_add(&FR, out, a, b); }
+void oracle_fr_sub(const fe* a, const fe* b, fe* out) { fe_sub(&FR, out, a, b); }
+void oracle_fr_mul(const fe* a, const fe* b, fe* out) { fe_mul(&FR, out, a, b); }
+void oracle_fr_inv(const fe* a, fe* out) { fe_inv(&FR, out, a); }
+void oracle_fr_from_i64(int64_t v, fe* out) {
+  uint64_t mag = v < 0 ? (uint64_t)(-(v + 1)) + 1 : (uint64_t)v;
+  fe t = {{mag, 0, 0, 0}};
+  fe_to_mont(&FR, &t, &t);
+  if (v < 0) fe_neg(&FR, &t, &t);
+  *out = t;
+}
+
+/* SplitMix64; one draw = eight outputs (lo words, then hi words), value (lo + hi * 2^256) mod r */
+static uint64_t splitmix_next(uint64_t* state) {
+  *state += 0x9E3779B97F4A7C15ull;
+  uint64_t z = *state;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+uint64_t oracle_rng_init(uint64_t seed, uint64_t tag) {
+  return seed * 0x9E3779B97F4A7C15ull + tag * 0xD1B54A32D192ED03ull + 0x632BE59BD9B4E019ull;
+}
+void oracle_rng_fr(uint64_t* state, fe* out) {
+  fe lo, hi, r2;
+  for (int i = 0; i < 4; i++) lo.w[i] = splitmix_next(state);
+  for (int i = 0; i < 4; i++) hi.w[i] = splitmix_next(state);
+  memcpy(&r2, FR.r2, 32);
+  fe_mul(&FR, &lo, &lo, &r2);      /* lo * 2^256 */
+  fe_mul(&FR, &hi, &hi, &r2);      /* hi * 2^256 */
+  fe_mul(&FR, &hi, &hi, &r2);      /* hi * 2^512 = Montgomery form of hi * 2^256 */
+  fe_add(&FR, out, &lo, &hi);
+}
+
+void oracle_g1_add(const jac* a, const jac* b, jac* out) {
+  xyzz x, y;
+  xyzz_from_jac(&x, a);
+  xyzz_from_jac(&y, b);
+  xyzz_add(&x, &y);
+  jac_store_normalised(out, &x);
+}
+void oracle_g1_mul(const fe* scalar_mont, const jac* p, jac* out) {
+  fe s;
+  fe_from_mont(&FR, &s, scalar_mont);
+  xyzz base, acc;
+  xyzz_from_jac(&base, p);
+  xyzz_set_inf(&acc);
+  for (int i = 3; i >= 0; i--)
+    for (int b = 63; b >= 0; b--) {
+      xyzz_dbl(&acc, &acc);
+      if ((s.w[i] >> b) & 1) xyzz_add(&acc, &base);
+    }
+  jac_store_normalised(out, &acc);
+}
+int oracle_g1_eq(const jac* a, const jac* b) {
+  xyzz x, y;
+  jac na, nb;
+  xyzz_from_jac(&x, a);
+  xyzz_from_jac(&y, b);
+  jac_store_normalised(&na, &x);
+  jac_store_normalised(&nb, &y);
+  return memcmp(&na, &nb, sizeof(jac)) == 0;
+}
+void oracle_g1_generator(jac* out) {
+  fe one = {{1, 0, 0, 0}}, two = {{2, 0, 0, 0}};
+  fe_to_mont(&FP, &out->x, &one);
+  fe_to_mont(&FP, &out->y, &two);
+  memcpy(&out->z, FP.one, 32);
+}

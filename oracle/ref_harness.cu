@@ -1,0 +1,153 @@
+// Harness that drives the REFERENCE's own library (its unmodified src/*.cu, compiled against the
+// libff stand-in in oracle/ref_shim) so that its outputs can pin the oracle and this repository's
+// kernels, and so that its commitment kernel can be timed on the same GPU.
+// TEST INFRASTRUCTURE ONLY.  Built by oracle/Makefile into oracle/_ref/ (never committed).
+//
+//   ref_harness parity <in.bin> <out.bin>     commit / open / prove_matmul / tLookupRange on given data
+//   ref_harness commit-bench <rows> <steps>   times Hyrax::commit(int*) on int16-range rows of 4096
+//
+// Shapes are restricted to what the reference's kernels handle without reading out of bounds
+// (they have no guards): rows a multiple of 32, power-of-two sizes.
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <random>
+#include <vector>
+
+#include "Hyrax.cuh"
+#include "prove.cuh"
+#include "tlookup.cuh"
+
+template <class T>
+static void put(std::vector<unsigned char>& out, const T* p, size_t n) {
+  const unsigned char* b = reinterpret_cast<const unsigned char*>(p);
+  out.insert(out.end(), b, b + n * sizeof(T));
+}
+
+template <class T>
+static T* to_dev(const T* h, size_t n) {
+  T* d;
+  cudaMalloc(&d, n * sizeof(T));
+  cudaMemcpy(d, h, n * sizeof(T), cudaMemcpyHostToDevice);
+  return d;
+}
+
+static int parity(const char* in_path, const char* out_path) {
+  FILE* f = fopen(in_path, "rb");
+  if (!f) return 3;
+  uint32_t hdr[10];
+  if (fread(hdr, 4, 10, f) != 10) return 4;
+  const uint32_t n_gens = hdr[0], size = hdr[1], N = hdr[2], layer_num = hdr[3], L = hdr[4], Nn = hdr[5], M = hdr[6],
+                 K = hdr[7], lk_len = hdr[8], lk_D = hdr[9];
+  std::vector<int> tensor(size), A((size_t)L * Nn * K), B((size_t)L * M * K), Y((size_t)L * Nn * M), Q(lk_D);
+  if (fread(tensor.data(), 4, tensor.size(), f) != tensor.size() || fread(A.data(), 4, A.size(), f) != A.size() ||
+      fread(B.data(), 4, B.size(), f) != B.size() || fread(Y.data(), 4, Y.size(), f) != Y.size() ||
+      fread(Q.data(), 4, Q.size(), f) != Q.size())
+    return 5;
+  fclose(f);
+  std::vector<unsigned char> out;
+  ppT::init_public_params();
+  ref_shim_seed(99);
+  // test/ppgen.cu: generators and the 256-row table
+  affine_t* points;
+  cudaMalloc(&points, sizeof(affine_t) * (size_t)n_gens * 256);
+  std::vector<bn128> cpu_points = precompute_generators(n_gens, 256, points);
+  cudaDeviceSynchronize();
+  put(out, cpu_points.data(), cpu_points.size());
+  // test/HyraxTest.cu
+  int* d_tensor = to_dev(tensor.data(), tensor.size());
+  Hyrax hyrax(layer_num, n_gens / 16, points, cpu_points[0]);
+  FrTensor fr_tensor(size, d_tensor);
+  jacob_t* c0 = hyrax.commit(d_tensor, size, N);
+  jacob_t* c1 = hyrax.commit(fr_tensor, size, N);
+  const uint rows = size / (N * 16);
+  std::vector<jacob_t> h0(rows), h1(rows);
+  cudaMemcpy(h0.data(), c0, rows * sizeof(jacob_t), cudaMemcpyDeviceToHost);
+  cudaMemcpy(h1.data(), c1, rows * sizeof(jacob_t), cudaMemcpyDeviceToHost);
+  put(out, h0.data(), rows);
+  put(out, h1.data(), rows);
+  std::vector<Fr> eval_point = random_vec(Log2(size));
+  Fr cc = Fr::random_element();
+  Hyrax_proof proof = hyrax.open(fr_tensor, eval_point, cc, size, N);
+  put(out, &proof.result, 1);
+  put(out, proof.z, proof.z_size);
+  put(out, &proof.commit_d, 1);
+  put(out, &proof.commit_ad, 1);
+  // test/matmul.cu
+  int* dA = to_dev(A.data(), A.size());
+  int* dB = to_dev(B.data(), B.size());
+  int* dY = to_dev(Y.data(), Y.size());
+  FrTensor x(A.size(), dA), w(B.size(), dB), y(Y.size(), dY);
+  std::vector<Fr> u = random_vec(Log2(Y.size())), v = random_vec(Log2(K * L));
+  Fr claim = y(u);
+  Fr claim0 = claim;
+  auto pr = prove_matmul(x, w, L, Nn, M, K, u, v, claim);
+  put(out, &claim0, 1);
+  put(out, &pr.first, 1);
+  put(out, &pr.second, 1);
+  put(out, &claim, 1);
+  // test/tlookupTest.cu
+  int* dQ = to_dev(Q.data(), Q.size());
+  tLookupRange rs(-(int)(lk_len / 2), lk_len);
+  FrTensor x_tensor(lk_D, dQ), lookup_A(lk_D);
+  std::vector<Fr> lv = random_vec(Log2(lk_D));
+  double com_time = 0.0;
+  Fr value = rs.prove(x_tensor, lookup_A, lv, hyrax, n_gens / 16, com_time);
+  put(out, &value, 1);
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    fprintf(stderr, "CUDA error: %s\n", cudaGetErrorString(e));
+    return 6;
+  }
+  f = fopen(out_path, "wb");
+  fwrite(out.data(), 1, out.size(), f);
+  fclose(f);
+  return 0;
+}
+
+static int commit_bench(uint32_t rows, int steps) {
+  const uint32_t wd = 4096, n_gens = 4096;
+  ppT::init_public_params();
+  ref_shim_seed(0xC4);
+  affine_t* points;
+  cudaMalloc(&points, sizeof(affine_t) * (size_t)n_gens * 256);
+  auto t0 = std::chrono::high_resolution_clock::now();
+  std::vector<bn128> cpu_points = precompute_generators(n_gens, 256, points);
+  cudaDeviceSynchronize();
+  double table_s = std::chrono::duration<double>(std::chrono::high_resolution_clock::now() - t0).count();
+  std::mt19937 rng(7);
+  std::normal_distribution<float> dist(0.f, 0.02f * 65536.f);
+  std::vector<int> h((size_t)rows * wd);
+  for (auto& x : h) {
+    float v = std::round(dist(rng));
+    x = (int)std::min(32767.f, std::max(-32768.f, v));
+  }
+  int* d = to_dev(h.data(), h.size());
+  Hyrax hyrax(1, n_gens / 16, points, cpu_points[0]);
+  jacob_t* c = hyrax.commit(d, rows * wd, wd / 16);  // warm-up
+  cudaFree(c);
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0);
+  cudaEventCreate(&e1);
+  cudaEventRecord(e0);
+  for (int s = 0; s < steps; s++) {
+    c = hyrax.commit(d, rows * wd, wd / 16);
+    cudaFree(c);
+  }
+  cudaEventRecord(e1);
+  cudaEventSynchronize(e1);
+  float ms = 0;
+  cudaEventElapsedTime(&ms, e0, e1);
+  cudaError_t e = cudaGetLastError();
+  printf("{\"rows\": %u, \"row_len\": %u, \"steps\": %d, \"ms_per_step\": %.4f, \"points_per_s\": %.1f, "
+         "\"table_build_s\": %.3f, \"cuda_status\": \"%s\"}\n",
+         rows, wd, steps, ms / steps, (double)rows * wd * steps / (ms * 1e-3), table_s, cudaGetErrorString(e));
+  return e == cudaSuccess ? 0 : 6;
+}
+
+int main(int argc, char** argv) {
+  if (argc >= 4 && std::string(argv[1]) == "parity") return parity(argv[2], argv[3]);
+  if (argc >= 4 && std::string(argv[1]) == "commit-bench") return commit_bench(atoi(argv[2]), atoi(argv[3]));
+  fprintf(stderr, "usage: ref_harness parity <in> <out> | commit-bench <rows> <steps>\n");
+  return 2;
+}
