@@ -152,11 +152,50 @@ def cpu_baseline(gens: np.ndarray, scalars: np.ndarray, target_seconds: float, c
                        "fixed-base 8-bit-window table as in the reference"}, rows, rec)
 
 
+REF_HARNESS = ROOT / "oracle" / "_ref" / "ref_harness"
+
+
+def reference_cuda(rows: int, steps: int):
+    """The reference's own commit kernels (its unmodified src/*.cu built into oracle/_ref by
+    `make -C oracle ref`), timed on this GPU by oracle/ref_harness.cu.  None when that build is absent."""
+    if not REF_HARNESS.exists():
+        return None
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    try:
+        res = subprocess.run([str(REF_HARNESS), "commit-bench", str(rows), str(steps)], capture_output=True,
+                             text=True, env=env, timeout=600)
+    except (OSError, subprocess.TimeoutExpired) as e:
+        return {"unavailable": str(e)}
+    for ln in reversed(res.stdout.strip().splitlines()):
+        if ln.startswith("{"):
+            d = json.loads(ln)
+            d["what"] = ("reference CUDA (fixed-base 8-bit windows, one warp per row), unmodified sources, "
+                         "libff replaced by a stand-in; same rows x 4096 int16-range workload")
+            return d
+    return {"unavailable": (res.stderr or res.stdout)[-300:]}
+
+
 def run_reference(args):
     """The reference's algorithm on the host cores (C restatement; the reference's own code for this
     path is CUDA and needs libsnark, which is not vendored, so it cannot be built)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
+        return
+    ref = reference_cuda(workload_config()["rows_per_step"], max(args.steps, 1))
+    if ref and "points_per_s" in ref and ref.get("cuda_status") == "no error":
+        cfg = workload_config()
+        line = {"impl": "reference", "metric": METRIC, "value": ref["points_per_s"], "unit": UNIT, "n_gpus": 1,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ref["ms_per_step"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "u32 limbs (254-bit fields)", "data": "synthetic", "config": cfg,
+                "cpu_baseline": {"value": ref["points_per_s"], "unit": UNIT, "cores": 1, "kind": "reference",
+                                 "sample": "whole layer (49 408 rows); the reference's implementation of this path is "
+                                           "CUDA, so its own kernels run on GPU 0 driven by one host thread"},
+                "e2e": {"value": ref["e2e_points_per_s"], "unit": UNIT, "h2d_bytes_per_step": 0,
+                        "d2h_bytes_per_step": 0, "ms_per_step": ref["e2e_ms_per_step"],
+                        "note": "the reference's own data movement (cudaMemcpy from pageable memory) is inside"},
+                "gpu_launches": 0, "reference_build": ref["what"]}
+        print(json.dumps(line))
         return
     from oracle import bn254, cport
     from grape_b200 import workloads as wl  # shapes only; the arithmetic below is the oracle's
@@ -372,6 +411,8 @@ def run_own(args):
             "gpu_launches": int(launches), "roofline": roofline, "device_status": status,
             "table_bytes": table.nbytes}
 
+    if wd == WD and not args.rows:
+        line["reference_cuda"] = reference_cuda(rows, 2)
     if args.proof_layers:
         line["layer_proof"] = layer_proof(ctx, args.proof_layers, args.proof_window_bits, args.proof_scope)
     if not args.no_cpu_baseline and wd == WD:

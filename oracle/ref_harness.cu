@@ -138,10 +138,25 @@ static int commit_bench(uint32_t rows, int steps) {
   cudaEventSynchronize(e1);
   float ms = 0;
   cudaEventElapsedTime(&ms, e0, e1);
+  // the same with the reference's own data movement around it: pageable host tensor -> device
+  // (load_data, src/ioutils.cu:105-124), commit, commitments back to the host (savebin, :3-40)
+  std::vector<jacob_t> h_out(rows);
+  cudaEventRecord(e0);
+  for (int s = 0; s < steps; s++) {
+    cudaMemcpy(d, h.data(), h.size() * sizeof(int), cudaMemcpyHostToDevice);
+    c = hyrax.commit(d, rows * wd, wd / 16);
+    cudaMemcpy(h_out.data(), c, rows * sizeof(jacob_t), cudaMemcpyDeviceToHost);
+    cudaFree(c);
+  }
+  cudaEventRecord(e1);
+  cudaEventSynchronize(e1);
+  float ms_e2e = 0;
+  cudaEventElapsedTime(&ms_e2e, e0, e1);
   cudaError_t e = cudaGetLastError();
   printf("{\"rows\": %u, \"row_len\": %u, \"steps\": %d, \"ms_per_step\": %.4f, \"points_per_s\": %.1f, "
-         "\"table_build_s\": %.3f, \"cuda_status\": \"%s\"}\n",
-         rows, wd, steps, ms / steps, (double)rows * wd * steps / (ms * 1e-3), table_s, cudaGetErrorString(e));
+         "\"e2e_ms_per_step\": %.4f, \"e2e_points_per_s\": %.1f, \"table_build_s\": %.3f, \"cuda_status\": \"%s\"}\n",
+         rows, wd, steps, ms / steps, (double)rows * wd * steps / (ms * 1e-3), ms_e2e / steps,
+         (double)rows * wd * steps / (ms_e2e * 1e-3), table_s, cudaGetErrorString(e));
   return e == cudaSuccess ? 0 : 6;
 }
 
