@@ -44,6 +44,16 @@ static int parity(const char* in_path, const char* out_path) {
       fread(B.data(), 4, B.size(), f) != B.size() || fread(Y.data(), 4, Y.size(), f) != Y.size() ||
       fread(Q.data(), 4, Q.size(), f) != Q.size())
     return 5;
+  // second part: Hadamard product, claim batching, mapping lookup
+  uint32_t hdr2[6];
+  if (fread(hdr2, 4, 6, f) != 6) return 4;
+  const uint32_t eL = hdr2[0], eM = hdr2[1], eN = hdr2[2], map_len = hdr2[3], map_D = hdr2[4];
+  const int map_low = (int)hdr2[5];
+  const size_t esize = (size_t)eL * eM * eN;
+  std::vector<int> EA(esize), EB(esize), MIN(map_D), MOUT(map_D);
+  if (fread(EA.data(), 4, esize, f) != esize || fread(EB.data(), 4, esize, f) != esize ||
+      fread(MIN.data(), 4, map_D, f) != map_D || fread(MOUT.data(), 4, map_D, f) != map_D)
+    return 5;
   fclose(f);
   std::vector<unsigned char> out;
   ppT::init_public_params();
@@ -94,6 +104,43 @@ static int parity(const char* in_path, const char* out_path) {
   double com_time = 0.0;
   Fr value = rs.prove(x_tensor, lookup_A, lv, hyrax, n_gens / 16, com_time);
   put(out, &value, 1);
+  // prove_eleMul (test/eleWiseMul.cu flow): claim = (A.B)~(u)
+  {
+    int* dEA = to_dev(EA.data(), esize);
+    int* dEB = to_dev(EB.data(), esize);
+    FrTensor ea(esize, dEA), eb(esize, dEB);
+    FrTensor prod(ea);
+    prod *= eb;
+    std::vector<Fr> eu = random_vec(Log2(esize)), ev = random_vec(Log2(esize));
+    Fr ecl = prod(eu);
+    Fr ecl0 = ecl;
+    auto ep = prove_eleMul(ea, eb, eL, eM, eN, eu, ev, ecl);
+    put(out, &ecl0, 1);
+    put(out, &ep.first, 1);
+    put(out, &ep.second, 1);
+    // combine_claims (test/combine_value.cu flow) on the first factor, two points
+    FrTensor X(esize, dEA);
+    std::vector<Fr> u1 = random_vec(Log2(esize)), u2 = random_vec(Log2(esize)), cv = random_vec(Log2(esize));
+    FrTensor t1(X), t2(X);
+    Fr c1 = t1(u1), c2 = t2(u2);
+    Fr comb = combine_claims(X, {c1, c2}, {u1, u2}, cv, esize);
+    put(out, &c1, 1);
+    put(out, &c2, 1);
+    put(out, &comb, 1);
+  }
+  // tLookupRangeMapping (test/tlookupMapTest.cu flow); the table file was written by the caller
+  {
+    std::string table_path = std::string(in_path) + ".table";
+    tLookupRangeMapping mp(map_low, map_len, table_path);
+    int* dIN = to_dev(MIN.data(), map_D);
+    int* dOUT = to_dev(MOUT.data(), map_D);
+    FrTensor s_in(map_D, dIN), s_out(map_D, dOUT), mA(map_D);
+    std::vector<Fr> mv = random_vec(Log2(map_D));
+    double com_time = 0.0;
+    Fr mval = mp.prove(s_in, s_out, mA, mv, hyrax, n_gens / 16, com_time);
+    put(out, &mp.r, 1);
+    put(out, &mval, 1);
+  }
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) {
     fprintf(stderr, "CUDA error: %s\n", cudaGetErrorString(e));

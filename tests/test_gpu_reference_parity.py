@@ -2,8 +2,8 @@
 
 ``oracle/_ref/ref_harness`` is the reference's unmodified src/*.cu linked with a libff stand-in
 (oracle/ref_shim) and built by ``make -C oracle ref`` where the reference tree is available.  The
-harness runs the reference's commit (int and Fr), open, prove_matmul and tLookupRange::prove on a
-blob of inputs with a seeded random stream; here the same inputs and the same stream go through
+harness runs the reference's commit (int and Fr), open, prove_matmul, prove_eleMul, combine_claims,
+tLookupRange::prove and tLookupRangeMapping::prove on a blob of inputs with a seeded random stream; here the same inputs and the same stream go through
 the oracle and through libgrape_b200, and every value is compared.  Shapes respect what the
 reference's unguarded kernels can take (row counts that fill whole blocks, power-of-two sizes).
 """
@@ -42,10 +42,22 @@ def test_reference_outputs_equal_oracle_and_library(gctx, tmp_path):
     B = rng.integers(-2**12, 2**12, size=L * M * K).astype(np.int32)
     Y = (A.reshape(L, Nn, K).astype(np.int64) @ B.reshape(L, M, K).astype(np.int64).transpose(0, 2, 1)).astype(np.int32)
     Q = rng.integers(-(lk_len // 2), lk_len // 2, size=lk_D).astype(np.int32)
+    eL, eM, eN = 2, 4, 8
+    esize = eL * eM * eN
+    EA = rng.integers(-2**20, 2**20, size=esize).astype(np.int32)
+    EB = rng.integers(-2**20, 2**20, size=esize).astype(np.int32)
+    map_len, map_D, map_low = 4096, 16384, -2048
+    map_table = rng.integers(-2**16, 2**16, size=map_len).astype(np.int32)
+    MIN = rng.integers(map_low, map_low + map_len, size=map_D).astype(np.int32)
+    MOUT = map_table[MIN - map_low]
     blob, out = tmp_path / "in.bin", tmp_path / "out.bin"
+    map_table.tofile(str(blob) + ".table")
     with open(blob, "wb") as f:
         f.write(np.array([n_gens, size, N, layer_num, L, Nn, M, K, lk_len, lk_D], dtype=np.uint32).tobytes())
         for arr in (tensor, A, B, Y, Q):
+            f.write(arr.tobytes())
+        f.write(np.array([eL, eM, eN, map_len, map_D, map_low & 0xFFFFFFFF], dtype=np.uint32).tobytes())
+        for arr in (EA, EB, MIN, MOUT):
             f.write(arr.tobytes())
     env = dict(os.environ, OMP_NUM_THREADS="1")   # the reference draws the blinding vector in an OpenMP loop
     res = subprocess.run([str(HARNESS), "parity", str(blob), str(out)], capture_output=True, text=True, env=env,
@@ -70,6 +82,9 @@ def test_reference_outputs_equal_oracle_and_library(gctx, tmp_path):
     ref_com_d, ref_com_ad = bn254.jacobian_from_bytes(take(96)), bn254.jacobian_from_bytes(take(96))
     ref_claim0, ref_a, ref_b, ref_final = take(32), take(32), take(32), take(32)
     ref_lookup = take(32)
+    ref_ecl0, ref_ea, ref_eb = take(32), take(32), take(32)
+    ref_k1, ref_k2, ref_comb = take(32), take(32), take(32)
+    ref_map_r, ref_map_val = take(32), take(32)
     assert pos == len(raw)
 
     # ---- the oracle, same stream
@@ -96,6 +111,20 @@ def test_reference_outputs_equal_oracle_and_library(gctx, tmp_path):
     lu = draw.fr_vec(pr.log2ceil(lk_D))
     got = lk.prove([int(x) % R for x in Q], lv, lu)
     assert ref_lookup == bn254.fr_to_bytes(got["claim"])
+    fa, fb = [int(x) % R for x in EA], [int(x) % R for x in EB]
+    eu, ev = draw.fr_vec(6), draw.fr_vec(6)
+    ecl = _mle([x * y % R for x, y in zip(fa, fb)], eu)
+    o_ea, o_eb, _, _ = pr.prove_elemul(fa, fb, eL, eM, eN, eu, ev, ecl)
+    assert (ref_ecl0, ref_ea, ref_eb) == tuple(bn254.fr_to_bytes(x) for x in (ecl, o_ea, o_eb))
+    u1, u2, cv = draw.fr_vec(6), draw.fr_vec(6), draw.fr_vec(6)
+    k1, k2 = _mle(fa, u1), _mle(fa, u2)
+    o_comb, _ = pr.combine_claims(fa, [k1, k2], [u1, u2], cv, esize)
+    assert (ref_k1, ref_k2, ref_comb) == tuple(bn254.fr_to_bytes(x) for x in (k1, k2, o_comb))
+    omap = pr.LookupRangeMapping(map_low, map_len, [int(x) for x in map_table], draw.next_fr(), draw.next_fr())
+    mv = draw.fr_vec(pr.log2ceil(map_D))
+    mu = draw.fr_vec(pr.log2ceil(map_D))
+    o_map = omap.prove_pairs([int(x) % R for x in MIN], [int(x) % R for x in MOUT], mv, mu)
+    assert ref_map_r == bn254.fr_to_bytes(omap.r) and ref_map_val == bn254.fr_to_bytes(o_map["claim"])
 
     # ---- this library, same stream
     gens_j = wl.make_generators(gctx, n_gens, seed=99)
@@ -126,4 +155,18 @@ def test_reference_outputs_equal_oracle_and_library(gctx, tmp_path):
     value, _ = lkm.prove(dS, lk_D, gctx.alloc(lk_D * 32), lv2, table=table, msm_size=n_gens // 16)
     assert bn254.fr_to_bytes(value) == ref_lookup
     lkm.close()
+    eu2, ev2 = host.decode_field(gctx.random_fr(6)), host.decode_field(gctx.random_fr(6))
+    m_ea, m_eb, _, _ = host.prove_elemul(gctx, gctx.fr_upload(fa), gctx.fr_upload(fb), eL, eM, eN, eu2, ev2, ecl)
+    assert (bn254.fr_to_bytes(m_ea), bn254.fr_to_bytes(m_eb)) == (ref_ea, ref_eb)
+    us2 = [host.decode_field(gctx.random_fr(6)) for _ in range(2)]
+    cv2 = host.decode_field(gctx.random_fr(6))
+    m_comb, _ = host.combine_claims(gctx, gctx.fr_upload(fa), esize, [k1, k2], us2, cv2)
+    assert bn254.fr_to_bytes(m_comb) == ref_comb
+    mmap = host.Lookup(gctx, map_low, map_len, map_table)
+    assert bn254.fr_to_bytes(mmap.r) == ref_map_r
+    mv2 = host.decode_field(gctx.random_fr(len(mv)))
+    m_val, _ = mmap.prove_pairs(gctx.fr_upload([int(x) for x in MIN]), gctx.fr_upload([int(x) for x in MOUT]), map_D,
+                                gctx.alloc(map_D * 32), gctx.alloc(map_D * 32), mv2, table=table, msm_size=n_gens // 16)
+    assert bn254.fr_to_bytes(m_val) == ref_map_val
+    mmap.close()
     table.close()
