@@ -76,6 +76,11 @@ def _declare(lib):
     f("grape_host_alloc_pinned", [vp, sz, C.POINTER(vp)])
     f("grape_host_free_pinned", [vp, vp])
     f("grape_table_create", [vp, vp, u32, u32, u32, C.POINTER(vp)])
+    f("grape_bls12_381_table_create", [vp, vp, u32, u32, u32, C.POINTER(vp)])
+    f("grape_table_curve", [vp], u32)
+    f("grape_bls12_381_field_binary", [vp, C.c_int, C.c_int, vp, vp, vp, u64])
+    f("grape_bls12_381_fr_from_i32", [vp, vp, vp, u64])
+    f("grape_bls12_381_measure_mul_peak", [vp, C.POINTER(C.c_double)])
     f("grape_table_from_reference", [vp, vp, u32, C.POINTER(vp)])
     f("grape_table_destroy", [vp])
     f("grape_table_bytes", [vp], u64)

@@ -1,0 +1,115 @@
+// BLS12-381 instantiation: field test hooks and a multiplication-rate measurement.
+//
+// The commitment kernels themselves are the curve-generic ones in msm.cu (grape_bls12_381_table_create
+// builds the table; grape_commit_i32 / grape_commit_fr dispatch on the table's curve).  The reference
+// lists this curve's constants (include/field/bls12-381.cuh:7-46) but compiles nothing against them,
+// so these entry points have no reference call site; they exist because the commitment is specified
+// over this curve as well.
+#include "ctx.cuh"
+#include "curve.cuh"
+
+namespace grape {
+
+constexpr int BLS_THREADS = 256;
+
+template <int OP, class F>
+__global__ void k_bls_binary(const uint32_t* a, const uint32_t* b, uint32_t* out, uint64_t n) {
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+    F x = F::load(a + i * F::N), y = F::load(b + i * F::N);
+    F r = OP == 0 ? fe_add(x, y) : OP == 1 ? fe_sub(x, y) : fe_mul(x, y);
+    r.store(out + i * F::N);
+  }
+}
+
+__global__ void k_bls_from_i32(const int32_t* __restrict__ in, uint32_t* __restrict__ out, uint64_t n) {
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
+    fe_from_i32<BlsFrParams>(__ldg(in + i)).store(out + i * 8);
+}
+
+// Two dependent chains of base-field multiplications per thread, operands in registers.
+constexpr int BLS_PEAK_ITERS = 2048;
+__global__ void __launch_bounds__(256) k_bls_mul_peak(uint32_t* sink, uint32_t seed) {
+  uint32_t a = threadIdx.x * 2654435761u + seed, b = blockIdx.x * 40503u + 12345u;
+  BlsFp x[2], y;
+#pragma unroll
+  for (int i = 0; i < 12; i++) { x[0].v[i] = a + i; x[1].v[i] = b + i; y.v[i] = (a ^ b) + i; }
+  x[0].v[11] &= 0x0fffffffu; x[1].v[11] &= 0x0fffffffu; y.v[11] &= 0x0fffffffu;
+  for (int it = 0; it < BLS_PEAK_ITERS; it++) {
+    x[0] = fe_mul(x[0], y);
+    x[1] = fe_mul(x[1], y);
+  }
+  if (x[0].v[0] == 0x12345 && x[1].v[3] == 7) sink[0] = x[0].v[1];
+}
+
+static inline uint32_t bls_blocks(const grape_ctx* ctx, uint64_t n) {
+  uint64_t b = (n + BLS_THREADS - 1) / BLS_THREADS;
+  uint64_t cap = (uint64_t)ctx->sm_count * 16;
+  if (b > cap) b = cap;
+  return (uint32_t)(b ? b : 1);
+}
+
+}  // namespace grape
+
+using namespace grape;
+
+extern "C" int grape_bls12_381_field_binary(grape_ctx* ctx, int field, int op, const void* d_a, const void* d_b,
+                                            void* d_out, uint64_t n) {
+  if (!ctx) return GRAPE_ERR_INVALID;
+  if (field < 0 || field > 1 || op < 0 || op > 2)
+    return fail(ctx, GRAPE_ERR_INVALID, "field must be 0 (Fr) or 1 (Fp), op 0 (add), 1 (sub) or 2 (mul)");
+  if (n == 0) return GRAPE_OK;
+  const uint32_t* a = reinterpret_cast<const uint32_t*>(d_a);
+  const uint32_t* b = reinterpret_cast<const uint32_t*>(d_b);
+  uint32_t* o = reinterpret_cast<uint32_t*>(d_out);
+  uint32_t g = bls_blocks(ctx, n);
+  cudaStream_t s = ctx->stream;
+  if (field == 0) {
+    if (op == 0) k_bls_binary<0, BlsFr><<<g, BLS_THREADS, 0, s>>>(a, b, o, n);
+    else if (op == 1) k_bls_binary<1, BlsFr><<<g, BLS_THREADS, 0, s>>>(a, b, o, n);
+    else k_bls_binary<2, BlsFr><<<g, BLS_THREADS, 0, s>>>(a, b, o, n);
+  } else {
+    if (op == 0) k_bls_binary<0, BlsFp><<<g, BLS_THREADS, 0, s>>>(a, b, o, n);
+    else if (op == 1) k_bls_binary<1, BlsFp><<<g, BLS_THREADS, 0, s>>>(a, b, o, n);
+    else k_bls_binary<2, BlsFp><<<g, BLS_THREADS, 0, s>>>(a, b, o, n);
+  }
+  ctx->launches += 1;
+  GRAPE_CUDA_TRY(ctx, cudaGetLastError());
+  return GRAPE_OK;
+}
+
+extern "C" int grape_bls12_381_fr_from_i32(grape_ctx* ctx, const int32_t* d_in, void* d_out, uint64_t n) {
+  if (!ctx) return GRAPE_ERR_INVALID;
+  if (n == 0) return GRAPE_OK;
+  k_bls_from_i32<<<bls_blocks(ctx, n), BLS_THREADS, 0, ctx->stream>>>(d_in, reinterpret_cast<uint32_t*>(d_out), n);
+  ctx->launches += 1;
+  GRAPE_CUDA_TRY(ctx, cudaGetLastError());
+  return GRAPE_OK;
+}
+
+extern "C" int grape_bls12_381_measure_mul_peak(grape_ctx* ctx, double* muls_per_second) {
+  if (!ctx || !muls_per_second) return GRAPE_ERR_INVALID;
+  arena_reset(ctx);
+  uint32_t* sink = nullptr;
+  int rc = arena_alloc_t(ctx, 64, &sink);
+  if (rc) return rc;
+  const int blocks = ctx->sm_count * 8, threads = 256;
+  cudaEvent_t e0, e1;
+  GRAPE_CUDA_TRY(ctx, cudaEventCreate(&e0));
+  GRAPE_CUDA_TRY(ctx, cudaEventCreate(&e1));
+  float best = 1e30f;
+  for (int rep = 0; rep < 4; rep++) {
+    cudaEventRecord(e0, ctx->stream);
+    k_bls_mul_peak<<<blocks, threads, 0, ctx->stream>>>(sink, rep + 1);
+    cudaEventRecord(e1, ctx->stream);
+    ctx->launches += 1;
+    GRAPE_CUDA_TRY(ctx, cudaEventSynchronize(e1));
+    float ms = 0;
+    cudaEventElapsedTime(&ms, e0, e1);
+    if (rep > 0 && ms < best) best = ms;
+  }
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  GRAPE_CUDA_TRY(ctx, cudaGetLastError());
+  *muls_per_second = 2.0 * BLS_PEAK_ITERS * blocks * threads / (best * 1e-3);
+  return GRAPE_OK;
+}

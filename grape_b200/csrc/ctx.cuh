@@ -48,6 +48,7 @@ struct grape_table {
   uint32_t n_digits = 128;      // addressable magnitudes per window: 1..n_digits
   uint64_t window_stride = 0;   // records between consecutive windows
   uint32_t first_digit_row = 0; // row holding magnitude 1 (1 for the reference's 256-row layout)
+  uint32_t curve = 0;           // GRAPE_CURVE_BN254 or GRAPE_CURVE_BLS12_381
 };
 
 namespace grape {

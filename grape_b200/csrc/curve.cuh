@@ -1,6 +1,8 @@
-// BN254 G1 (y^2 = x^3 + 3) point arithmetic for the commitment kernels.
+// Short-Weierstrass G1 point arithmetic (a = 0: BN254 y^2 = x^3 + 3, BLS12-381 y^2 = x^3 + 4; the
+// formulas never use b) for the commitment kernels, generic over the coordinate field F.
 //
-// Record layouts follow the reference so buffers are interchangeable with it:
+// Record layouts follow the reference so buffers are interchangeable with it (sizes for BN254, whose
+// coordinates are 32 B; BLS12-381 coordinates are 48 B and every record grows by 3/2):
 //   affine   64 B  X|Y, Montgomery form, (0,0) is the point at infinity  (include/curve/affine_t.cuh:17-75)
 //   jacobian 96 B  X|Y|Z, Z = 0 is infinity                              (include/curve/jacobian_t.cuh:10-60)
 //   xyzz    128 B  X|Y|ZZZ|ZZ with x = X/ZZ, y = Y/ZZZ, ZZ = 0 is infinity (include/curve/xyzz_t.cuh:16-40)
@@ -12,80 +14,85 @@
 
 namespace grape {
 
-struct __align__(16) Affine {
-  Fp x, y;
+template <class F>
+struct __align__(16) AffineT {
+  F x, y;
   __device__ __forceinline__ bool is_inf() const { return x.is_zero() && y.is_zero(); }
-  __device__ __forceinline__ static Affine inf() { return Affine{Fp::zero(), Fp::zero()}; }
-  __device__ __forceinline__ static Affine load_nc(const void* p) {
+  __device__ __forceinline__ static AffineT<F> inf() { return AffineT<F>{F::zero(), F::zero()}; }
+  __device__ __forceinline__ static AffineT<F> load_nc(const void* p) {
     const char* c = reinterpret_cast<const char*>(p);
-    return Affine{Fp::load_nc(c), Fp::load_nc(c + 32)};
+    return AffineT<F>{F::load_nc(c), F::load_nc(c + F::BYTES)};
   }
-  __device__ __forceinline__ static Affine load(const void* p) {
+  __device__ __forceinline__ static AffineT<F> load(const void* p) {
     const char* c = reinterpret_cast<const char*>(p);
-    return Affine{Fp::load(c), Fp::load(c + 32)};
+    return AffineT<F>{F::load(c), F::load(c + F::BYTES)};
   }
   __device__ __forceinline__ void store(void* p) const {
     char* c = reinterpret_cast<char*>(p);
     x.store(c);
-    y.store(c + 32);
+    y.store(c + F::BYTES);
   }
 };
 
-struct __align__(16) Jacobian {
-  Fp x, y, z;
+template <class F>
+struct __align__(16) JacobianT {
+  F x, y, z;
 };
 
-struct __align__(16) Xyzz {
-  Fp x, y, zzz, zz;
+template <class F>
+struct __align__(16) XyzzT {
+  F x, y, zzz, zz;
 
-  __device__ __forceinline__ static Xyzz inf() {
-    return Xyzz{Fp::zero(), Fp::zero(), Fp::zero(), Fp::zero()};
+  __device__ __forceinline__ static XyzzT<F> inf() {
+    return XyzzT<F>{F::zero(), F::zero(), F::zero(), F::zero()};
   }
   __device__ __forceinline__ bool is_inf() const { return zz.is_zero(); }
-  __device__ __forceinline__ static Xyzz from_affine(const Affine& p) {
+  __device__ __forceinline__ static XyzzT<F> from_affine(const AffineT<F>& p) {
     if (p.is_inf()) return inf();
-    return Xyzz{p.x, p.y, Fp::one(), Fp::one()};
+    return XyzzT<F>{p.x, p.y, F::one(), F::one()};
   }
-  __device__ __forceinline__ static Xyzz load(const void* p) {
+  __device__ __forceinline__ static XyzzT<F> load(const void* p) {
     const char* c = reinterpret_cast<const char*>(p);
-    return Xyzz{Fp::load(c), Fp::load(c + 32), Fp::load(c + 64), Fp::load(c + 96)};
+    return XyzzT<F>{F::load(c), F::load(c + F::BYTES), F::load(c + 2 * F::BYTES), F::load(c + 3 * F::BYTES)};
   }
   __device__ __forceinline__ void store(void* p) const {
     char* c = reinterpret_cast<char*>(p);
     x.store(c);
-    y.store(c + 32);
-    zzz.store(c + 64);
-    zz.store(c + 96);
+    y.store(c + F::BYTES);
+    zzz.store(c + 2 * F::BYTES);
+    zz.store(c + 3 * F::BYTES);
   }
 };
 
 // 2 * (affine point), affine point finite.
-__device__ __forceinline__ Xyzz xyzz_dbl_affine(const Affine& p) {
-  Fp U = fe_dbl(p.y);
-  Fp V = fe_sqr(U);
-  Fp W = fe_mul(U, V);
-  Fp S = fe_mul(p.x, V);
-  Fp X2 = fe_sqr(p.x);
-  Fp M = fe_add(fe_dbl(X2), X2);
-  Xyzz r;
+template <class F>
+__device__ __forceinline__ XyzzT<F> xyzz_dbl_affine(const AffineT<F>& p) {
+  F U = fe_dbl(p.y);
+  F V = fe_sqr(U);
+  F W = fe_mul(U, V);
+  F S = fe_mul(p.x, V);
+  F X2 = fe_sqr(p.x);
+  F M = fe_add(fe_dbl(X2), X2);
+  XyzzT<F> r;
   r.x = fe_sub(fe_sqr(M), fe_dbl(S));
   r.y = fe_sub(fe_mul(M, fe_sub(S, r.x)), fe_mul(W, p.y));
   r.zz = V;
   r.zzz = W;
-  if (p.y.is_zero()) return Xyzz::inf();  // order-2 point (none on this curve, kept for safety)
+  if (p.y.is_zero()) return XyzzT<F>::inf();  // order-2 point (none on this curve, kept for safety)
   return r;
 }
 
 // 2 * P
-__device__ __forceinline__ Xyzz xyzz_dbl(const Xyzz& p) {
+template <class F>
+__device__ __forceinline__ XyzzT<F> xyzz_dbl(const XyzzT<F>& p) {
   if (p.is_inf()) return p;
-  Fp U = fe_dbl(p.y);
-  Fp V = fe_sqr(U);
-  Fp W = fe_mul(U, V);
-  Fp S = fe_mul(p.x, V);
-  Fp X2 = fe_sqr(p.x);
-  Fp M = fe_add(fe_dbl(X2), X2);
-  Xyzz r;
+  F U = fe_dbl(p.y);
+  F V = fe_sqr(U);
+  F W = fe_mul(U, V);
+  F S = fe_mul(p.x, V);
+  F X2 = fe_sqr(p.x);
+  F M = fe_add(fe_dbl(X2), X2);
+  XyzzT<F> r;
   r.x = fe_sub(fe_sqr(M), fe_dbl(S));
   r.y = fe_sub(fe_mul(M, fe_sub(S, r.x)), fe_mul(W, p.y));
   r.zz = fe_mul(V, p.zz);
@@ -94,26 +101,27 @@ __device__ __forceinline__ Xyzz xyzz_dbl(const Xyzz& p) {
 }
 
 // acc += q (q affine).  The rare cases branch; the common path is straight-line.
-__device__ __forceinline__ void xyzz_madd(Xyzz& acc, const Affine& q) {
+template <class F>
+__device__ __forceinline__ void xyzz_madd(XyzzT<F>& acc, const AffineT<F>& q) {
   if (q.is_inf()) return;
   if (acc.is_inf()) {
-    acc = Xyzz{q.x, q.y, Fp::one(), Fp::one()};
+    acc = XyzzT<F>{q.x, q.y, F::one(), F::one()};
     return;
   }
-  Fp U2 = fe_mul(q.x, acc.zz);
-  Fp S2 = fe_mul(q.y, acc.zzz);
-  Fp Pd = fe_sub(U2, acc.x);
-  Fp Rd = fe_sub(S2, acc.y);
+  F U2 = fe_mul(q.x, acc.zz);
+  F S2 = fe_mul(q.y, acc.zzz);
+  F Pd = fe_sub(U2, acc.x);
+  F Rd = fe_sub(S2, acc.y);
   if (Pd.is_zero()) {
     if (Rd.is_zero()) acc = xyzz_dbl_affine(q);
-    else acc = Xyzz::inf();
+    else acc = XyzzT<F>::inf();
     return;
   }
-  Fp PP = fe_sqr(Pd);
-  Fp PPP = fe_mul(Pd, PP);
-  Fp Q = fe_mul(acc.x, PP);
-  Fp X3 = fe_sub(fe_sub(fe_sqr(Rd), PPP), fe_dbl(Q));
-  Fp Y3 = fe_sub(fe_mul(Rd, fe_sub(Q, X3)), fe_mul(acc.y, PPP));
+  F PP = fe_sqr(Pd);
+  F PPP = fe_mul(Pd, PP);
+  F Q = fe_mul(acc.x, PP);
+  F X3 = fe_sub(fe_sub(fe_sqr(Rd), PPP), fe_dbl(Q));
+  F Y3 = fe_sub(fe_mul(Rd, fe_sub(Q, X3)), fe_mul(acc.y, PPP));
   acc.x = X3;
   acc.y = Y3;
   acc.zz = fe_mul(acc.zz, PP);
@@ -121,67 +129,94 @@ __device__ __forceinline__ void xyzz_madd(Xyzz& acc, const Affine& q) {
 }
 
 // acc += q (both XYZZ)
-__device__ __forceinline__ void xyzz_add(Xyzz& acc, const Xyzz& q) {
+template <class F>
+__device__ __forceinline__ void xyzz_add(XyzzT<F>& acc, const XyzzT<F>& q) {
   if (q.is_inf()) return;
   if (acc.is_inf()) {
     acc = q;
     return;
   }
-  Fp U1 = fe_mul(acc.x, q.zz);
-  Fp U2 = fe_mul(q.x, acc.zz);
-  Fp S1 = fe_mul(acc.y, q.zzz);
-  Fp S2 = fe_mul(q.y, acc.zzz);
-  Fp Pd = fe_sub(U2, U1);
-  Fp Rd = fe_sub(S2, S1);
+  F U1 = fe_mul(acc.x, q.zz);
+  F U2 = fe_mul(q.x, acc.zz);
+  F S1 = fe_mul(acc.y, q.zzz);
+  F S2 = fe_mul(q.y, acc.zzz);
+  F Pd = fe_sub(U2, U1);
+  F Rd = fe_sub(S2, S1);
   if (Pd.is_zero()) {
     if (Rd.is_zero()) acc = xyzz_dbl(acc);
-    else acc = Xyzz::inf();
+    else acc = XyzzT<F>::inf();
     return;
   }
-  Fp PP = fe_sqr(Pd);
-  Fp PPP = fe_mul(Pd, PP);
-  Fp Q = fe_mul(U1, PP);
-  Fp X3 = fe_sub(fe_sub(fe_sqr(Rd), PPP), fe_dbl(Q));
-  Fp Y3 = fe_sub(fe_mul(Rd, fe_sub(Q, X3)), fe_mul(S1, PPP));
+  F PP = fe_sqr(Pd);
+  F PPP = fe_mul(Pd, PP);
+  F Q = fe_mul(U1, PP);
+  F X3 = fe_sub(fe_sub(fe_sqr(Rd), PPP), fe_dbl(Q));
+  F Y3 = fe_sub(fe_mul(Rd, fe_sub(Q, X3)), fe_mul(S1, PPP));
   acc.x = X3;
   acc.y = Y3;
   acc.zz = fe_mul(fe_mul(acc.zz, q.zz), PP);
   acc.zzz = fe_mul(fe_mul(acc.zzz, q.zzz), PPP);
 }
 
-__device__ __forceinline__ Xyzz xyzz_shfl_down(const Xyzz& p, int delta) {
-  return Xyzz{fe_shfl_down(p.x, delta), fe_shfl_down(p.y, delta), fe_shfl_down(p.zzz, delta),
+template <class F>
+__device__ __forceinline__ XyzzT<F> xyzz_shfl_down(const XyzzT<F>& p, int delta) {
+  return XyzzT<F>{fe_shfl_down(p.x, delta), fe_shfl_down(p.y, delta), fe_shfl_down(p.zzz, delta),
               fe_shfl_down(p.zz, delta)};
 }
 
 // Jacobian (any Z) -> XYZZ:  ZZ = Z^2, ZZZ = Z^3.
-__device__ __forceinline__ Xyzz xyzz_from_jacobian(const Jacobian& j) {
-  if (j.z.is_zero()) return Xyzz::inf();
-  Fp zz = fe_sqr(j.z);
-  return Xyzz{j.x, j.y, fe_mul(zz, j.z), zz};
+template <class F>
+__device__ __forceinline__ XyzzT<F> xyzz_from_jacobian(const JacobianT<F>& j) {
+  if (j.z.is_zero()) return XyzzT<F>::inf();
+  F zz = fe_sqr(j.z);
+  return XyzzT<F>{j.x, j.y, fe_mul(zz, j.z), zz};
 }
 
 // XYZZ -> affine (one inversion).
-__device__ __forceinline__ Affine xyzz_to_affine(const Xyzz& p) {
-  if (p.is_inf()) return Affine::inf();
-  Fp t = fe_inv(fe_mul(p.zz, p.zzz));
-  Fp izz = fe_mul(t, p.zzz);
-  Fp izzz = fe_mul(t, p.zz);
-  return Affine{fe_mul(p.x, izz), fe_mul(p.y, izzz)};
+template <class F>
+__device__ __forceinline__ AffineT<F> xyzz_to_affine(const XyzzT<F>& p) {
+  if (p.is_inf()) return AffineT<F>::inf();
+  F t = fe_inv(fe_mul(p.zz, p.zzz));
+  F izz = fe_mul(t, p.zzz);
+  F izzz = fe_mul(t, p.zz);
+  return AffineT<F>{fe_mul(p.x, izz), fe_mul(p.y, izzz)};
 }
 
 // Canonical Jacobian record: (x, y, 1), or (1, 1, 0) for infinity.
-__device__ __forceinline__ void store_jacobian_normalised(void* out, const Affine& a, bool inf) {
+template <class F>
+__device__ __forceinline__ void store_jacobian_normalised(void* out, const AffineT<F>& a, bool inf) {
   char* c = reinterpret_cast<char*>(out);
   if (inf) {
-    Fp::one().store(c);
-    Fp::one().store(c + 32);
-    Fp::zero().store(c + 64);
+    F::one().store(c);
+    F::one().store(c + F::BYTES);
+    F::zero().store(c + 2 * F::BYTES);
   } else {
     a.x.store(c);
-    a.y.store(c + 32);
-    Fp::one().store(c + 64);
+    a.y.store(c + F::BYTES);
+    F::one().store(c + 2 * F::BYTES);
   }
 }
+
+// Curve descriptors for the kernels that are generic over the curve: coordinate field, scalar field,
+// identifier stored in a generator table, scalar width, and how many 128-thread blocks of the
+// accumulation kernel should share an SM (the 12-limb field needs about 3/2 of the registers).
+struct Bn254 {
+  using F = Fp;
+  using S = Fr;
+  static constexpr uint32_t ID = 0;
+  static constexpr uint32_t SCALAR_BITS = 254;
+  static constexpr int MSM_BLOCKS = 4;
+};
+struct Bls12381 {
+  using F = BlsFp;
+  using S = BlsFr;
+  static constexpr uint32_t ID = 1;
+  static constexpr uint32_t SCALAR_BITS = 255;
+  static constexpr int MSM_BLOCKS = 2;
+};
+
+using Affine = AffineT<Fp>;
+using Jacobian = JacobianT<Fp>;
+using Xyzz = XyzzT<Fp>;
 
 }  // namespace grape

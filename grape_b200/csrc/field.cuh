@@ -1,6 +1,6 @@
-// Montgomery arithmetic for the two 254-bit BN254 prime fields on 8 x 32-bit limbs, written for
-// the integer pipe of sm_100a (mad.lo.cc / madc.hi.cc carry chains that the assembler pairs into
-// wide multiply-adds).
+// Montgomery arithmetic for prime fields on 8 or 12 x 32-bit limbs (the two 254-bit BN254 fields; the
+// 381-bit base field and 255-bit scalar field of BLS12-381), written for the integer pipe of sm_100a
+// (mad.lo.cc / madc.hi.cc carry chains that the assembler pairs into wide multiply-adds).
 //
 // Element layout is the reference's (include/field/mont_t.cuh:30-36, alt_bn128.cuh:53-73): eight
 // little-endian 32-bit limbs holding value * 2^256 mod m, always fully reduced in memory.
@@ -23,6 +23,7 @@ namespace grape {
 // Field parameters.  MOD: modulus, R2: 2^512 mod m, ONE: 2^256 mod m, M0: -m^-1 mod 2^32.
 // ---------------------------------------------------------------------------------------------
 struct FpParams {  // base field of BN254 (reference: ALT_BN128_P, include/field/alt_bn128.cuh:11-27)
+  static constexpr int LIMBS = 8;
   __host__ __device__ static constexpr uint32_t mod(int i) {
     constexpr uint32_t t[8] = {0xd87cfd47u, 0x3c208c16u, 0x6871ca8du, 0x97816a91u,
                                       0x8181585du, 0xb85045b6u, 0xe131a029u, 0x30644e72u};
@@ -42,6 +43,7 @@ struct FpParams {  // base field of BN254 (reference: ALT_BN128_P, include/field
 };
 
 struct FrParams {  // scalar field of BN254 (reference: ALT_BN128_r, include/field/alt_bn128.cuh:29-45)
+  static constexpr int LIMBS = 8;
   __host__ __device__ static constexpr uint32_t mod(int i) {
     constexpr uint32_t t[8] = {0xf0000001u, 0x43e1f593u, 0x79b97091u, 0x2833e848u,
                                       0x8181585du, 0xb85045b6u, 0xe131a029u, 0x30644e72u};
@@ -58,6 +60,52 @@ struct FrParams {  // scalar field of BN254 (reference: ALT_BN128_r, include/fie
     return t[i];
   }
   static constexpr uint32_t M0 = 0xefffffffu;
+};
+
+
+// BLS12-381: 381-bit base field on twelve limbs (radix 2^384) and 255-bit scalar field on eight
+// (radix 2^256); the reference lists these constants in include/field/bls12-381.cuh:7-46.
+struct BlsFpParams {  // base field of BLS12-381
+  static constexpr int LIMBS = 12;
+  __host__ __device__ static constexpr uint32_t mod(int i) {
+    constexpr uint32_t t[12] = {0xffffaaabu, 0xb9feffffu, 0xb153ffffu, 0x1eabfffeu,
+                                      0xf6b0f624u, 0x6730d2a0u, 0xf38512bfu, 0x64774b84u,
+                                      0x434bacd7u, 0x4b1ba7b6u, 0x397fe69au, 0x1a0111eau};
+    return t[i];
+  }
+  __host__ __device__ static constexpr uint32_t r2(int i) {
+    constexpr uint32_t t[12] = {0x1c341746u, 0xf4df1f34u, 0x09d104f1u, 0x0a76e6a6u,
+                                      0x4c95b6d5u, 0x8de5476cu, 0x939d83c0u, 0x67eb88a9u,
+                                      0xb519952du, 0x9a793e85u, 0x92cae3aau, 0x11988fe5u};
+    return t[i];
+  }
+  __host__ __device__ static constexpr uint32_t one(int i) {
+    constexpr uint32_t t[12] = {0x0002fffdu, 0x76090000u, 0xc40c0002u, 0xebf4000bu,
+                                      0x53c758bau, 0x5f489857u, 0x70525745u, 0x77ce5853u,
+                                      0xa256ec6du, 0x5c071a97u, 0xfa80e493u, 0x15f65ec3u};
+    return t[i];
+  }
+  static constexpr uint32_t M0 = 0xfffcfffdu;
+};
+
+struct BlsFrParams {  // scalar field of BLS12-381
+  static constexpr int LIMBS = 8;
+  __host__ __device__ static constexpr uint32_t mod(int i) {
+    constexpr uint32_t t[8] = {0x00000001u, 0xffffffffu, 0xfffe5bfeu, 0x53bda402u,
+                                      0x09a1d805u, 0x3339d808u, 0x299d7d48u, 0x73eda753u};
+    return t[i];
+  }
+  __host__ __device__ static constexpr uint32_t r2(int i) {
+    constexpr uint32_t t[8] = {0xf3f29c6du, 0xc999e990u, 0x87925c23u, 0x2b6cedcbu,
+                                      0x7254398fu, 0x05d31496u, 0x9f59ff11u, 0x0748d9d9u};
+    return t[i];
+  }
+  __host__ __device__ static constexpr uint32_t one(int i) {
+    constexpr uint32_t t[8] = {0xfffffffeu, 0x00000001u, 0x00034802u, 0x5884b7fau,
+                                      0xecbc4ff5u, 0x998c4fefu, 0xacc5056fu, 0x1824b159u};
+    return t[i];
+  }
+  static constexpr uint32_t M0 = 0xffffffffu;
 };
 
 // ---------------------------------------------------------------------------------------------
@@ -175,112 +223,278 @@ __device__ __forceinline__ uint32_t sub8(uint32_t (&r)[8], const uint32_t (&a)[8
   return m;
 }
 
+// Twelve-limb counterparts of the helpers above (six products per chain).
+__device__ __forceinline__ void mul6(uint32_t (&t)[12], uint32_t s0, uint32_t s1, uint32_t s2,
+                                     uint32_t s3, uint32_t s4, uint32_t s5, uint32_t b) {
+  asm("mul.lo.u32 %0, %12, %18;\n\t"
+      "mul.hi.u32 %1, %12, %18;\n\t"
+      "mul.lo.u32 %2, %13, %18;\n\t"
+      "mul.hi.u32 %3, %13, %18;\n\t"
+      "mul.lo.u32 %4, %14, %18;\n\t"
+      "mul.hi.u32 %5, %14, %18;\n\t"
+      "mul.lo.u32 %6, %15, %18;\n\t"
+      "mul.hi.u32 %7, %15, %18;\n\t"
+      "mul.lo.u32 %8, %16, %18;\n\t"
+      "mul.hi.u32 %9, %16, %18;\n\t"
+      "mul.lo.u32 %10, %17, %18;\n\t"
+      "mul.hi.u32 %11, %17, %18;"
+      : "=&r"(t[0]), "=&r"(t[1]), "=&r"(t[2]), "=&r"(t[3]), "=&r"(t[4]), "=&r"(t[5]), "=&r"(t[6]), "=&r"(t[7]), "=&r"(t[8]), "=&r"(t[9]), "=&r"(t[10]), "=&r"(t[11])
+      : "r"(s0), "r"(s1), "r"(s2), "r"(s3), "r"(s4), "r"(s5), "r"(b));
+}
+
+__device__ __forceinline__ void mad6_top(uint32_t (&t)[12], uint32_t& top, uint32_t s0, uint32_t s1, uint32_t s2,
+    uint32_t s3, uint32_t s4, uint32_t s5, uint32_t b) {
+  asm("mad.lo.cc.u32 %0, %13, %19, %0;\n\t"
+      "madc.hi.cc.u32 %1, %13, %19, %1;\n\t"
+      "madc.lo.cc.u32 %2, %14, %19, %2;\n\t"
+      "madc.hi.cc.u32 %3, %14, %19, %3;\n\t"
+      "madc.lo.cc.u32 %4, %15, %19, %4;\n\t"
+      "madc.hi.cc.u32 %5, %15, %19, %5;\n\t"
+      "madc.lo.cc.u32 %6, %16, %19, %6;\n\t"
+      "madc.hi.cc.u32 %7, %16, %19, %7;\n\t"
+      "madc.lo.cc.u32 %8, %17, %19, %8;\n\t"
+      "madc.hi.cc.u32 %9, %17, %19, %9;\n\t"
+      "madc.lo.cc.u32 %10, %18, %19, %10;\n\t"
+      "madc.hi.cc.u32 %11, %18, %19, %11;\n\t"
+      "addc.u32 %12, %12, 0;"
+      : "+r"(t[0]), "+r"(t[1]), "+r"(t[2]), "+r"(t[3]), "+r"(t[4]), "+r"(t[5]), "+r"(t[6]), "+r"(t[7]), "+r"(t[8]), "+r"(t[9]), "+r"(t[10]), "+r"(t[11]), "+r"(top)
+      : "r"(s0), "r"(s1), "r"(s2), "r"(s3), "r"(s4), "r"(s5), "r"(b));
+}
+
+__device__ __forceinline__ void mad6(uint32_t (&t)[12], uint32_t s0, uint32_t s1, uint32_t s2,
+    uint32_t s3, uint32_t s4, uint32_t s5, uint32_t b) {
+  asm("mad.lo.cc.u32 %0, %12, %18, %0;\n\t"
+      "madc.hi.cc.u32 %1, %12, %18, %1;\n\t"
+      "madc.lo.cc.u32 %2, %13, %18, %2;\n\t"
+      "madc.hi.cc.u32 %3, %13, %18, %3;\n\t"
+      "madc.lo.cc.u32 %4, %14, %18, %4;\n\t"
+      "madc.hi.cc.u32 %5, %14, %18, %5;\n\t"
+      "madc.lo.cc.u32 %6, %15, %18, %6;\n\t"
+      "madc.hi.cc.u32 %7, %15, %18, %7;\n\t"
+      "madc.lo.cc.u32 %8, %16, %18, %8;\n\t"
+      "madc.hi.cc.u32 %9, %16, %18, %9;\n\t"
+      "madc.lo.cc.u32 %10, %17, %18, %10;\n\t"
+      "madc.hi.u32 %11, %17, %18, %11;"
+      : "+r"(t[0]), "+r"(t[1]), "+r"(t[2]), "+r"(t[3]), "+r"(t[4]), "+r"(t[5]), "+r"(t[6]), "+r"(t[7]), "+r"(t[8]), "+r"(t[9]), "+r"(t[10]), "+r"(t[11])
+      : "r"(s0), "r"(s1), "r"(s2), "r"(s3), "r"(s4), "r"(s5), "r"(b));
+}
+
+__device__ __forceinline__ void shift_mad6(uint32_t (&n)[12], uint32_t& lo0, const uint32_t (&e)[12],
+    uint32_t s0, uint32_t s1, uint32_t s2, uint32_t s3, uint32_t s4, uint32_t s5, uint32_t b) {
+  asm("add.cc.u32 %12, %12, %13;\n\t"
+      "madc.lo.cc.u32 %0, %24, %30, %14;\n\t"
+      "madc.hi.cc.u32 %1, %24, %30, %15;\n\t"
+      "madc.lo.cc.u32 %2, %25, %30, %16;\n\t"
+      "madc.hi.cc.u32 %3, %25, %30, %17;\n\t"
+      "madc.lo.cc.u32 %4, %26, %30, %18;\n\t"
+      "madc.hi.cc.u32 %5, %26, %30, %19;\n\t"
+      "madc.lo.cc.u32 %6, %27, %30, %20;\n\t"
+      "madc.hi.cc.u32 %7, %27, %30, %21;\n\t"
+      "madc.lo.cc.u32 %8, %28, %30, %22;\n\t"
+      "madc.hi.cc.u32 %9, %28, %30, %23;\n\t"
+      "madc.lo.cc.u32 %10, %29, %30, 0;\n\t"
+      "madc.hi.u32 %11, %29, %30, 0;"
+      : "=&r"(n[0]), "=&r"(n[1]), "=&r"(n[2]), "=&r"(n[3]), "=&r"(n[4]), "=&r"(n[5]), "=&r"(n[6]), "=&r"(n[7]), "=&r"(n[8]), "=&r"(n[9]), "=&r"(n[10]), "=&r"(n[11]), "+r"(lo0)
+      : "r"(e[1]), "r"(e[2]), "r"(e[3]), "r"(e[4]), "r"(e[5]), "r"(e[6]), "r"(e[7]), "r"(e[8]), "r"(e[9]), "r"(e[10]), "r"(e[11]), "r"(s0), "r"(s1), "r"(s2), "r"(s3), "r"(s4), "r"(s5), "r"(b));
+}
+
+__device__ __forceinline__ uint32_t add12(uint32_t (&r)[12], const uint32_t (&a)[12],
+                                          const uint32_t (&b)[12]) {
+  uint32_t c;
+  asm("add.cc.u32 %0, %13, %25;\n\t"
+      "addc.cc.u32 %1, %14, %26;\n\t"
+      "addc.cc.u32 %2, %15, %27;\n\t"
+      "addc.cc.u32 %3, %16, %28;\n\t"
+      "addc.cc.u32 %4, %17, %29;\n\t"
+      "addc.cc.u32 %5, %18, %30;\n\t"
+      "addc.cc.u32 %6, %19, %31;\n\t"
+      "addc.cc.u32 %7, %20, %32;\n\t"
+      "addc.cc.u32 %8, %21, %33;\n\t"
+      "addc.cc.u32 %9, %22, %34;\n\t"
+      "addc.cc.u32 %10, %23, %35;\n\t"
+      "addc.cc.u32 %11, %24, %36;\n\t"
+      "addc.u32 %12, 0, 0;"
+      : "=&r"(r[0]), "=&r"(r[1]), "=&r"(r[2]), "=&r"(r[3]), "=&r"(r[4]), "=&r"(r[5]), "=&r"(r[6]), "=&r"(r[7]), "=&r"(r[8]), "=&r"(r[9]), "=&r"(r[10]), "=&r"(r[11]), "=&r"(c)
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]), "r"(a[8]), "r"(a[9]), "r"(a[10]), "r"(a[11]), "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(b[4]), "r"(b[5]), "r"(b[6]), "r"(b[7]), "r"(b[8]), "r"(b[9]), "r"(b[10]), "r"(b[11]));
+  return c;
+}
+
+__device__ __forceinline__ uint32_t sub12(uint32_t (&r)[12], const uint32_t (&a)[12],
+                                          const uint32_t (&b)[12]) {
+  uint32_t c;
+  asm("sub.cc.u32 %0, %13, %25;\n\t"
+      "subc.cc.u32 %1, %14, %26;\n\t"
+      "subc.cc.u32 %2, %15, %27;\n\t"
+      "subc.cc.u32 %3, %16, %28;\n\t"
+      "subc.cc.u32 %4, %17, %29;\n\t"
+      "subc.cc.u32 %5, %18, %30;\n\t"
+      "subc.cc.u32 %6, %19, %31;\n\t"
+      "subc.cc.u32 %7, %20, %32;\n\t"
+      "subc.cc.u32 %8, %21, %33;\n\t"
+      "subc.cc.u32 %9, %22, %34;\n\t"
+      "subc.cc.u32 %10, %23, %35;\n\t"
+      "subc.cc.u32 %11, %24, %36;\n\t"
+      "subc.u32 %12, 0, 0;"
+      : "=&r"(r[0]), "=&r"(r[1]), "=&r"(r[2]), "=&r"(r[3]), "=&r"(r[4]), "=&r"(r[5]), "=&r"(r[6]), "=&r"(r[7]), "=&r"(r[8]), "=&r"(r[9]), "=&r"(r[10]), "=&r"(r[11]), "=&r"(c)
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]), "r"(a[8]), "r"(a[9]), "r"(a[10]), "r"(a[11]), "r"(b[0]), "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(b[4]), "r"(b[5]), "r"(b[6]), "r"(b[7]), "r"(b[8]), "r"(b[9]), "r"(b[10]), "r"(b[11]));
+  return c;
+}
+
+// Size-generic front ends: PAR selects the even (0) or odd (1) limbs of `a` as the multiplicands.
+template <int PAR>
+__device__ __forceinline__ void mul_half(uint32_t (&t)[8], const uint32_t (&a)[8], uint32_t b) {
+  mul4(t, a[PAR], a[PAR + 2], a[PAR + 4], a[PAR + 6], b);
+}
+template <int PAR>
+__device__ __forceinline__ void mul_half(uint32_t (&t)[12], const uint32_t (&a)[12], uint32_t b) {
+  mul6(t, a[PAR], a[PAR + 2], a[PAR + 4], a[PAR + 6], a[PAR + 8], a[PAR + 10], b);
+}
+template <int PAR>
+__device__ __forceinline__ void mad_half(uint32_t (&t)[8], const uint32_t (&a)[8], uint32_t b) {
+  mad4(t, a[PAR], a[PAR + 2], a[PAR + 4], a[PAR + 6], b);
+}
+template <int PAR>
+__device__ __forceinline__ void mad_half(uint32_t (&t)[12], const uint32_t (&a)[12], uint32_t b) {
+  mad6(t, a[PAR], a[PAR + 2], a[PAR + 4], a[PAR + 6], a[PAR + 8], a[PAR + 10], b);
+}
+template <int PAR>
+__device__ __forceinline__ void mad_half_top(uint32_t (&t)[8], uint32_t& top, const uint32_t (&a)[8], uint32_t b) {
+  mad4_top(t, top, a[PAR], a[PAR + 2], a[PAR + 4], a[PAR + 6], b);
+}
+template <int PAR>
+__device__ __forceinline__ void mad_half_top(uint32_t (&t)[12], uint32_t& top, const uint32_t (&a)[12], uint32_t b) {
+  mad6_top(t, top, a[PAR], a[PAR + 2], a[PAR + 4], a[PAR + 6], a[PAR + 8], a[PAR + 10], b);
+}
+template <int PAR>
+__device__ __forceinline__ void shift_mad_half(uint32_t (&n)[8], uint32_t& lo0, const uint32_t (&e)[8],
+                                               const uint32_t (&a)[8], uint32_t b) {
+  shift_mad4(n, lo0, e, a[PAR], a[PAR + 2], a[PAR + 4], a[PAR + 6], b);
+}
+template <int PAR>
+__device__ __forceinline__ void shift_mad_half(uint32_t (&n)[12], uint32_t& lo0, const uint32_t (&e)[12],
+                                               const uint32_t (&a)[12], uint32_t b) {
+  shift_mad6(n, lo0, e, a[PAR], a[PAR + 2], a[PAR + 4], a[PAR + 6], a[PAR + 8], a[PAR + 10], b);
+}
+__device__ __forceinline__ uint32_t addn(uint32_t (&r)[8], const uint32_t (&a)[8], const uint32_t (&b)[8]) { return add8(r, a, b); }
+__device__ __forceinline__ uint32_t addn(uint32_t (&r)[12], const uint32_t (&a)[12], const uint32_t (&b)[12]) { return add12(r, a, b); }
+__device__ __forceinline__ uint32_t subn(uint32_t (&r)[8], const uint32_t (&a)[8], const uint32_t (&b)[8]) { return sub8(r, a, b); }
+__device__ __forceinline__ uint32_t subn(uint32_t (&r)[12], const uint32_t (&a)[12], const uint32_t (&b)[12]) { return sub12(r, a, b); }
+
 // ---------------------------------------------------------------------------------------------
 // Field element
 // ---------------------------------------------------------------------------------------------
 template <class PARAMS>
 struct __align__(16) Fe {
-  uint32_t v[8];
+  static constexpr int N = PARAMS::LIMBS;   // 32-bit limbs (8 or 12)
+  static constexpr int BYTES = 4 * N;
+  uint32_t v[N];
   using Params = PARAMS;
 
-  __device__ __forceinline__ static void mod_limbs(uint32_t (&m)[8]) {
+  __device__ __forceinline__ static void mod_limbs(uint32_t (&m)[N]) {
 #pragma unroll
-    for (int i = 0; i < 8; i++) m[i] = PARAMS::mod(i);
+    for (int i = 0; i < N; i++) m[i] = PARAMS::mod(i);
   }
   __device__ __forceinline__ static Fe zero() {
     Fe r;
 #pragma unroll
-    for (int i = 0; i < 8; i++) r.v[i] = 0;
+    for (int i = 0; i < N; i++) r.v[i] = 0;
     return r;
   }
   __device__ __forceinline__ static Fe one() {
     Fe r;
 #pragma unroll
-    for (int i = 0; i < 8; i++) r.v[i] = PARAMS::one(i);
+    for (int i = 0; i < N; i++) r.v[i] = PARAMS::one(i);
     return r;
   }
   __device__ __forceinline__ static Fe r2() {
     Fe r;
 #pragma unroll
-    for (int i = 0; i < 8; i++) r.v[i] = PARAMS::r2(i);
+    for (int i = 0; i < N; i++) r.v[i] = PARAMS::r2(i);
     return r;
   }
   __device__ __forceinline__ bool is_zero() const {
     uint32_t o = 0;
 #pragma unroll
-    for (int i = 0; i < 8; i++) o |= v[i];
+    for (int i = 0; i < N; i++) o |= v[i];
     return o == 0;
   }
   __device__ __forceinline__ bool operator==(const Fe& b) const {
     uint32_t o = 0;
 #pragma unroll
-    for (int i = 0; i < 8; i++) o |= v[i] ^ b.v[i];
+    for (int i = 0; i < N; i++) o |= v[i] ^ b.v[i];
     return o == 0;
   }
   __device__ __forceinline__ bool operator!=(const Fe& b) const { return !(*this == b); }
 
-  // Loads / stores as two 16-byte vectors.
+  // Loads / stores as 16-byte vectors (two for 8 limbs, three for 12).
   __device__ __forceinline__ static Fe load(const void* p) {
     Fe r;
     const uint4* q = reinterpret_cast<const uint4*>(p);
-    uint4 a = q[0], b = q[1];
-    r.v[0] = a.x; r.v[1] = a.y; r.v[2] = a.z; r.v[3] = a.w;
-    r.v[4] = b.x; r.v[5] = b.y; r.v[6] = b.z; r.v[7] = b.w;
+#pragma unroll
+    for (int k = 0; k < N / 4; k++) {
+      uint4 a = q[k];
+      r.v[4 * k] = a.x; r.v[4 * k + 1] = a.y; r.v[4 * k + 2] = a.z; r.v[4 * k + 3] = a.w;
+    }
     return r;
   }
   __device__ __forceinline__ static Fe load_nc(const void* p) {
     Fe r;
     const uint4* q = reinterpret_cast<const uint4*>(p);
-    uint4 a = __ldg(q), b = __ldg(q + 1);
-    r.v[0] = a.x; r.v[1] = a.y; r.v[2] = a.z; r.v[3] = a.w;
-    r.v[4] = b.x; r.v[5] = b.y; r.v[6] = b.z; r.v[7] = b.w;
+#pragma unroll
+    for (int k = 0; k < N / 4; k++) {
+      uint4 a = __ldg(q + k);
+      r.v[4 * k] = a.x; r.v[4 * k + 1] = a.y; r.v[4 * k + 2] = a.z; r.v[4 * k + 3] = a.w;
+    }
     return r;
   }
   __device__ __forceinline__ void store(void* p) const {
     uint4* q = reinterpret_cast<uint4*>(p);
-    q[0] = make_uint4(v[0], v[1], v[2], v[3]);
-    q[1] = make_uint4(v[4], v[5], v[6], v[7]);
+#pragma unroll
+    for (int k = 0; k < N / 4; k++) q[k] = make_uint4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
   }
 };
 
 // r = a + b mod m
 template <class P>
 __device__ __forceinline__ Fe<P> fe_add(const Fe<P>& a, const Fe<P>& b) {
-  uint32_t s[8], t[8], m[8];
+  constexpr int N = P::LIMBS;
+  uint32_t s[N], t[N], m[N];
   Fe<P>::mod_limbs(m);
-  add8(s, a.v, b.v);  // both < m < 2^254: cannot carry out
-  uint32_t borrow = sub8(t, s, m);
+  addn(s, a.v, b.v);  // both operands < m < 2^(32 N - 1): cannot carry out
+  uint32_t borrow = subn(t, s, m);
   Fe<P> r;
 #pragma unroll
-  for (int i = 0; i < 8; i++) r.v[i] = borrow ? s[i] : t[i];
+  for (int i = 0; i < N; i++) r.v[i] = borrow ? s[i] : t[i];
   return r;
 }
 
 // r = a - b mod m
 template <class P>
 __device__ __forceinline__ Fe<P> fe_sub(const Fe<P>& a, const Fe<P>& b) {
-  uint32_t s[8], t[8], m[8];
+  constexpr int N = P::LIMBS;
+  uint32_t s[N], t[N], m[N];
   Fe<P>::mod_limbs(m);
-  uint32_t borrow = sub8(s, a.v, b.v);
+  uint32_t borrow = subn(s, a.v, b.v);
 #pragma unroll
-  for (int i = 0; i < 8; i++) m[i] &= borrow;
-  add8(t, s, m);
+  for (int i = 0; i < N; i++) m[i] &= borrow;
+  addn(t, s, m);
   Fe<P> r;
 #pragma unroll
-  for (int i = 0; i < 8; i++) r.v[i] = t[i];
+  for (int i = 0; i < N; i++) r.v[i] = t[i];
   return r;
 }
 
 // r = -a mod m (0 stays 0)
 template <class P>
 __device__ __forceinline__ Fe<P> fe_neg(const Fe<P>& a) {
-  uint32_t m[8], t[8];
+  constexpr int N = P::LIMBS;
+  uint32_t m[N], t[N];
   Fe<P>::mod_limbs(m);
-  sub8(t, m, a.v);
+  subn(t, m, a.v);
   bool z = a.is_zero();
   Fe<P> r;
 #pragma unroll
-  for (int i = 0; i < 8; i++) r.v[i] = z ? 0u : t[i];
+  for (int i = 0; i < N; i++) r.v[i] = z ? 0u : t[i];
   return r;
 }
 
@@ -289,7 +503,7 @@ __device__ __forceinline__ Fe<P> fe_cneg(const Fe<P>& a, bool flag) {
   Fe<P> n = fe_neg(a);
   Fe<P> r;
 #pragma unroll
-  for (int i = 0; i < 8; i++) r.v[i] = flag ? n.v[i] : a.v[i];
+  for (int i = 0; i < P::LIMBS; i++) r.v[i] = flag ? n.v[i] : a.v[i];
   return r;
 }
 
@@ -299,45 +513,50 @@ __device__ __forceinline__ Fe<P> fe_dbl(const Fe<P>& a) { return fe_add(a, a); }
 // One reduction step shared by the multiplication and by leaving Montgomery form:
 // adds mi * MOD so that limb 0 of E cancels.
 template <class P>
-__device__ __forceinline__ void redc_step(uint32_t (&E)[8], uint32_t (&O)[8]) {
+__device__ __forceinline__ void redc_step(uint32_t (&E)[P::LIMBS], uint32_t (&O)[P::LIMBS]) {
+  constexpr int N = P::LIMBS;
+  uint32_t m[N];
+  Fe<P>::mod_limbs(m);
   uint32_t mi = E[0] * P::M0;
-  mad4(O, P::mod(1), P::mod(3), P::mod(5), P::mod(7), mi);
-  mad4_top(E, O[7], P::mod(0), P::mod(2), P::mod(4), P::mod(6), mi);
+  mad_half<1>(O, m, mi);
+  mad_half_top<0>(E, O[N - 1], m, mi);
 }
 
 // Final merge: value = (E >> 32) + O, then one conditional subtraction.
 template <class P>
-__device__ __forceinline__ Fe<P> mont_finish(const uint32_t (&E)[8], const uint32_t (&O)[8]) {
-  uint32_t hi[8], s[8], t[8], m[8];
+__device__ __forceinline__ Fe<P> mont_finish(const uint32_t (&E)[P::LIMBS], const uint32_t (&O)[P::LIMBS]) {
+  constexpr int N = P::LIMBS;
+  uint32_t hi[N], s[N], t[N], m[N];
 #pragma unroll
-  for (int i = 0; i < 7; i++) hi[i] = E[i + 1];
-  hi[7] = 0;
-  add8(s, hi, O);
+  for (int i = 0; i < N - 1; i++) hi[i] = E[i + 1];
+  hi[N - 1] = 0;
+  addn(s, hi, O);
   Fe<P>::mod_limbs(m);
-  uint32_t borrow = sub8(t, s, m);
+  uint32_t borrow = subn(t, s, m);
   Fe<P> r;
 #pragma unroll
-  for (int i = 0; i < 8; i++) r.v[i] = borrow ? s[i] : t[i];
+  for (int i = 0; i < N; i++) r.v[i] = borrow ? s[i] : t[i];
   return r;
 }
 
-// r = a * b / 2^256 mod m
+// r = a * b / 2^(32 N) mod m.  Operands must be below 2^(32 N - 1) (true of every reduced element).
 template <class P>
 __device__ GRAPE_MUL_ATTR Fe<P> fe_mul(const Fe<P>& a, const Fe<P>& b) {
-  uint32_t E[8], O[8];
-  mul4(E, a.v[0], a.v[2], a.v[4], a.v[6], b.v[0]);
-  mul4(O, a.v[1], a.v[3], a.v[5], a.v[7], b.v[0]);
+  constexpr int N = P::LIMBS;
+  uint32_t E[N], O[N];
+  mul_half<0>(E, a.v, b.v[0]);
+  mul_half<1>(O, a.v, b.v[0]);
   redc_step<P>(E, O);
 #pragma unroll
-  for (int i = 1; i < 8; i++) {
-    uint32_t N[8];
+  for (int i = 1; i < N; i++) {
+    uint32_t Nx[N];
     // divide by 2^32: O becomes the even accumulator, E[2..] + odd products the new odd one
-    shift_mad4(N, O[0], E, a.v[1], a.v[3], a.v[5], a.v[7], b.v[i]);
-    mad4_top(O, N[7], a.v[0], a.v[2], a.v[4], a.v[6], b.v[i]);
+    shift_mad_half<1>(Nx, O[0], E, a.v, b.v[i]);
+    mad_half_top<0>(O, Nx[N - 1], a.v, b.v[i]);
 #pragma unroll
-    for (int k = 0; k < 8; k++) {
+    for (int k = 0; k < N; k++) {
       E[k] = O[k];
-      O[k] = N[k];
+      O[k] = Nx[k];
     }
     redc_step<P>(E, O);
   }
@@ -347,40 +566,42 @@ __device__ GRAPE_MUL_ATTR Fe<P> fe_mul(const Fe<P>& a, const Fe<P>& b) {
 template <class P>
 __device__ __forceinline__ Fe<P> fe_sqr(const Fe<P>& a) { return fe_mul(a, a); }
 
-// Leave Montgomery form: a / 2^256 mod m (eight reduction steps on the bare value).
+// Leave Montgomery form: a / 2^(32 N) mod m (N reduction steps on the bare value).
 template <class P>
 __device__ __forceinline__ Fe<P> fe_from_mont(const Fe<P>& a) {
-  uint32_t E[8], O[8];
+  constexpr int N = P::LIMBS;
+  uint32_t E[N], O[N], Z[N];
 #pragma unroll
-  for (int i = 0; i < 8; i++) { E[i] = a.v[i]; O[i] = 0; }
+  for (int i = 0; i < N; i++) { E[i] = a.v[i]; O[i] = 0; Z[i] = 0; }
   redc_step<P>(E, O);
 #pragma unroll
-  for (int i = 1; i < 8; i++) {
-    uint32_t N[8];
-    shift_mad4(N, O[0], E, 0u, 0u, 0u, 0u, 0u);
+  for (int i = 1; i < N; i++) {
+    uint32_t Nx[N];
+    shift_mad_half<1>(Nx, O[0], E, Z, 0u);
 #pragma unroll
-    for (int k = 0; k < 8; k++) {
+    for (int k = 0; k < N; k++) {
       E[k] = O[k];
-      O[k] = N[k];
+      O[k] = Nx[k];
     }
     redc_step<P>(E, O);
   }
   return mont_finish<P>(E, O);
 }
 
-// Enter Montgomery form: a * 2^256 mod m for any 256-bit a (the product with R^2 reduces it).
+// Enter Montgomery form: a * 2^(32 N) mod m (the product with R^2 reduces it).
 template <class P>
 __device__ __forceinline__ Fe<P> fe_to_mont(const Fe<P>& a) { return fe_mul(a, Fe<P>::r2()); }
 
 // a^(m-2) by square-and-multiply over the constant exponent (a = 0 maps to 0).
 template <class P>
 __device__ __noinline__ Fe<P> fe_inv(const Fe<P>& a) {
-  uint32_t e[8];
+  constexpr int N = P::LIMBS;
+  uint32_t e[N];
 #pragma unroll
-  for (int i = 0; i < 8; i++) e[i] = P::mod(i);
-  e[0] -= 2;  // MOD[0] >= 2 for both fields, no borrow
+  for (int i = 0; i < N; i++) e[i] = P::mod(i);
+  e[0] -= 2;  // MOD[0] >= 2 for every field here, no borrow
   Fe<P> acc = Fe<P>::one();
-  for (int w = 7; w >= 0; w--) {
+  for (int w = N - 1; w >= 0; w--) {
     uint32_t word = e[w];
     for (int bit = 31; bit >= 0; bit--) {
       acc = fe_sqr(acc);
@@ -412,7 +633,7 @@ template <class P>
 __device__ __forceinline__ Fe<P> fe_shfl_xor(const Fe<P>& a, int lane_mask) {
   Fe<P> r;
 #pragma unroll
-  for (int i = 0; i < 8; i++) r.v[i] = __shfl_xor_sync(0xffffffffu, a.v[i], lane_mask);
+  for (int i = 0; i < P::LIMBS; i++) r.v[i] = __shfl_xor_sync(0xffffffffu, a.v[i], lane_mask);
   return r;
 }
 
@@ -420,11 +641,13 @@ template <class P>
 __device__ __forceinline__ Fe<P> fe_shfl_down(const Fe<P>& a, int delta) {
   Fe<P> r;
 #pragma unroll
-  for (int i = 0; i < 8; i++) r.v[i] = __shfl_down_sync(0xffffffffu, a.v[i], delta);
+  for (int i = 0; i < P::LIMBS; i++) r.v[i] = __shfl_down_sync(0xffffffffu, a.v[i], delta);
   return r;
 }
 
 using Fp = Fe<FpParams>;
 using Fr = Fe<FrParams>;
+using BlsFp = Fe<BlsFpParams>;
+using BlsFr = Fe<BlsFrParams>;
 
 }  // namespace grape

@@ -85,6 +85,7 @@ extern "C" int grape_hyrax_open(grape_ctx* ctx, const grape_table* table, const 
                                 void* h_com_d, void* h_com_ad) {
   if (!ctx || !table || !d_tensor || !h_eval_point || !h_c || !h_G_jacobian || !h_result || !h_z || !h_com_d || !h_com_ad)
     return fail(ctx, GRAPE_ERR_INVALID, "null argument");
+  if (table->curve != 0) return fail(ctx, GRAPE_ERR_INVALID, "open: the opening protocol is built over BN254 only");
   if (N == 0 || layer_num == 0) return fail(ctx, GRAPE_ERR_INVALID, "open: zero dimension");
   if (size / N / GRAPE_COM_SCALE < layer_num)
     return fail(ctx, GRAPE_ERR_INVALID, "Size too small: size < N * com_scale * layer_num");

@@ -1,4 +1,5 @@
-// Hyrax row commitments: fixed-base multi-scalar multiplication over BN254 G1.
+// Hyrax row commitments: fixed-base multi-scalar multiplication over G1 of BN254 (the curve the
+// reference compiles) or BLS12-381 (same kernels instantiated on the 12-limb base field).
 //
 // Replaces (paths inside the reference project):
 //   precompute_generators / naive_msm                 src/ec_operation.cu:15-49
@@ -26,22 +27,26 @@
 
 namespace grape {
 
-struct TableView {
-  const Affine* base;
+template <class F>
+struct TableViewT {
+  const AffineT<F>* base;
   uint32_t n_gens;
   uint32_t window_bits;    // c
   uint32_t n_windows;      // windows whose 2^(c*w) multiples are stored
   uint32_t half;           // 2^(c-1): largest digit magnitude
   uint64_t window_stride;  // records per window
   uint32_t first_row;      // row of magnitude 1
-  __device__ __forceinline__ const Affine* entry(uint32_t w, uint32_t mag, uint32_t i) const {
+  __device__ __forceinline__ const AffineT<F>* entry(uint32_t w, uint32_t mag, uint32_t i) const {
     return base + (uint64_t)w * window_stride + (uint64_t)(mag - 1 + first_row) * n_gens + i;
   }
 };
 
-static TableView make_view(const grape_table* t) {
-  TableView v;
-  v.base = reinterpret_cast<const Affine*>(t->data);
+using TableView = TableViewT<Fp>;
+
+template <class F>
+static TableViewT<F> make_view(const grape_table* t) {
+  TableViewT<F> v;
+  v.base = reinterpret_cast<const AffineT<F>*>(t->data);
   v.n_gens = t->n_gens;
   v.window_bits = t->window_bits;
   v.n_windows = t->n_windows;
@@ -57,10 +62,15 @@ static TableView make_view(const grape_table* t) {
 constexpr int TABLE_BLOCK = 16;  // consecutive multiples produced (and batch-normalised) per thread
 
 // One thread: generator i, window w, magnitudes d0+1 .. d0+TABLE_BLOCK.
-__global__ void __launch_bounds__(128) table_build_kernel(const Jacobian* __restrict__ gens,
-                                                          Affine* __restrict__ table, uint32_t n_gens,
-                                                          uint32_t window_bits, uint32_t n_windows,
-                                                          uint32_t half) {
+template <class C>
+__global__ void __launch_bounds__(128) table_build_kernel(const JacobianT<typename C::F>* __restrict__ gens,
+                                                          AffineT<typename C::F>* __restrict__ table,
+                                                          uint32_t n_gens, uint32_t window_bits,
+                                                          uint32_t n_windows, uint32_t half) {
+  using Fp = typename C::F;
+  using Jacobian = JacobianT<Fp>;
+  using Affine = AffineT<Fp>;
+  using Xyzz = XyzzT<Fp>;
   const uint32_t blocks_per_window = half / TABLE_BLOCK;
   uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   uint64_t total = (uint64_t)n_gens * n_windows * blocks_per_window;
@@ -73,8 +83,8 @@ __global__ void __launch_bounds__(128) table_build_kernel(const Jacobian* __rest
   Jacobian gj;
   const char* gp = reinterpret_cast<const char*>(gens + i);
   gj.x = Fp::load(gp);
-  gj.y = Fp::load(gp + 32);
-  gj.z = Fp::load(gp + 64);
+  gj.y = Fp::load(gp + Fp::BYTES);
+  gj.z = Fp::load(gp + 2 * Fp::BYTES);
   Xyzz b = xyzz_from_jacobian(gj);
   for (uint32_t k = 0; k < window_bits * w; k++) b = xyzz_dbl(b);
   Affine base = xyzz_to_affine(b);  // 2^(c w) * G_i
@@ -124,14 +134,16 @@ struct Bias256 {
   uint32_t v[8];
 };
 
+template <class C>
 __global__ void fr_bias_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out,
                                uint64_t n, Bias256 bias) {
+  using Fr = typename C::S;
   uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= n) return;
   Fr s = Fr::load_nc(in + gid * 8);
   s = fe_from_mont(s);
   uint32_t r[8];
-  add8(r, s.v, bias.v);  // value < 2^254 and bias < 2^254: no carry out
+  add8(r, s.v, bias.v);  // value < 2^255 and bias < 2^255: no carry out
   uint4* o = reinterpret_cast<uint4*>(out + gid * 8);
   o[0] = make_uint4(r[0], r[1], r[2], r[3]);
   o[1] = make_uint4(r[4], r[5], r[6], r[7]);
@@ -165,11 +177,14 @@ struct DigitI32 {
   }
 };
 
-template <bool FR>
-__global__ void __launch_bounds__(MSM_THREADS, 4)
-commit_accumulate_kernel(const void* __restrict__ scalars, TableView tab, uint32_t wd,
+template <class C, bool FR>
+__global__ void __launch_bounds__(MSM_THREADS, C::MSM_BLOCKS)
+commit_accumulate_kernel(const void* __restrict__ scalars, TableViewT<typename C::F> tab, uint32_t wd,
                          uint32_t total_windows, uint32_t n_chunks, uint32_t chunk_len,
-                         uint64_t n_units, Xyzz* __restrict__ partials, uint32_t* __restrict__ status) {
+                         uint64_t n_units, XyzzT<typename C::F>* __restrict__ partials,
+                         uint32_t* __restrict__ status) {
+  using Affine = AffineT<typename C::F>;
+  using Xyzz = XyzzT<typename C::F>;
   const uint64_t unit = (uint64_t)blockIdx.x * (MSM_THREADS / 32) + (threadIdx.x >> 5);
   if (unit >= n_units) return;  // whole warps leave together
   const uint32_t lane = threadIdx.x & 31;
@@ -242,9 +257,12 @@ commit_accumulate_kernel(const void* __restrict__ scalars, TableView tab, uint32
   if (lane == 0) acc.store(partials + unit);
 }
 
-__global__ void __launch_bounds__(128) commit_finalize_kernel(const Xyzz* __restrict__ partials,
+template <class C>
+__global__ void __launch_bounds__(128) commit_finalize_kernel(const XyzzT<typename C::F>* __restrict__ partials,
                                                               uint32_t n_chunks, uint64_t rows,
-                                                              Jacobian* __restrict__ out) {
+                                                              JacobianT<typename C::F>* __restrict__ out) {
+  using Affine = AffineT<typename C::F>;
+  using Xyzz = XyzzT<typename C::F>;
   uint64_t row = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= rows) return;
   Xyzz acc = Xyzz::load(partials + row * n_chunks);
@@ -277,10 +295,10 @@ static uint32_t pick_chunks(const grape_ctx* ctx, uint64_t rows, uint32_t wd) {
   return (uint32_t)want;
 }
 
-template <bool FR>
+template <class C, bool FR>
 static int launch_commit(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t rows,
-                         uint32_t wd, uint32_t total_windows, Xyzz* partials, uint32_t n_chunks,
-                         void* d_out) {
+                         uint32_t wd, uint32_t total_windows, XyzzT<typename C::F>* partials,
+                         uint32_t n_chunks, void* d_out) {
   uint32_t chunk_len = (wd + n_chunks - 1) / n_chunks;
   uint64_t units = rows * n_chunks;
   if (units == 0) return GRAPE_OK;
@@ -288,11 +306,12 @@ static int launch_commit(grape_ctx* ctx, const grape_table* t, const void* d_sca
   if (blocks > 0x7fffffffull) return fail(ctx, GRAPE_ERR_LIMIT, "too many commitment rows for one launch");
   {
     ProfScope prof(ctx);
-    commit_accumulate_kernel<FR><<<(uint32_t)blocks, MSM_THREADS, 0, ctx->stream>>>(
-        d_scalars, make_view(t), wd, total_windows, n_chunks, chunk_len, units, partials, ctx->d_status);
+    commit_accumulate_kernel<C, FR><<<(uint32_t)blocks, MSM_THREADS, 0, ctx->stream>>>(
+        d_scalars, make_view<typename C::F>(t), wd, total_windows, n_chunks, chunk_len, units, partials,
+        ctx->d_status);
   }
-  commit_finalize_kernel<<<(uint32_t)((rows + 127) / 128), 128, 0, ctx->stream>>>(
-      partials, n_chunks, rows, reinterpret_cast<Jacobian*>(d_out));
+  commit_finalize_kernel<C><<<(uint32_t)((rows + 127) / 128), 128, 0, ctx->stream>>>(
+      partials, n_chunks, rows, reinterpret_cast<JacobianT<typename C::F>*>(d_out));
   ctx->launches += 2;
   GRAPE_CUDA_TRY(ctx, cudaGetLastError());
   return GRAPE_OK;
@@ -300,10 +319,13 @@ static int launch_commit(grape_ctx* ctx, const grape_table* t, const void* d_sca
 
 }  // namespace grape
 
-using namespace grape;
+namespace grape {
 
-extern "C" int grape_table_create(grape_ctx* ctx, const void* d_gens_jacobian, uint32_t n_gens,
-                                  uint32_t window_bits, uint32_t n_windows, grape_table** out) {
+template <class C>
+static int table_create_impl(grape_ctx* ctx, const void* d_gens_jacobian, uint32_t n_gens, uint32_t window_bits,
+                             uint32_t n_windows, grape_table** out) {
+  using AffineC = AffineT<typename C::F>;
+  using JacobianC = JacobianT<typename C::F>;
   if (!ctx || !out || !d_gens_jacobian) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
   if (window_bits < 5 || window_bits > 16)
     return fail(ctx, GRAPE_ERR_INVALID, "window_bits must be between 5 and 16");
@@ -312,7 +334,7 @@ extern "C" int grape_table_create(grape_ctx* ctx, const void* d_gens_jacobian, u
   uint32_t half = 1u << (window_bits - 1);
   uint64_t records = (uint64_t)half * n_gens * n_windows;
   void* data = nullptr;
-  cudaError_t e = cudaMalloc(&data, records * sizeof(Affine));
+  cudaError_t e = cudaMalloc(&data, records * sizeof(AffineC));
   if (e != cudaSuccess) return fail(ctx, GRAPE_ERR_NOMEM, "generator table allocation failed");
   uint64_t threads = (uint64_t)n_gens * n_windows * (half / TABLE_BLOCK);
   uint64_t blocks = (threads + 127) / 128;
@@ -320,8 +342,8 @@ extern "C" int grape_table_create(grape_ctx* ctx, const void* d_gens_jacobian, u
     cudaFree(data);
     return fail(ctx, GRAPE_ERR_LIMIT, "table too large for one launch");
   }
-  table_build_kernel<<<(uint32_t)blocks, 128, 0, ctx->stream>>>(
-      reinterpret_cast<const Jacobian*>(d_gens_jacobian), reinterpret_cast<Affine*>(data), n_gens,
+  table_build_kernel<C><<<(uint32_t)blocks, 128, 0, ctx->stream>>>(
+      reinterpret_cast<const JacobianC*>(d_gens_jacobian), reinterpret_cast<AffineC*>(data), n_gens,
       window_bits, n_windows, half);
   ctx->launches += 1;
   cudaError_t le = cudaGetLastError();
@@ -339,8 +361,59 @@ extern "C" int grape_table_create(grape_ctx* ctx, const void* d_gens_jacobian, u
   t->n_digits = half;
   t->window_stride = (uint64_t)half * n_gens;
   t->first_digit_row = 0;
+  t->curve = C::ID;
   *out = t;
   return GRAPE_OK;
+}
+
+template <class C>
+static int commit_i32_impl(grape_ctx* ctx, const grape_table* t, const int32_t* d_scalars, uint64_t rows,
+                           uint32_t wd, uint32_t max_bits, void* d_out) {
+  uint32_t total_windows = (max_bits + t->window_bits - 1) / t->window_bits;
+  uint32_t n_chunks = pick_chunks(ctx, rows, wd);
+  arena_reset(ctx);
+  XyzzT<typename C::F>* partials = nullptr;
+  int rc = arena_alloc_t(ctx, rows * n_chunks, &partials);
+  if (rc) return rc;
+  return launch_commit<C, false>(ctx, t, d_scalars, rows, wd, total_windows, partials, n_chunks, d_out);
+}
+
+// The number of windows is chosen so that window_bits * windows exceeds the scalar width: the top
+// window is read unsigned and then never exceeds the largest stored magnitude.
+template <class C>
+static int commit_fr_impl(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t size,
+                          uint64_t rows, uint32_t wd, void* d_out) {
+  uint32_t total_windows = (C::SCALAR_BITS + t->window_bits) / t->window_bits;
+  if (C::ID == Bn254::ID) total_windows = (254 + t->window_bits - 1) / t->window_bits;
+  uint32_t n_chunks = pick_chunks(ctx, rows, wd);
+  XyzzT<typename C::F>* partials = nullptr;
+  uint32_t* biased = nullptr;
+  int rc = arena_alloc_t(ctx, rows * n_chunks, &partials);
+  if (rc) return rc;
+  rc = arena_alloc_t(ctx, size * 8, &biased);
+  if (rc) return rc;
+  fr_bias_kernel<C><<<(uint32_t)((size + 255) / 256), 256, 0, ctx->stream>>>(
+      reinterpret_cast<const uint32_t*>(d_scalars), biased, size, make_bias(t->window_bits, total_windows));
+  ctx->launches += 1;
+  return launch_commit<C, true>(ctx, t, biased, rows, wd, total_windows, partials, n_chunks, d_out);
+}
+
+static size_t jacobian_bytes(const grape_table* t) {
+  return t->curve == Bls12381::ID ? sizeof(JacobianT<BlsFp>) : sizeof(Jacobian);
+}
+
+}  // namespace grape
+
+using namespace grape;
+
+extern "C" int grape_table_create(grape_ctx* ctx, const void* d_gens_jacobian, uint32_t n_gens,
+                                  uint32_t window_bits, uint32_t n_windows, grape_table** out) {
+  return table_create_impl<Bn254>(ctx, d_gens_jacobian, n_gens, window_bits, n_windows, out);
+}
+
+extern "C" int grape_bls12_381_table_create(grape_ctx* ctx, const void* d_gens_jacobian, uint32_t n_gens,
+                                            uint32_t window_bits, uint32_t n_windows, grape_table** out) {
+  return table_create_impl<Bls12381>(ctx, d_gens_jacobian, n_gens, window_bits, n_windows, out);
 }
 
 extern "C" int grape_table_from_reference(grape_ctx* ctx, const void* d_points, uint32_t n_gens,
@@ -356,6 +429,7 @@ extern "C" int grape_table_from_reference(grape_ctx* ctx, const void* d_points, 
   t->n_digits = 128;
   t->window_stride = (uint64_t)256 * n_gens;
   t->first_digit_row = 1;  // row 0 of that layout is 0*G = infinity
+  t->curve = Bn254::ID;
   *out = t;
   return GRAPE_OK;
 }
@@ -370,10 +444,12 @@ extern "C" int grape_table_destroy(grape_table* t) {
 extern "C" uint64_t grape_table_bytes(const grape_table* t) {
   if (!t) return 0;
   uint64_t rows = t->owned ? (uint64_t)t->n_digits * t->n_windows : 256;
-  return rows * t->n_gens * sizeof(Affine);
+  return rows * t->n_gens * (t->curve == Bls12381::ID ? sizeof(AffineT<BlsFp>) : sizeof(Affine));
 }
 
 extern "C" const void* grape_table_data(const grape_table* t) { return t ? t->data : nullptr; }
+
+extern "C" uint32_t grape_table_curve(const grape_table* t) { return t ? t->curve : 0; }
 
 extern "C" int grape_commit_i32(grape_ctx* ctx, const grape_table* t, const int32_t* d_scalars,
                                 uint64_t size, uint32_t wd, uint32_t max_bits, void* d_out) {
@@ -384,13 +460,8 @@ extern "C" int grape_commit_i32(grape_ctx* ctx, const grape_table* t, const int3
   if (size == 0) return GRAPE_OK;
   if (!d_scalars || !d_out) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
   uint64_t rows = size / wd;
-  uint32_t total_windows = (max_bits + t->window_bits - 1) / t->window_bits;
-  uint32_t n_chunks = pick_chunks(ctx, rows, wd);
-  arena_reset(ctx);
-  Xyzz* partials = nullptr;
-  rc = arena_alloc_t(ctx, rows * n_chunks, &partials);
-  if (rc) return rc;
-  return launch_commit<false>(ctx, t, d_scalars, rows, wd, total_windows, partials, n_chunks, d_out);
+  if (t->curve == Bls12381::ID) return commit_i32_impl<Bls12381>(ctx, t, d_scalars, rows, wd, max_bits, d_out);
+  return commit_i32_impl<Bn254>(ctx, t, d_scalars, rows, wd, max_bits, d_out);
 }
 
 namespace grape {
@@ -404,18 +475,8 @@ int commit_fr_async(grape_ctx* ctx, const grape_table* t, const void* d_scalars,
   if (size == 0) return GRAPE_OK;
   if (!d_scalars || !d_out) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
   uint64_t rows = size / wd;
-  uint32_t total_windows = (254 + t->window_bits - 1) / t->window_bits;
-  uint32_t n_chunks = pick_chunks(ctx, rows, wd);
-  Xyzz* partials = nullptr;
-  uint32_t* biased = nullptr;
-  rc = arena_alloc_t(ctx, rows * n_chunks, &partials);
-  if (rc) return rc;
-  rc = arena_alloc_t(ctx, size * 8, &biased);
-  if (rc) return rc;
-  fr_bias_kernel<<<(uint32_t)((size + 255) / 256), 256, 0, ctx->stream>>>(
-      reinterpret_cast<const uint32_t*>(d_scalars), biased, size, make_bias(t->window_bits, total_windows));
-  ctx->launches += 1;
-  return launch_commit<true>(ctx, t, biased, rows, wd, total_windows, partials, n_chunks, d_out);
+  if (t->curve == Bls12381::ID) return commit_fr_impl<Bls12381>(ctx, t, d_scalars, size, rows, wd, d_out);
+  return commit_fr_impl<Bn254>(ctx, t, d_scalars, size, rows, wd, d_out);
 }
 }  // namespace grape
 
@@ -434,7 +495,8 @@ extern "C" int grape_commit_i32_host(grape_ctx* ctx, const grape_table* t, const
   if (size == 0) return GRAPE_OK;
   uint64_t rows = size / wd;
   size_t in_bytes = size * sizeof(int32_t);
-  size_t out_bytes = rows * GRAPE_JACOBIAN_BYTES;
+  const size_t jac = jacobian_bytes(t);
+  size_t out_bytes = rows * jac;
   size_t need = ((in_bytes + 255) & ~size_t(255)) + out_bytes;
   if (need > ctx->dstage_bytes) {
     GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
@@ -472,7 +534,7 @@ extern "C" int grape_commit_i32_host(grape_ctx* ctx, const grape_table* t, const
     if (r0 >= rows) break;
     const uint64_t r1 = std::min<uint64_t>(rows, r0 + rows_per_slice);
     GRAPE_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->copy_events[sidx], 0));
-    rc = grape_commit_i32(ctx, t, d_in + r0 * wd, (r1 - r0) * wd, wd, max_bits, d_out + r0 * GRAPE_JACOBIAN_BYTES);
+    rc = grape_commit_i32(ctx, t, d_in + r0 * wd, (r1 - r0) * wd, wd, max_bits, d_out + r0 * jac);
     if (rc) return rc;
   }
   GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(h_out, d_out, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
@@ -602,9 +664,9 @@ extern "C" int grape_commit_i32_static(const void* d_table, uint32_t n_gens, uin
   Xyzz* partials = reinterpret_cast<Xyzz*>(st->partials);
   cudaError_t e = cudaMemsetAsync(st->status, 0, sizeof(uint32_t), s);  // must start at zero
   if (e == cudaSuccess) {
-    commit_accumulate_kernel<false><<<(uint32_t)blocks, MSM_THREADS, 0, s>>>(
+    commit_accumulate_kernel<Bn254, false><<<(uint32_t)blocks, MSM_THREADS, 0, s>>>(
         d_scalars, view, wd, total_windows, (uint32_t)n_chunks, chunk_len, units, partials, st->status);
-    commit_finalize_kernel<<<(uint32_t)((rows + 127) / 128), 128, 0, s>>>(partials, (uint32_t)n_chunks, rows,
+    commit_finalize_kernel<Bn254><<<(uint32_t)((rows + 127) / 128), 128, 0, s>>>(partials, (uint32_t)n_chunks, rows,
                                                                           reinterpret_cast<Jacobian*>(d_out));
     e = cudaGetLastError();
   }

@@ -346,6 +346,7 @@ static int lookup_prove(grape_ctx* ctx, grape_lookup* lk, uint32_t* d_S, uint64_
   const uint32_t lD = log2ceil(D);
   const uint64_t Dp = uint64_t(1) << lD;
   if (n_v != lD) return fail(ctx, GRAPE_ERR_INVALID, "lookup: v.size() != ceilLog2(D)");
+  if (table && table->curve != 0) return fail(ctx, GRAPE_ERR_INVALID, "lookup: commitments are built over BN254 only");
   if (Dp < N) return fail(ctx, GRAPE_ERR_INVALID, "lookup: fewer queries than table entries is not supported");
   if (D != Dp && (inner == 0 || inner_pad < inner || D % inner != 0 || (D / inner) * (uint64_t)inner_pad != Dp))
     return fail(ctx, GRAPE_ERR_INVALID, "lookup: cannot pad the queries to a power of two with the given row lengths");

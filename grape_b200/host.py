@@ -281,16 +281,23 @@ def _p(x):
 class GeneratorTable:
     """Fixed-base table of the Hyrax generators (replaces ``precompute_generators``)."""
 
-    def __init__(self, ctx: Context, gens_jacobian: np.ndarray, window_bits: int = 8, n_windows: int = 1):
+    def __init__(self, ctx: Context, gens_jacobian: np.ndarray, window_bits: int = 8, n_windows: int = 1,
+                 curve: str = "bn254"):
+        """``curve`` is "bn254" (96-byte Jacobian generator records) or "bls12_381" (144-byte)."""
+        if curve not in ("bn254", "bls12_381"):
+            raise ValueError("curve must be 'bn254' or 'bls12_381'")
         self.ctx = ctx
-        gens = np.ascontiguousarray(gens_jacobian, dtype=np.uint32).reshape(-1, 24)
+        self.curve = curve
+        #: bytes of one commitment (Jacobian) record on this curve
+        self.jacobian_bytes = 96 if curve == "bn254" else 144
+        gens = np.ascontiguousarray(gens_jacobian, dtype=np.uint32).reshape(-1, self.jacobian_bytes // 4)
         self.n_gens = gens.shape[0]
         self.window_bits = window_bits
         self.n_windows = n_windows
         self._gens_dev = ctx.upload(gens)
         h = C.c_void_p()
-        ctx._check(ctx.lib.grape_table_create(ctx.handle, self._gens_dev.ptr, self.n_gens, window_bits,
-                                              n_windows, C.byref(h)))
+        create = ctx.lib.grape_table_create if curve == "bn254" else ctx.lib.grape_bls12_381_table_create
+        ctx._check(create(ctx.handle, self._gens_dev.ptr, self.n_gens, window_bits, n_windows, C.byref(h)))
         self.handle = h.value
 
     @property
@@ -320,11 +327,12 @@ def commit_fr(ctx: Context, table: GeneratorTable, d_scalars, size: int, wd: int
 
 def commit_i32_host(ctx: Context, table: GeneratorTable, scalars: np.ndarray, wd: int, max_bits: int = 32,
                     out: np.ndarray | None = None) -> np.ndarray:
-    """Host int32 tensor in, host Jacobian records (uint32[rows, 24]) out; copies included."""
+    """Host int32 tensor in, host Jacobian records (uint32[rows, 24], or [rows, 36] on BLS12-381) out;
+    copies included."""
     scalars = np.ascontiguousarray(scalars, dtype=np.int32).reshape(-1)
     rows = scalars.size // wd
     if out is None:
-        out = np.empty((rows, 24), dtype=np.uint32)
+        out = np.empty((rows, table.jacobian_bytes // 4), dtype=np.uint32)
     ctx._check(ctx.lib.grape_commit_i32_host(ctx.handle, table.handle, scalars.ctypes.data, scalars.size, wd,
                                              max_bits, out.ctypes.data))
     return out

@@ -34,6 +34,10 @@ extern "C" {
 #define GRAPE_FR_BYTES 32
 #define GRAPE_AFFINE_BYTES 64
 #define GRAPE_JACOBIAN_BYTES 96
+#define GRAPE_BLS12_381_AFFINE_BYTES 96
+#define GRAPE_BLS12_381_JACOBIAN_BYTES 144
+#define GRAPE_CURVE_BN254 0u
+#define GRAPE_CURVE_BLS12_381 1u
 #define GRAPE_COM_SCALE 16 /* reference: Hyrax::com_scale, src/Hyrax.cu:229 */
 
 typedef struct grape_ctx grape_ctx;
@@ -77,6 +81,17 @@ int grape_table_create(grape_ctx* ctx, const void* d_gens_jacobian, uint32_t n_g
  * row w = w*G_i (src/ec_operation.cu:24).  Borrows d_points (no copy). */
 int grape_table_from_reference(grape_ctx* ctx, const void* d_points, uint32_t n_gens,
                                grape_table** out);
+/* The same table over BLS12-381 G1 (y^2 = x^3 + 4; Fp on twelve 32-bit limbs with Montgomery radix
+ * 2^384, Fr on eight with radix 2^256 -- the constants of include/field/bls12-381.cuh:7-46, which the
+ * reference defines but compiles nothing against, so there is no reference call site).  Records are
+ * 3/2 the BN254 sizes: generators and commitments are 144-byte Jacobian records (X|Y|Z, 48 B each),
+ * table entries 96-byte affine records.  grape_commit_i32, grape_commit_fr and
+ * grape_commit_i32_host accept such a table and then read BLS12-381 Fr scalars / write 144-byte
+ * records; the opening and lookup entry points reject it. */
+int grape_bls12_381_table_create(grape_ctx* ctx, const void* d_gens_jacobian, uint32_t n_gens,
+                                 uint32_t window_bits, uint32_t n_windows, grape_table** out);
+/* GRAPE_CURVE_BN254 or GRAPE_CURVE_BLS12_381. */
+uint32_t grape_table_curve(const grape_table* t);
 int grape_table_destroy(grape_table* t);
 uint64_t grape_table_bytes(const grape_table* t);
 const void* grape_table_data(const grape_table* t);
@@ -252,6 +267,13 @@ const char* grape_static_error(void);
 /* ---- diagnostics and measurement ----------------------------------------------------------- */
 /* Element-wise add (0) / sub (1) / mul (2) over the base field Fp; test hook for the curve code. */
 int grape_fp_binary(grape_ctx* ctx, int op, const void* d_a, const void* d_b, void* d_out, uint64_t n);
+/* BLS12-381 field hooks (no reference call site): element-wise add (0) / sub (1) / mul (2) over Fr
+ * (field 0, 32-byte elements) or Fp (field 1, 48-byte elements); signed int32 -> Fr as
+ * grape_fr_from_i32 does for BN254; base-field multiplications per second on register operands. */
+int grape_bls12_381_field_binary(grape_ctx* ctx, int field, int op, const void* d_a, const void* d_b,
+                                 void* d_out, uint64_t n);
+int grape_bls12_381_fr_from_i32(grape_ctx* ctx, const int32_t* d_in, void* d_out, uint64_t n);
+int grape_bls12_381_measure_mul_peak(grape_ctx* ctx, double* muls_per_second);
 /* Device status word: bit 0 = a scalar exceeded max_bits, bit 1 = lookup query outside its table.
  * Kernels set bits instead of trapping; reading synchronises and clears. */
 int grape_ctx_status(grape_ctx* ctx, uint32_t* flags);
