@@ -53,7 +53,7 @@ def parse_args():
                     help="also time the proof of this many decoder layers (one batch, seq 2048)")
     ap.add_argument("--proof-window-bits", type=int, default=13)
     ap.add_argument("--proof-scope", default="layer", choices=["layer", "ffn"])
-    ap.add_argument("--workload", default="commit", choices=["commit", "matmul", "lookup"],
+    ap.add_argument("--workload", default="commit", choices=["commit", "matmul", "lookup", "commit-bls12-381"],
                     help="commit = C4 (the headline); matmul = C2 prove_matmul; lookup = C3 range lookup")
     ap.add_argument("--shrink", type=int, default=1, help="divide the matmul / lookup sizes (profiling cases)")
     ap.add_argument("--rows", type=int, default=0, help="commit only this many rows (reduced case for profiling)")
@@ -477,6 +477,42 @@ def run_secondary(args):
                              "note": "mean over the A-fold and B-fold launches; 32 B read and one field "
                                      "multiplication per element, so the integer pipe caps it near 2.2 TB/s"},
                 "gpu_launches": int(launches)}
+    elif args.workload == "commit-bls12-381":
+        # The C4 shape over BLS12-381 G1 (the reference compiles BN254 only; reported separately).
+        wd = args.gens
+        n = wl.layer_weight_elements() // args.shrink if not args.rows else args.rows * wd
+        n -= n % wd
+        rows = n // wd
+        gens = wl.make_generators_bls12_381(ctx, wd, SEED)
+        table = g.GeneratorTable(ctx, gens, args.window_bits, 1 if args.window_bits == 16 else 2, curve="bls12_381")
+        h_scalars = wl.quantised_normal(rng, n)
+        d_scalars, d_out = ctx.upload(h_scalars), ctx.alloc(rows * 144)
+        launches = 0
+        for it in range(args.warmup + args.steps):
+            if it == args.warmup:
+                ctx.prof_enable(True)
+            l0 = ctx.launches
+            ctx.timer_begin()
+            g.commit_i32(ctx, table, d_scalars, n, wd, d_out, max_bits=16)
+            ms = ctx.timer_end()
+            if it >= args.warmup:
+                times.append(ms)
+                launches += ctx.launches - l0
+        k_ms, k_n = ctx.prof_read()
+        per_launch = k_ms / max(k_n, 1)
+        mul_peak = ctx.measure_bls12_381_mul_peak()
+        adds = n * (1 if args.window_bits == 16 else 2)
+        muls_per_s = adds * 10 / (per_launch * 1e-3)
+        line = {"metric": "Hyrax MSM points/s over BLS12-381 G1", "value": n / (float(np.mean(times)) * 1e-3),
+                "unit": "points/s", "higher_is_better": True, "ms_per_step": float(np.mean(times)),
+                "config": {"workload": f"C4 shape over BLS12-381: {rows} rows x {wd} generators, int16 scalars, "
+                                       f"{args.window_bits}-bit signed windows; inputs resident in HBM"},
+                "roofline": {"bound": "int32-multiply pipe", "kernel": "commit_accumulate_kernel<Bls12381>",
+                             "achieved": muls_per_s / 1e9, "peak": mul_peak / 1e9, "unit": "G 12-limb field mul/s",
+                             "frac": muls_per_s / mul_peak, "kernel_ms": per_launch, "traffic": None,
+                             "note": "10 field multiplications per mixed addition (8 products + 2 squarings); peak = "
+                                     "the same multiplication looped on registers, measured in this run"},
+                "gpu_launches": int(launches), "table_bytes": table.nbytes, "device_status": ctx.status()}
     else:
         D, Nt = (1 << 22) // args.shrink, 1 << 16
         gens = wl.make_generators(ctx, 4096, 0xC3)
@@ -504,7 +540,8 @@ def run_secondary(args):
                 "config": {"workload": f"C3: range lookup, {D} queries into a 2^16 table, commitments of A and m over 4096 generators"},
                 "without_commitments_ms": res["without_commitments"], "gpu_launches": int(launches)}
     line.update({"n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "data": "synthetic",
-                 "dtype": "u32 limbs (254-bit fields)", "vs_baseline": None})
+                 "dtype": "u32 limbs (381-bit base field)" if args.workload == "commit-bls12-381"
+                 else "u32 limbs (254-bit fields)", "vs_baseline": None})
     print(json.dumps(line))
 
 

@@ -212,7 +212,10 @@ struct Bls12381 {
   using S = BlsFr;
   static constexpr uint32_t ID = 1;
   static constexpr uint32_t SCALAR_BITS = 255;
-  static constexpr int MSM_BLOCKS = 2;
+#ifndef GRAPE_BLS_MSM_BLOCKS
+#define GRAPE_BLS_MSM_BLOCKS 3
+#endif
+  static constexpr int MSM_BLOCKS = GRAPE_BLS_MSM_BLOCKS;
 };
 
 using Affine = AffineT<Fp>;

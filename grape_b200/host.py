@@ -189,6 +189,12 @@ class Context:
         self._check(self.lib.grape_measure_int_peak(self.handle, kind, C.byref(v)))
         return v.value
 
+    def measure_bls12_381_mul_peak(self) -> float:
+        """12-limb base-field multiplications per second on register operands."""
+        v = C.c_double()
+        self._check(self.lib.grape_bls12_381_measure_mul_peak(self.handle, C.byref(v)))
+        return v.value
+
     def measure_madd_peak(self) -> float:
         """Mixed point additions per second with register-resident operands."""
         v = C.c_double()

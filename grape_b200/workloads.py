@@ -64,3 +64,30 @@ def exact_matmul_cuda(a: np.ndarray, b: np.ndarray) -> np.ndarray:
     del ta, tb
     torch.cuda.empty_cache()
     return r
+
+
+#: the standard BLS12-381 G1 generator as a 144-byte Jacobian record (X|Y|1, Montgomery limbs, radix 2^384)
+_BLS_P = 0x1A0111EA397FE69A4B1BA7B6434BACD764774B84F38512BF6730D2A0F6B0F6241EABFFFEB153FFFFB9FEFFFFFFFFAAAB
+_BLS_G1 = (
+    0x17F1D3A73197D7942695638C4FA9AC0FC3688C4F9774B905A14E3A3F171BAC586C55E83FF97A1AEFFB3AF00ADB22C6BB,
+    0x08B3F481E3AAA0F1A09E30ED741D8AE4FCF5E095D5D00AF600DB18CB2C04B3EDD03CC744A2888AE40CAA232946C5E7E1,
+)
+
+
+def make_generators_bls12_381(ctx: Context, n: int, seed: int) -> np.ndarray:
+    """n BLS12-381 generators [rho_i] * G1 as uint32[n, 36] Jacobian records, computed on the GPU
+    with the library's own fixed-base commitment over the single standard generator.  rho_i are the
+    seeded stream's 32-byte draws read as BLS12-381 scalar-field residues."""
+    rec = b"".join(((c << 384) % _BLS_P).to_bytes(48, "little") for c in (_BLS_G1[0], _BLS_G1[1], 1))
+    base = GeneratorTable(ctx, np.frombuffer(rec, dtype=np.uint32).reshape(1, 36), window_bits=8, n_windows=32,
+                          curve="bls12_381")
+    ctx.seed(seed)
+    rho = ctx.random_fr(n)
+    d_rho = ctx.upload(rho)
+    d_out = ctx.alloc(n * 144)
+    commit_fr(ctx, base, d_rho, n, 1, d_out)
+    gens = ctx.download(d_out, n * 144).reshape(n, 36)
+    base.close()
+    d_rho.free()
+    d_out.free()
+    return gens

@@ -142,3 +142,12 @@ def test_bn254_only_entry_points_reject_a_bls_table(gctx):
     with pytest.raises(Exception):
         g.hyrax_open(gctx, table, gctx.alloc(16 * 32), 16, 1, 1, [0, 0, 0, 0], 1, np.zeros(24, dtype=np.uint32))
     table.close()
+
+
+def test_synthetic_generators_are_multiples_of_the_standard_generator(gctx):
+    from grape_b200 import workloads as wl
+    gens = wl.make_generators_bls12_381(gctx, 5, seed=77)
+    gctx.seed(77)
+    rho = gctx.random_fr(5).tobytes()
+    want = [bls.scalar_mul(bls.fr_from_bytes(rho[i * 32:(i + 1) * 32]), bls.G1_GEN) for i in range(5)]
+    assert _dec_jac(gens) == want
