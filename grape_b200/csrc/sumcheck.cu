@@ -251,6 +251,92 @@ static void launch_round_two(grape_ctx* ctx, uint32_t* A, uint32_t* B, uint64_t 
 
 }  // namespace grape
 
+namespace grape {
+
+// Everything grape_prove_matmul enqueues before its host pass: the two axis folds and one fused
+// kernel pair per round.  On return the stream holds all the work; `sums` gets three field
+// elements per round and a_[0], b_[0] the fully folded values.
+struct MatmulRun {
+  uint32_t *d_u = nullptr, *d_v = nullptr, *a_ = nullptr, *b_ = nullptr, *partial = nullptr, *sums = nullptr, *wl = nullptr;
+  uint32_t lL = 0, lK = 0, u_end = 0, v_end = 0;
+  std::vector<RoundInfo> rounds;
+};
+
+static int matmul_enqueue(grape_ctx* ctx, void* d_A, void* d_B, uint32_t L, uint32_t N, uint32_t M, uint32_t K,
+                          const HostFr* u, uint32_t n_u, const HostFr* v, uint32_t n_v, MatmulRun& run) {
+  if (!L || !N || !M || !K) return fail(ctx, GRAPE_ERR_INVALID, "prove_matmul: zero dimension");
+  const uint32_t lL = log2ceil(L), lN = log2ceil(N), lM = log2ceil(M), lK = log2ceil(K);
+  if ((1u << lL) != L) return fail(ctx, GRAPE_ERR_INVALID, "prove_matmul: L must be a power of two");
+  const uint32_t u_end = log2ceil((uint64_t)L * N * M), v_end = log2ceil((uint64_t)L * K);
+  if (n_u < u_end || n_u < lM + lN + lL || n_v < v_end || n_v < lK)
+    return fail(ctx, GRAPE_ERR_INVALID, "prove_matmul: challenge vectors too short");
+  run.lL = lL;
+  run.lK = lK;
+  run.u_end = u_end;
+  run.v_end = v_end;
+  arena_reset(ctx);
+  int rc;
+  if ((rc = upload_fr(ctx, u, n_u, &run.d_u))) return rc;
+  if ((rc = upload_fr(ctx, v, n_v, &run.d_v))) return rc;
+  const uint64_t LK = (uint64_t)L * K;
+  if ((rc = arena_alloc_t(ctx, LK * 8, &run.a_))) return rc;
+  if ((rc = arena_alloc_t(ctx, LK * 8, &run.b_))) return rc;
+  const uint32_t total_rounds = lL + lK;
+  if ((rc = arena_alloc_t(ctx, (size_t)ctx->sm_count * 4 * 3 * 8 + 64, &run.partial))) return rc;
+  if ((rc = arena_alloc_t(ctx, (size_t)(total_rounds + 1) * 3 * 8, &run.sums))) return rc;
+  if ((rc = arena_alloc_t(ctx, (size_t)L * 8 + 8, &run.wl))) return rc;
+  uint32_t *d_u = run.d_u, *d_v = run.d_v, *a_ = run.a_, *b_ = run.b_;
+  // a_[l][k] = sum_n eq(u_N, n) A[l][n][k],  b_[l][k] = sum_m eq(u_M, m) B[l][m][k]
+  if ((rc = fold_axis_async<false>(ctx, d_A, (uint64_t)L * N * K, d_u + (size_t)lM * 8, N, K, a_))) return rc;
+  if ((rc = fold_axis_async<false>(ctx, d_B, (uint64_t)L * M * K, d_u, M, K, b_))) return rc;
+
+  std::vector<RoundInfo>& rounds = run.rounds;
+  uint64_t in_size = LK, out_size = LK / 2;
+  const uint32_t u_l0 = u_end - lL;
+  for (uint32_t i = 0; i < lL; i++) {  // phase 1: layer variables, top first
+    const uint32_t rem_layers = (uint32_t)(out_size / K);
+    eq_weights_async(ctx, d_u + (size_t)u_l0 * 8, log2ceil(rem_layers), rem_layers, run.wl);
+    PairWeights pw{run.wl, nullptr, K};
+    launch_round_two<true, false>(ctx, a_, b_, in_size, out_size, d_v + (size_t)(v_end - i - 1) * 8, pw, run.partial,
+                                  run.sums + (size_t)rounds.size() * 3 * 8);
+    rounds.push_back({true, u[u_end - i - 1], v[v_end - i - 1]});
+    in_size = out_size;
+    out_size /= 2;
+  }
+  in_size = K;
+  out_size = lK ? (uint64_t(1) << (lK - 1)) : 0;
+  for (uint32_t i = 0; i < lK; i++) {  // phase 2: inner-product variables, top first
+    PairWeights pw{nullptr, nullptr, 1};
+    launch_round_two<false, false>(ctx, a_, b_, in_size, out_size, d_v + (size_t)(lK - i - 1) * 8, pw, run.partial,
+                                   run.sums + (size_t)rounds.size() * 3 * 8);
+    rounds.push_back({false, fr_zero(), v[lK - i - 1]});
+    in_size = out_size;
+    out_size /= 2;
+  }
+  GRAPE_CUDA_TRY(ctx, cudaGetLastError());
+  return GRAPE_OK;
+}
+
+// Sharded finish: adds the per-rank round sums (mod r) and lays the per-rank folded values out as
+// the two length-P vectors the last log2(P) rounds run over.  One block.
+//   gathered: [P][stride] field elements, stride = 3 * local_rounds + 2
+__global__ void __launch_bounds__(RT) k_gather_reduce(const uint32_t* __restrict__ gathered, uint32_t P,
+                                                      uint32_t local_rounds, uint32_t* __restrict__ sums,
+                                                      uint32_t* __restrict__ a_, uint32_t* __restrict__ b_) {
+  const uint32_t stride = 3 * local_rounds + 2;
+  for (uint32_t s = threadIdx.x; s < 3 * local_rounds; s += RT) {
+    Fr acc = Fr::load_nc(gathered + (uint64_t)s * 8);
+    for (uint32_t r = 1; r < P; r++) acc = fe_add(acc, Fr::load_nc(gathered + ((uint64_t)r * stride + s) * 8));
+    acc.store(sums + (uint64_t)s * 8);
+  }
+  for (uint32_t r = threadIdx.x; r < P; r += RT) {
+    Fr::load_nc(gathered + ((uint64_t)r * stride + 3 * local_rounds) * 8).store(a_ + (uint64_t)r * 8);
+    Fr::load_nc(gathered + ((uint64_t)r * stride + 3 * local_rounds + 1) * 8).store(b_ + (uint64_t)r * 8);
+  }
+}
+
+}  // namespace grape
+
 using namespace grape;
 
 // prove_matmul (src/prove.cu:175-210).  d_A = [L][N][K], d_B = [L][M][K] Fr tensors; both are
@@ -260,57 +346,99 @@ extern "C" int grape_prove_matmul(grape_ctx* ctx, void* d_A, void* d_B, uint32_t
                                   void* h_claim, void* h_out_claims, void* h_transcript,
                                   uint32_t transcript_capacity, uint32_t* n_rounds) {
   if (!ctx || !d_A || !d_B || !h_u || !h_v || !h_claim || !h_out_claims) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
-  if (!L || !N || !M || !K) return fail(ctx, GRAPE_ERR_INVALID, "prove_matmul: zero dimension");
-  const uint32_t lL = log2ceil(L), lN = log2ceil(N), lM = log2ceil(M), lK = log2ceil(K);
-  if ((1u << lL) != L) return fail(ctx, GRAPE_ERR_INVALID, "prove_matmul: L must be a power of two");
+  MatmulRun run;
+  int rc = matmul_enqueue(ctx, d_A, d_B, L, N, M, K, reinterpret_cast<const HostFr*>(h_u), n_u,
+                          reinterpret_cast<const HostFr*>(h_v), n_v, run);
+  if (rc) return rc;
+  std::vector<HostFr> transcript;
+  rc = finish_two(ctx, run.rounds, run.sums, run.a_, run.b_, reinterpret_cast<HostFr*>(h_claim),
+                  reinterpret_cast<HostFr*>(h_out_claims), &transcript, "prove_matmul");
+  if (n_rounds) *n_rounds = (uint32_t)(transcript.size() / 4);
+  if (h_transcript) {
+    size_t n = std::min<size_t>(transcript.size(), (size_t)transcript_capacity * 4);
+    memcpy(h_transcript, transcript.data(), n * 32);
+  }
+  return rc;
+}
+
+// ---- prove_matmul split over P provers --------------------------------------------------------
+// The inner dimension is dealt to P = 2^p provers by residue class: prover r holds the columns
+// k = k' * P + r of A and B as dense [L][N][K/P] and [L][M][K/P] tensors.  The reference folds the
+// most significant variable first, so every round over the top log2(K) - p variables pairs elements
+// that live on the same prover: each prover runs those rounds alone on its shard (all challenges
+// are inputs) and produces per-round PARTIAL sums; the true round sums are the sums of the partials
+// over the provers.  One exchange -- (3 * local_rounds + 2) field elements per prover, gathered to
+// everyone -- replaces any per-round communication; the last p rounds run over the P gathered
+// folded values.  The transcript is bit-identical to grape_prove_matmul on the unsharded tensors.
+//
+// Step 1 (every prover): enqueue the local rounds on the shard and leave, in d_part (device memory
+// of this prover, (3 * local_rounds + 2) * 32 bytes), the partial sums followed by the shard's fully
+// folded A and B values.  h_v_local is v without its lowest p entries.  Asynchronous on the
+// context's stream; *local_rounds = log2(L) + log2ceil(K_local).
+extern "C" int grape_prove_matmul_partial(grape_ctx* ctx, void* d_A_shard, void* d_B_shard, uint32_t L, uint32_t N,
+                                          uint32_t M, uint32_t K_local, const void* h_u, uint32_t n_u,
+                                          const void* h_v_local, uint32_t n_v_local, void* d_part,
+                                          uint32_t* local_rounds) {
+  if (!ctx || !d_A_shard || !d_B_shard || !h_u || !h_v_local || !d_part)
+    return fail(ctx, GRAPE_ERR_INVALID, "null argument");
+  MatmulRun run;
+  int rc = matmul_enqueue(ctx, d_A_shard, d_B_shard, L, N, M, K_local, reinterpret_cast<const HostFr*>(h_u), n_u,
+                          reinterpret_cast<const HostFr*>(h_v_local), n_v_local, run);
+  if (rc) return rc;
+  const size_t nr = run.rounds.size();
+  char* out = reinterpret_cast<char*>(d_part);
+  if (nr) GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(out, run.sums, nr * 96, cudaMemcpyDeviceToDevice, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(out + nr * 96, run.a_, 32, cudaMemcpyDeviceToDevice, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(out + nr * 96 + 32, run.b_, 32, cudaMemcpyDeviceToDevice, ctx->stream));
+  if (local_rounds) *local_rounds = (uint32_t)nr;
+  return GRAPE_OK;
+}
+
+// Step 2 (any prover that holds the gathered buffer): d_gathered = the P provers' d_part buffers in
+// rank order.  Reduces the partial sums on the device, runs the last log2(P) rounds over the
+// gathered folded values, then the host pass of grape_prove_matmul (round checks, claims,
+// transcript).  N, M, K are the full dimensions; h_u, h_v, h_claim as in grape_prove_matmul.
+extern "C" int grape_prove_matmul_finish(grape_ctx* ctx, const void* d_gathered, uint32_t P, uint32_t L, uint32_t N,
+                                         uint32_t M, uint32_t K, const void* h_u, uint32_t n_u, const void* h_v,
+                                         uint32_t n_v, void* h_claim, void* h_out_claims, void* h_transcript,
+                                         uint32_t transcript_capacity, uint32_t* n_rounds) {
+  if (!ctx || !d_gathered || !h_u || !h_v || !h_claim || !h_out_claims) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
+  if (!P || !L || !N || !M || !K) return fail(ctx, GRAPE_ERR_INVALID, "prove_matmul_finish: zero dimension");
+  const uint32_t lP = log2ceil(P), lL = log2ceil(L), lK = log2ceil(K);
+  if ((1u << lP) != P || (1u << lL) != L) return fail(ctx, GRAPE_ERR_INVALID, "prove_matmul_finish: P and L must be powers of two");
+  if (K % P != 0 || lK < lP) return fail(ctx, GRAPE_ERR_INVALID, "prove_matmul_finish: P must divide K");
   const uint32_t u_end = log2ceil((uint64_t)L * N * M), v_end = log2ceil((uint64_t)L * K);
-  if (n_u < u_end || n_u < lM + lN + lL || n_v < v_end || n_v < lK)
-    return fail(ctx, GRAPE_ERR_INVALID, "prove_matmul: challenge vectors too short");
+  if (n_u < u_end || n_v < v_end || n_v < lK)
+    return fail(ctx, GRAPE_ERR_INVALID, "prove_matmul_finish: challenge vectors too short");
   const HostFr* u = reinterpret_cast<const HostFr*>(h_u);
   const HostFr* v = reinterpret_cast<const HostFr*>(h_v);
+  const uint32_t local_rounds = lL + (lK - lP);
   arena_reset(ctx);
-  uint32_t *d_u, *d_v, *a_, *b_, *partial, *sums, *wl;
+  uint32_t *d_v, *a_, *b_, *partial, *sums;
   int rc;
-  if ((rc = upload_fr(ctx, u, n_u, &d_u))) return rc;
   if ((rc = upload_fr(ctx, v, n_v, &d_v))) return rc;
-  const uint64_t LK = (uint64_t)L * K;
-  if ((rc = arena_alloc_t(ctx, LK * 8, &a_))) return rc;
-  if ((rc = arena_alloc_t(ctx, LK * 8, &b_))) return rc;
-  const uint32_t total_rounds = lL + lK;
+  if ((rc = arena_alloc_t(ctx, (size_t)P * 8 + 8, &a_))) return rc;
+  if ((rc = arena_alloc_t(ctx, (size_t)P * 8 + 8, &b_))) return rc;
   if ((rc = arena_alloc_t(ctx, (size_t)ctx->sm_count * 4 * 3 * 8 + 64, &partial))) return rc;
-  if ((rc = arena_alloc_t(ctx, (size_t)(total_rounds + 1) * 3 * 8, &sums))) return rc;
-  if ((rc = arena_alloc_t(ctx, (size_t)L * 8 + 8, &wl))) return rc;
-  // a_[l][k] = sum_n eq(u_N, n) A[l][n][k],  b_[l][k] = sum_m eq(u_M, m) B[l][m][k]
-  if ((rc = fold_axis_async<false>(ctx, d_A, (uint64_t)L * N * K, d_u + (size_t)lM * 8, N, K, a_))) return rc;
-  if ((rc = fold_axis_async<false>(ctx, d_B, (uint64_t)L * M * K, d_u, M, K, b_))) return rc;
-
+  if ((rc = arena_alloc_t(ctx, (size_t)(lL + lK + 1) * 3 * 8, &sums))) return rc;
+  k_gather_reduce<<<1, RT, 0, ctx->stream>>>(reinterpret_cast<const uint32_t*>(d_gathered), P, local_rounds, sums, a_, b_);
+  ctx->launches += 1;
   std::vector<RoundInfo> rounds;
-  uint64_t in_size = LK, out_size = LK / 2;
-  const uint32_t u_l0 = u_end - lL;
-  for (uint32_t i = 0; i < lL; i++) {  // phase 1: layer variables, top first
-    const uint32_t rem_layers = (uint32_t)(out_size / K);
-    eq_weights_async(ctx, d_u + (size_t)u_l0 * 8, log2ceil(rem_layers), rem_layers, wl);
-    PairWeights pw{wl, nullptr, K};
-    launch_round_two<true, false>(ctx, a_, b_, in_size, out_size, d_v + (size_t)(v_end - i - 1) * 8, pw, partial,
-                                  sums + (size_t)rounds.size() * 3 * 8);
-    rounds.push_back({true, u[u_end - i - 1], v[v_end - i - 1]});
-    in_size = out_size;
-    out_size /= 2;
-  }
-  in_size = K;
-  out_size = lK ? (uint64_t(1) << (lK - 1)) : 0;
-  for (uint32_t i = 0; i < lK; i++) {  // phase 2: inner-product variables, top first
+  for (uint32_t i = 0; i < lL; i++) rounds.push_back({true, u[u_end - i - 1], v[v_end - i - 1]});
+  for (uint32_t i = 0; i < lK - lP; i++) rounds.push_back({false, fr_zero(), v[lK - i - 1]});
+  uint64_t in_size = P, out_size = P / 2;
+  for (uint32_t i = 0; i < lP; i++) {  // the variables that index the provers
     PairWeights pw{nullptr, nullptr, 1};
-    launch_round_two<false, false>(ctx, a_, b_, in_size, out_size, d_v + (size_t)(lK - i - 1) * 8, pw, partial,
+    launch_round_two<false, false>(ctx, a_, b_, in_size, out_size, d_v + (size_t)(lP - i - 1) * 8, pw, partial,
                                    sums + (size_t)rounds.size() * 3 * 8);
-    rounds.push_back({false, fr_zero(), v[lK - i - 1]});
+    rounds.push_back({false, fr_zero(), v[lP - i - 1]});
     in_size = out_size;
     out_size /= 2;
   }
   GRAPE_CUDA_TRY(ctx, cudaGetLastError());
   std::vector<HostFr> transcript;
   rc = finish_two(ctx, rounds, sums, a_, b_, reinterpret_cast<HostFr*>(h_claim), reinterpret_cast<HostFr*>(h_out_claims),
-                  &transcript, "prove_matmul");
+                  &transcript, "prove_matmul (sharded)");
   if (n_rounds) *n_rounds = (uint32_t)(transcript.size() / 4);
   if (h_transcript) {
     size_t n = std::min<size_t>(transcript.size(), (size_t)transcript_capacity * 4);

@@ -375,6 +375,41 @@ def prove_matmul(ctx: Context, d_A, d_B, L: int, N: int, M: int, K: int, u, v, c
     return a, b, decode_field(hc)[0], polys
 
 
+def matmul_partial_elems(L: int, K_local: int) -> int:
+    """Field elements one prover contributes to the exchange of the sharded ``prove_matmul``."""
+    rounds = max(L - 1, 0).bit_length() + max(K_local - 1, 0).bit_length()
+    return 3 * rounds + 2
+
+
+def prove_matmul_partial(ctx: Context, d_A_shard, d_B_shard, L: int, N: int, M: int, K_local: int, u, v_local, d_part):
+    """Step 1 of the sharded ``prove_matmul``: the local rounds on this prover's shard (columns
+    k = k' * P + rank of A and B).  Writes ``matmul_partial_elems(L, K_local)`` field elements to the
+    device buffer ``d_part`` (a DeviceBuffer or a raw device address); asynchronous.  Both shards are consumed."""
+    hu, hv = _fr_host(u), _fr_host(v_local)
+    nr = C.c_uint32()
+    ctx._check(ctx.lib.grape_prove_matmul_partial(ctx.handle, _p(d_A_shard), _p(d_B_shard), L, N, M, K_local,
+                                                  hu.ctypes.data, len(u), hv.ctypes.data, len(v_local), _p(d_part),
+                                                  C.byref(nr)))
+    return nr.value
+
+
+def prove_matmul_finish(ctx: Context, d_gathered, P: int, L: int, N: int, M: int, K: int, u, v, claim: int):
+    """Step 2 of the sharded ``prove_matmul`` over the P provers' gathered buffers (rank order):
+    same return value as :func:`prove_matmul`."""
+    hu, hv = _fr_host(u), _fr_host(v)
+    hc = _fr_host([claim])
+    out = np.zeros((2, 8), dtype=np.uint32)
+    cap = len(u) + len(v) + 4
+    tr = np.zeros((cap, 4, 8), dtype=np.uint32)
+    nr = C.c_uint32()
+    ctx._check(ctx.lib.grape_prove_matmul_finish(ctx.handle, _p(d_gathered), P, L, N, M, K, hu.ctypes.data, len(u),
+                                                 hv.ctypes.data, len(v), hc.ctypes.data, out.ctypes.data,
+                                                 tr.ctypes.data, cap, C.byref(nr)))
+    a, b = decode_field(out)
+    polys = [decode_field(tr[i]) for i in range(nr.value)]
+    return a, b, decode_field(hc)[0], polys
+
+
 def prove_elemul(ctx: Context, d_A, d_B, L: int, M: int, N: int, u, v, claim: int):
     hu, hv = _fr_host(u), _fr_host(v)
     hc = _fr_host([claim])

@@ -4,6 +4,10 @@ Hyrax rows (and whole layers) are independent, so ranks need no data-path collec
 commits a contiguous block of rows with the generator table replicated in its own HBM, and only the
 96-byte row commitments are gathered (``torch.distributed`` all-gather; NCCL on GPUs, gloo in the
 CPU tests).  Timing across ranks is the maximum of the per-rank device times.
+
+The matrix-product sumcheck can also be split: the inner dimension is dealt to the ranks by residue
+class, every rank runs the rounds that stay inside its shard, and a single small all-gather carries
+the per-round partial sums (``prove_matmul_sharded``).
 """
 from __future__ import annotations
 
@@ -53,6 +57,57 @@ def commit_rows_sharded(scalars: np.ndarray, wd: int, commit_fn, dist=None, devi
     s, e = row_block(rows, rank, world)
     local = commit_fn(scalars[s * wd:e * wd]) if e > s else np.zeros((0, 24), dtype=np.uint32)
     return gather_rows(local, rows, dist, device)
+
+
+def shard_columns(t: np.ndarray, K: int, rank: int, world: int) -> np.ndarray:
+    """Residue-class shard of the last axis: ``t`` viewed as [..., K] -> the columns k = k' * world +
+    rank, contiguous.  This is how the inner dimension of a matrix product is dealt to the provers
+    of the sharded ``prove_matmul``."""
+    if K % world:
+        raise ValueError("the number of provers must divide the inner dimension")
+    return np.ascontiguousarray(np.asarray(t).reshape(-1, K)[:, rank::world])
+
+
+def gather_partials(part, dist=None):
+    """All-gather of one small per-rank buffer into [world, n], in rank order.  A CUDA torch tensor is
+    gathered in place on the GPU (NCCL over NVLink); a numpy uint32 array goes through the process
+    group's CPU path (gloo)."""
+    if dist is None or dist.get_world_size() == 1:
+        return part.reshape(1, -1)
+    import torch
+    world = dist.get_world_size()
+    if isinstance(part, torch.Tensor):
+        out = torch.empty((world, part.numel()), dtype=part.dtype, device=part.device)
+        dist.all_gather_into_tensor(out, part.reshape(-1))
+        return out
+    flat = np.ascontiguousarray(part, dtype=np.uint32).reshape(-1)
+    mine = torch.from_numpy(flat.astype(np.int64))
+    parts = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(parts, mine)
+    return np.stack([p.numpy().astype(np.uint32) for p in parts])
+
+
+def prove_matmul_sharded(ctx, d_A_shard, d_B_shard, L: int, N: int, M: int, K: int, u, v, claim: int, dist=None):
+    """``prove_matmul`` with the inner dimension dealt to the ranks by residue class (this rank holds
+    ``shard_columns(A, K, rank, world)`` as an Fr tensor on its GPU).  Each rank folds its shard and
+    runs the local rounds, ONE all-gather of a few hundred bytes per rank crosses NVLink, and every
+    rank finishes the proof (partial sums added mod r on the device, last log2(world) rounds, round
+    checks).  Returns what ``host.prove_matmul`` returns, bit-identical to the unsharded proof."""
+    import torch
+    from . import host
+    world = 1 if dist is None else dist.get_world_size()
+    if world & (world - 1) or K % world:
+        raise ValueError("the number of ranks must be a power of two that divides the inner dimension")
+    lp = world.bit_length() - 1
+    k_local = K // world
+    n_el = host.matmul_partial_elems(L, k_local)
+    device = torch.device("cuda", torch.cuda.current_device())
+    part = torch.empty(n_el * 8, dtype=torch.int32, device=device)
+    host.prove_matmul_partial(ctx, d_A_shard, d_B_shard, L, N, M, k_local, u, list(v)[lp:], part.data_ptr())
+    ctx.sync()                                   # the library's stream -> visible to the collective
+    gathered = gather_partials(part, dist)
+    torch.cuda.current_stream().synchronize()    # the collective -> visible to the library's stream
+    return host.prove_matmul_finish(ctx, gathered.data_ptr(), world, L, N, M, K, u, v, claim)
 
 
 def max_over_ranks(value: float, dist=None, device: str = "cpu") -> float:

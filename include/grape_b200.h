@@ -167,6 +167,28 @@ int grape_prove_matmul(grape_ctx* ctx, void* d_A, void* d_B, uint32_t L, uint32_
                        const void* h_u, uint32_t n_u, const void* h_v, uint32_t n_v, void* h_claim,
                        void* h_out_claims, void* h_transcript, uint32_t transcript_capacity,
                        uint32_t* n_rounds);
+
+/* prove_matmul split over P = 2^p provers (GPUs), one exchange in total.  No reference counterpart:
+ * the reference proves on one GPU (src/prove.cu:175-210); the result and the transcript are
+ * bit-identical to grape_prove_matmul on the unsharded tensors.
+ *   Sharding: prover r holds the inner-dimension columns k = k'*P + r of A and B as dense
+ *   [L][N][K/P] and [L][M][K/P] Fr tensors (P must divide K).  The rounds over the top
+ *   log2ceil(K) - p inner variables, and the layer variables before them, never pair elements of
+ *   different provers, and all challenges are inputs, so each prover runs them alone.
+ *   grape_prove_matmul_partial (every prover, asynchronous on the context's stream): writes
+ *   (3*local_rounds + 2) field elements to d_part (device memory): per-round partial sums, then the
+ *   shard's fully folded A and B values.  h_v_local = v without its p lowest entries.
+ *   The caller gathers the P d_part buffers in rank order (e.g. an NCCL all-gather) into d_gathered.
+ *   grape_prove_matmul_finish: adds the partial sums mod r on the device, runs the last p rounds
+ *   over the P folded values, then checks every round (GRAPE_ERR_CHECK) and returns the claims and
+ *   the transcript exactly as grape_prove_matmul does. */
+int grape_prove_matmul_partial(grape_ctx* ctx, void* d_A_shard, void* d_B_shard, uint32_t L, uint32_t N,
+                               uint32_t M, uint32_t K_local, const void* h_u, uint32_t n_u,
+                               const void* h_v_local, uint32_t n_v_local, void* d_part, uint32_t* local_rounds);
+int grape_prove_matmul_finish(grape_ctx* ctx, const void* d_gathered, uint32_t P, uint32_t L, uint32_t N,
+                              uint32_t M, uint32_t K, const void* h_u, uint32_t n_u, const void* h_v,
+                              uint32_t n_v, void* h_claim, void* h_out_claims, void* h_transcript,
+                              uint32_t transcript_capacity, uint32_t* n_rounds);
 /* prove_eleMul (src/prove.cu:212-241; eleMul_sumcheck :119-172).  d_A, d_B = [L*M][N]. */
 int grape_prove_elemul(grape_ctx* ctx, void* d_A, void* d_B, uint32_t L, uint32_t M, uint32_t N,
                        const void* h_u, uint32_t n_u, const void* h_v, uint32_t n_v, void* h_claim,

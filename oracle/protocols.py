@@ -219,6 +219,83 @@ def prove_matmul(A, B, L, N, M, K, u, v, claim):
     return A[0], B[0], claim, transcript
 
 
+def prove_matmul_partial(A, B, L, N, M, K_local, u, v_local):
+    """One prover's share of ``prove_matmul`` when the inner dimension is dealt to P = 2^p provers by
+    residue class (prover r holds the columns k = k' * P + r).  Not a reference function: the
+    reference proves on one GPU.  Because it folds the most significant variable first
+    (src/prove.cu:29-46 pairs g with g + out_size), the rounds over the layer variables and over
+    the top log2(K) - p inner variables pair elements of the same residue class, so they run on
+    each shard alone and the round sums are the sums of the per-shard values returned here.
+
+    ``v_local`` is v without its p lowest entries.  Returns ``(sums, a, b)``: per local round the
+    three raw sums (constant, linear, quadratic -- before the eq factors, which are common to all
+    shards) and the shard's fully folded values.
+    """
+    A = partial_eval(list(A), len(A), u, N, log2ceil(M), K_local)
+    B = partial_eval(list(B), len(B), u, M, 0, K_local)
+    u_end = log2ceil(L * N * M)
+    v_end = log2ceil(L * K_local)
+    sums = []
+    size = K_local * L
+    rounds = log2ceil(L)
+    in_size, out_size = size, size // 2
+    u_l0 = u_end - rounds
+    for i in range(rounds):
+        a, b, c = _split2(A, B, in_size, out_size, v_local[v_end - i - 1])
+        a = partial_eval(a, out_size, u[u_l0:], out_size // K_local, 0, K_local)
+        b = partial_eval(b, out_size, u[u_l0:], out_size // K_local, 0, K_local)
+        c = partial_eval(c, out_size, u[u_l0:], out_size // K_local, 0, K_local)
+        sums.append([sum(c[:K_local]) % R, sum(b[:K_local]) % R, sum(a[:K_local]) % R])
+        in_size, out_size = out_size, out_size // 2
+    rounds = log2ceil(K_local)
+    in_size = K_local
+    out_size = 1 << (rounds - 1) if rounds else 0
+    for i in range(rounds):
+        a, b, c = _split2(A, B, in_size, out_size, v_local[rounds - i - 1])
+        sums.append([sum(c) % R, sum(b) % R, sum(a) % R])
+        in_size, out_size = out_size, out_size // 2
+    return sums, A[0], B[0]
+
+
+def prove_matmul_finish(parts, L, N, M, K, u, v, claim):
+    """Combines the P provers' ``prove_matmul_partial`` results (rank order) into the proof:
+    adds the partial sums, runs the last log2(P) rounds over the P folded values, applies the eq
+    factors and the reference's round checks.  Returns what ``prove_matmul`` returns."""
+    P = len(parts)
+    lP, lL, lK = log2ceil(P), log2ceil(L), log2ceil(K)
+    assert (1 << lP) == P and K % P == 0
+    u_end = log2ceil(L * N * M)
+    v_end = log2ceil(L * K)
+    local_rounds = lL + lK - lP
+    assert all(len(p[0]) == local_rounds for p in parts)
+    raw = [[sum(p[0][i][k] for p in parts) % R for k in range(3)] for i in range(local_rounds)]
+    A = [p[1] for p in parts]
+    B = [p[2] for p in parts]
+    in_size, out_size = P, P // 2
+    for i in range(lP):
+        a, b, c = _split2(A, B, in_size, out_size, v[lP - i - 1])
+        raw.append([sum(c) % R, sum(b) % R, sum(a) % R])
+        in_size, out_size = out_size, out_size // 2
+    transcript = []
+    eq_acc = 1
+    for i, q in enumerate(raw):
+        if i < lL:
+            u_now, v_now = u[u_end - i - 1], v[v_end - i - 1]
+            p = poly_mul(q, poly_scale(poly_eq(u_now), eq_acc))
+        else:
+            v_now = v[lK - (i - lL) - 1]
+            p = [x * eq_acc % R for x in q]
+        transcript.append(p)
+        if poly_at01(p) != claim % R:
+            raise RuntimeError("prove_matmul (sharded): claim != p(0) + p(1)")
+        claim = poly_eval(p, v_now)
+        if i < lL:
+            eq_acc = eq_acc * eq2(u_now, v_now) % R
+    if A[0] * B[0] * eq_acc % R != claim:
+        raise AssertionError("prove_matmul (sharded): final identity failed")
+    return A[0], B[0], claim, transcript
+
+
 def reassemble_vectors(first, second, first_size, same_size, last_size):
     """``ReassembleVectors`` (src/ec_operation.cu:74-122): returns the new (first, second)."""
     r1 = second[:same_size] + first[last_size:last_size + first_size] + second[same_size:]

@@ -87,3 +87,53 @@ def test_combine_claims(gctx, nv, k):
     got_ret, got_tr = host.combine_claims(gctx, gctx.fr_upload(X), size, claims, us, v)
     assert got_ret == want_ret == _mle(X, v)
     assert got_tr == _pad4(want_tr)
+
+
+@pytest.mark.parametrize("L,N,M,K,P", [(1, 4, 8, 8, 2), (2, 4, 2, 24, 4), (4, 2, 4, 88, 8), (1, 16, 8, 2048, 8), (1, 3, 8, 44, 4), (2, 2, 2, 8, 8)])
+def test_sharded_prove_matmul_equals_unsharded(gctx, L, N, M, K, P):
+    """The inner dimension dealt to P provers by residue class.  The provers run one after another on
+    this GPU (their kernels never wait on each other); their buffers are concatenated in rank order
+    in place of the all-gather.  Claims and transcript must equal the single-prover proof bit for bit."""
+    import numpy as np
+    import grape_b200 as g
+    from grape_b200 import host
+    rng = random.Random(L * 1000 + N * 100 + M * 10 + K + P)
+    draw = bn254.SplitMix64(K + P, 5)
+    A = [rng.randrange(-2**15, 2**15) % R for _ in range(L * N * K)]
+    B = [rng.randrange(-2**15, 2**15) % R for _ in range(L * M * K)]
+    u = draw.fr_vec(pr.log2ceil(L * N * M))
+    v = draw.fr_vec(pr.log2ceil(L * K))
+    a_ = pr.partial_eval(list(A), len(A), u, N, pr.log2ceil(M), K)
+    b_ = pr.partial_eval(list(B), len(B), u, M, 0, K)
+    lL, u_end = pr.log2ceil(L), pr.log2ceil(L * N * M)
+    w = pr.eq_weights(u[u_end - lL:u_end], lL, L)
+    claim = sum(w[l] * a_[l * K + k] * b_[l * K + k] for l in range(L) for k in range(K)) % R
+    single = host.prove_matmul(gctx, gctx.fr_upload(A), gctx.fr_upload(B), L, N, M, K, u, v, claim)
+    want = pr.prove_matmul(A, B, L, N, M, K, u, v, claim)
+    assert single[:3] == want[:3] and single[3] == _pad4(want[3])
+
+    lp = P.bit_length() - 1
+    n_el = host.matmul_partial_elems(L, K // P)
+    gathered = gctx.alloc(P * n_el * 32)
+    Aenc = host.encode_field(A)
+    Benc = host.encode_field(B)
+    for r in range(P):
+        As = np.ascontiguousarray(Aenc.reshape(-1, K, 8)[:, r::P, :])
+        Bs = np.ascontiguousarray(Benc.reshape(-1, K, 8)[:, r::P, :])
+        rounds = host.prove_matmul_partial(gctx, gctx.upload(As), gctx.upload(Bs), L, N, M, K // P, u, v[lp:],
+                                           gathered.at(r * n_el * 32))
+        assert 3 * rounds + 2 == n_el
+    got = host.prove_matmul_finish(gctx, gathered, P, L, N, M, K, u, v, claim)
+    assert got[:3] == single[:3] and got[3] == single[3]
+    # the gathered partial sums are the oracle's
+    raw = gctx.download(gathered, P * n_el * 32).tobytes()
+    for r in range(P):
+        Asl = [A[(l * N + n) * K + k] for l in range(L) for n in range(N) for k in range(r, K, P)]
+        Bsl = [B[(l * M + m) * K + k] for l in range(L) for m in range(M) for k in range(r, K, P)]
+        sums, fa, fb = pr.prove_matmul_partial(Asl, Bsl, L, N, M, K // P, u, v[lp:])
+        vals = bn254.fr_vec_from_bytes(raw[r * n_el * 32:(r + 1) * n_el * 32])
+        assert vals == [x for q3 in sums for x in q3] + [fa, fb]
+    # a wrong claim fails the round check
+    with pytest.raises(g.GrapeError) as e:
+        host.prove_matmul_finish(gctx, gathered, P, L, N, M, K, u, v, (claim + 1) % R)
+    assert e.value.code == 3

@@ -108,3 +108,31 @@ def test_hyrax_open_verifies():
     assert pr.hyrax_verify(com, proof, e, c, size, N, layer_num, gens, gens[0])
     proof["z"][0] = (proof["z"][0] + 1) % R
     assert not pr.hyrax_verify(com, proof, e, c, size, N, layer_num, gens, gens[0])
+
+
+@pytest.mark.parametrize("L,N,M,K,P", [(1, 4, 4, 8, 2), (2, 3, 4, 8, 4), (1, 2, 2, 12, 4), (4, 2, 3, 8, 8), (1, 2, 2, 24, 8)])
+def test_sharded_matmul_sumcheck_equals_the_unsharded_one(L, N, M, K, P):
+    """The inner dimension dealt to P provers by residue class: local rounds + one exchange + the last
+    log2(P) rounds give the reference prover's transcript and claims, bit for bit."""
+    import random
+    rnd = random.Random(L * 1000 + K * 10 + P)
+    A = [rnd.randrange(-50, 50) % R for _ in range(L * N * K)]
+    B = [rnd.randrange(-50, 50) % R for _ in range(L * M * K)]
+    u = [rnd.randrange(R) for _ in range(pr.log2ceil(L * N * M) + 1)]
+    v = [rnd.randrange(R) for _ in range(pr.log2ceil(L * K))]
+    a_ = pr.partial_eval(list(A), len(A), u, N, pr.log2ceil(M), K)
+    b_ = pr.partial_eval(list(B), len(B), u, M, 0, K)
+    lL, u_end = pr.log2ceil(L), pr.log2ceil(L * N * M)
+    w = pr.eq_weights(u[u_end - lL:u_end], lL, L)
+    claim = sum(w[l] * a_[l * K + k] * b_[l * K + k] for l in range(L) for k in range(K)) % R
+    want = pr.prove_matmul(A, B, L, N, M, K, u, v, claim)
+    lp = pr.log2ceil(P)
+    parts = []
+    for r in range(P):
+        As = [A[(l * N + n) * K + k] for l in range(L) for n in range(N) for k in range(r, K, P)]
+        Bs = [B[(l * M + m) * K + k] for l in range(L) for m in range(M) for k in range(r, K, P)]
+        parts.append(pr.prove_matmul_partial(As, Bs, L, N, M, K // P, u, v[lp:]))
+    assert pr.prove_matmul_finish(parts, L, N, M, K, u, v, claim) == want
+    # a wrong claim is rejected by the round check, as in the reference
+    with pytest.raises(RuntimeError):
+        pr.prove_matmul_finish(parts, L, N, M, K, u, v, (claim + 1) % R)
