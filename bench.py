@@ -53,7 +53,7 @@ def parse_args():
                     help="also time the proof of this many decoder layers (one batch, seq 2048)")
     ap.add_argument("--proof-window-bits", type=int, default=13)
     ap.add_argument("--proof-scope", default="layer", choices=["layer", "ffn"])
-    ap.add_argument("--workload", default="commit", choices=["commit", "matmul", "lookup", "commit-bls12-381"],
+    ap.add_argument("--workload", default="commit", choices=["commit", "matmul", "lookup", "commit-bls12-381", "matmul-sharded"],
                     help="commit = C4 (the headline); matmul = C2 prove_matmul; lookup = C3 range lookup")
     ap.add_argument("--shrink", type=int, default=1, help="divide the matmul / lookup sizes (profiling cases)")
     ap.add_argument("--rows", type=int, default=0, help="commit only this many rows (reduced case for profiling)")
@@ -545,10 +545,95 @@ def run_secondary(args):
     print(json.dumps(line))
 
 
+def run_matmul_sharded(args):
+    """C2 with the inner dimension dealt to the ranks by residue class (one rank per GPU under
+    torchrun): per-rank folds and local rounds, one NCCL all-gather of the partial sums, finish on
+    every rank.  Tensors are born sharded (each rank synthesises its own columns)."""
+    import torch
+    import grape_b200 as g
+    from grape_b200 import host, parallel, workloads as wl
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = g.Context(local_rank)
+    L, N, M, K = 1, 2048 // args.shrink, 4096 // args.shrink, 4096
+    kl = K // world
+    rng = np.random.default_rng(0xC2 + rank)
+    A = wl.quantised_normal(rng, N * kl, lo=-2**31, hi=2**31 - 1)
+    B = wl.quantised_normal(rng, M * kl, lo=-2**31, hi=2**31 - 1)
+    dAi, dBi = ctx.upload(A), ctx.upload(B)
+    dA, dB = ctx.alloc(N * kl * 32), ctx.alloc(M * kl * 32)
+    ctx.seed(0xC2)
+    lM, lN, lK = (M - 1).bit_length(), (N - 1).bit_length(), (K - 1).bit_length()
+    u = host.decode_field(ctx.random_fr(lM + lN))
+    v = host.decode_field(ctx.random_fr(lK))
+    # the claim: sum over ranks of <fold(A_r), fold(B_r)>, all-reduced as integers on the host side
+    du = ctx.fr_upload(u)
+    a_, b_, one = ctx.alloc(kl * 32), ctx.alloc(kl * 32), ctx.alloc(32)
+    ctx.fr_from_i32(dAi, N * kl, dA)
+    ctx.fr_from_i32(dBi, M * kl, dB)
+    ctx.fr_fold(dA, N * kl, du.at(lM * 32), N, kl, a_)
+    ctx.fr_fold(dB, M * kl, du, M, kl, b_)
+    ctx.fr_binary("mul", a_, b_, a_, kl)
+    ctx.fr_sum(a_, kl, one)
+    mine = ctx.fr_download(one, 1)[0]
+    if dist is not None:
+        words = torch.tensor([(mine >> (32 * i)) & 0xFFFFFFFF for i in range(8)], dtype=torch.int64, device="cuda")
+        allw = [torch.empty_like(words) for _ in range(world)]
+        dist.all_gather(allw, words)
+        claim = sum(sum(int(x) << (32 * i) for i, x in enumerate(w.tolist())) for w in allw) % host.FR_MODULUS
+    else:
+        claim = mine
+
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    times, launches, result = [], 0, None
+    for it in range(args.warmup + args.steps):
+        ctx.fr_from_i32(dAi, N * kl, dA)
+        ctx.fr_from_i32(dBi, M * kl, dB)
+        barrier()
+        l0 = ctx.launches
+        t0 = time.perf_counter()
+        result = parallel.prove_matmul_sharded(ctx, dA, dB, L, N, M, K, u, v, claim, dist)
+        ctx.sync()
+        ms = (time.perf_counter() - t0) * 1e3      # the call synchronises with the host on both sides
+        if it >= args.warmup:
+            times.append(ms)
+            launches += ctx.launches - l0
+    ms = float(np.mean(times))
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        print(json.dumps({"metric": "prove_matmul_ms (inner dimension sharded over the GPUs)", "value": ms, "unit": "ms",
+                          "higher_is_better": False, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+                          "scaling": "strong", "data": "synthetic", "dtype": "u32 limbs (254-bit fields)",
+                          "vs_baseline": None, "gpu_launches": int(launches),
+                          "config": {"workload": f"C2: prove_matmul A {N}x{K} . B {M}x{K}^T, each rank holds K/{world} "
+                                                 f"columns as Fr tensors in HBM; one all-gather of "
+                                                 f"{host.matmul_partial_elems(L, kl) * 32} B per rank",
+                                     "timing": "host wall clock around the call (it synchronises), max over ranks"},
+                          "rounds": len(result[3])}))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "matmul-sharded":
+        run_matmul_sharded(args)
     elif args.workload != "commit":
         run_secondary(args)
     else:
