@@ -53,7 +53,7 @@ def parse_args():
                     help="also time the proof of this many decoder layers (one batch, seq 2048)")
     ap.add_argument("--proof-window-bits", type=int, default=13)
     ap.add_argument("--proof-scope", default="layer", choices=["layer", "ffn"])
-    ap.add_argument("--workload", default="commit", choices=["commit", "matmul", "lookup", "commit-bls12-381", "matmul-sharded"],
+    ap.add_argument("--workload", default="commit", choices=["commit", "matmul", "lookup", "commit-bls12-381", "matmul-sharded", "layer-proof"],
                     help="commit = C4 (the headline); matmul = C2 prove_matmul; lookup = C3 range lookup")
     ap.add_argument("--shrink", type=int, default=1, help="divide the matmul / lookup sizes (profiling cases)")
     ap.add_argument("--rows", type=int, default=0, help="commit only this many rows (reduced case for profiling)")
@@ -236,7 +236,7 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def layer_proof(ctx, layers: int, window_bits: int, scope: str):
+def layer_proof(ctx, layers: int, window_bits: int, scope: str, seed: int = 0xC5):
     """Proof of `layers` LLaMA-2-7B-shaped decoder layers in one batch (seq 2048, dim 4096, ffn 11008) in
     the call order of the reference's end-to-end driver test/llm.cu:73-611.  scope "layer": everything
     (11 matmul sumchecks, 3 Hadamard sumchecks, 14 range and 2 mapping lookups, 3 claim batchings and the
@@ -245,10 +245,10 @@ def layer_proof(ctx, layers: int, window_bits: int, scope: str):
     from grape_b200 import layer, layer_full, workloads as wl
     if scope == "ffn":
         shape = layer.FFNShape(layer_num=layers, tokens=2048, dim=4096, ffn=11008)
-        t = layer.synthesize_ffn(shape, seed=0xC5, x_range=1 << 13, matmul=wl.exact_matmul_cuda)
+        t = layer.synthesize_ffn(shape, seed=seed, x_range=1 << 13, matmul=wl.exact_matmul_cuda)
     else:
         shape = layer_full.LayerShape(layer_num=layers, tokens=2048, dim=4096, ffn=11008)
-        t = layer_full.synthesize_layer(shape, seed=0xC5, x_range=1 << 13, matmul=wl.exact_matmul_cuda)
+        t = layer_full.synthesize_layer(shape, seed=seed, x_range=1 << 13, matmul=wl.exact_matmul_cuda)
     gens = wl.make_generators(ctx, shape.ffn_pad * 16, 0xC5)
     t0 = time.perf_counter()
     table = g.GeneratorTable(ctx, gens, window_bits, 1)
@@ -628,10 +628,46 @@ def run_matmul_sharded(args):
         dist.destroy_process_group()
 
 
+def run_layer_proof(args):
+    """C5: every rank proves its own batch of `--proof-layers` (default 4) decoder layers; the batches
+    of a 32-layer model are independent, so there is no data-path collective (weak scaling).  The
+    reported time per layer is the slowest rank's batch time divided by all the layers proven."""
+    import torch
+    import grape_b200 as g
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = g.Context(local_rank)
+    layers = args.proof_layers or 4
+    if dist is not None:
+        dist.barrier()
+    res = layer_proof(ctx, layers, args.proof_window_bits, args.proof_scope, seed=0xC5 + rank)
+    t = torch.tensor([res["seconds"]], device="cuda", dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    slowest = float(t.item())
+    if rank == 0:
+        print(json.dumps({"metric": "proof_seconds_per_layer", "value": slowest / (layers * world), "unit": "s/layer",
+                          "higher_is_better": False, "n_gpus": world, "steps": 1, "warmup": 1, "scaling": "weak",
+                          "data": "synthetic", "dtype": "u32 limbs (254-bit fields)", "vs_baseline": None,
+                          "config": {"workload": f"C5: {world} batch(es) of {layers} LLaMA-2-7B-shaped decoder layers "
+                                                 f"(seq 2048, dim 4096, ffn 11008), one batch per GPU, scope {args.proof_scope}"},
+                          "slowest_batch_s": slowest, "rank0": res}))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "layer-proof":
+        run_layer_proof(args)
     elif args.workload == "matmul-sharded":
         run_matmul_sharded(args)
     elif args.workload != "commit":
