@@ -13,13 +13,16 @@
 // with 16-bit windows an int16-range scalar is a single digit, i.e. a single addition per pair,
 // at the price of a table of 2^15 rows that lives in HBM rather than in L2.
 //
-//   commit_accumulate:  one WARP per (row, chunk of generators), four warps per block.  A lane
-//                       walks its generators with stride 32 and keeps one XYZZ accumulator; the
-//                       32 accumulators are folded with a shuffle tree (5 general additions,
-//                       amortised over >= 64 mixed additions per lane when rows are long) and
-//                       lane 0 writes the partial sum to scratch memory.
-//   commit_finalize:    one thread per row adds the chunk partials, normalises (one inversion)
-//                       and writes the canonical Jacobian record.
+//   commit_accumulate:  one WARP per (row, window group, chunk of generators), four warps per
+//                       block; a window group is the set of windows the table stores pre-shifted
+//                       (all of them for 16-bit windows over int16 data).  A lane walks its
+//                       generators with stride 32 and keeps one XYZZ accumulator -- it never
+//                       doubles; the 32 accumulators are folded with a shuffle tree (5 general
+//                       additions) and lane 0 writes the partial sum to scratch memory.
+//   commit_finalize:    one thread per row recombines the groups (Horner: window_bits * n_windows
+//                       doublings between groups, paid once per row instead of once per lane),
+//                       adds the chunk partials, normalises (one inversion) and writes the
+//                       canonical Jacobian record.
 #include <algorithm>
 
 #include "ctx.cuh"
@@ -188,15 +191,19 @@ commit_accumulate_kernel(const void* __restrict__ scalars, TableViewT<typename C
   const uint64_t unit = (uint64_t)blockIdx.x * (MSM_THREADS / 32) + (threadIdx.x >> 5);
   if (unit >= n_units) return;  // whole warps leave together
   const uint32_t lane = threadIdx.x & 31;
-  const uint64_t row = unit / n_chunks;
-  const uint32_t chunk = (uint32_t)(unit % n_chunks);
-  const uint32_t i_begin = chunk * chunk_len;
-  const uint32_t i_end = min(wd, i_begin + chunk_len);
   const uint32_t c = tab.window_bits;
   const uint32_t mask = (1u << c) - 1u;
   const uint32_t half = tab.half;
   const uint32_t tw = tab.n_windows;
   const uint32_t groups = (total_windows + tw - 1) / tw;
+  // unit = (row, window group, chunk of generators): no doubling happens here; the finalize kernel
+  // recombines the groups of a row with c * tw doublings between them
+  const uint32_t chunk = (uint32_t)(unit % n_chunks);
+  const uint64_t rg = unit / n_chunks;
+  const uint32_t g = (uint32_t)(rg % groups);
+  const uint64_t row = rg / groups;
+  const uint32_t i_begin = chunk * chunk_len;
+  const uint32_t i_end = min(wd, i_begin + chunk_len);
 
   // bias for the int32 path: 2^(c-1) at every window below the top one
   uint32_t bias32 = 0;
@@ -205,10 +212,7 @@ commit_accumulate_kernel(const void* __restrict__ scalars, TableViewT<typename C
   }
 
   Xyzz acc = Xyzz::inf();
-  for (int g = (int)groups - 1; g >= 0; g--) {
-    if (g != (int)groups - 1) {
-      for (uint32_t k = 0; k < c * tw; k++) acc = xyzz_dbl(acc);
-    }
+  {
     const uint32_t w_lo = g * tw;
     const uint32_t w_hi = min(total_windows, w_lo + tw);
     for (uint32_t i = i_begin + lane; i < i_end; i += 32) {
@@ -257,17 +261,29 @@ commit_accumulate_kernel(const void* __restrict__ scalars, TableViewT<typename C
   if (lane == 0) acc.store(partials + unit);
 }
 
+// One thread per row: result = sum over window groups g of 2^(group_bits * g) * (sum of the row's
+// chunk partials of group g), evaluated top group first with group_bits doublings in between.
+// partials are laid out [row][group][chunk].
 template <class C>
 __global__ void __launch_bounds__(128) commit_finalize_kernel(const XyzzT<typename C::F>* __restrict__ partials,
-                                                              uint32_t n_chunks, uint64_t rows,
+                                                              uint32_t n_chunks, uint32_t groups,
+                                                              uint32_t group_bits, uint64_t rows,
                                                               JacobianT<typename C::F>* __restrict__ out) {
   using Affine = AffineT<typename C::F>;
   using Xyzz = XyzzT<typename C::F>;
   uint64_t row = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= rows) return;
-  Xyzz acc = Xyzz::load(partials + row * n_chunks);
+  Xyzz acc = Xyzz::inf();
 #pragma unroll 1
-  for (uint32_t k = 1; k < n_chunks; k++) xyzz_add(acc, Xyzz::load(partials + row * n_chunks + k));
+  for (int g = (int)groups - 1; g >= 0; g--) {
+    if (g != (int)groups - 1) {
+#pragma unroll 1
+      for (uint32_t k = 0; k < group_bits; k++) acc = xyzz_dbl(acc);
+    }
+    const Xyzz* p = partials + (row * groups + (uint32_t)g) * n_chunks;
+#pragma unroll 1
+    for (uint32_t k = 0; k < n_chunks; k++) xyzz_add(acc, Xyzz::load(p + k));
+  }
   bool inf = acc.is_inf();
   Affine a = xyzz_to_affine(acc);
   store_jacobian_normalised(out + row, a, inf);
@@ -285,8 +301,9 @@ static int check_table(grape_ctx* ctx, const grape_table* t, uint32_t wd) {
 
 // Picks how many warps share one row: one when there are enough rows to fill the GPU, otherwise
 // enough to reach a few warps per scheduler while leaving every lane at least two generators.
-static uint32_t pick_chunks(const grape_ctx* ctx, uint64_t rows, uint32_t wd) {
+static uint32_t pick_chunks(const grape_ctx* ctx, uint64_t rows, uint32_t wd, uint32_t groups = 1) {
   uint64_t target_warps = (uint64_t)ctx->sm_count * 32;
+  rows *= groups;  // every (row, window group) is a unit of its own
   if (rows >= target_warps) return 1;
   uint64_t want = (target_warps + rows - 1) / rows;
   uint64_t max_chunks = (wd + 63) / 64;
@@ -300,7 +317,8 @@ static int launch_commit(grape_ctx* ctx, const grape_table* t, const void* d_sca
                          uint32_t wd, uint32_t total_windows, XyzzT<typename C::F>* partials,
                          uint32_t n_chunks, void* d_out) {
   uint32_t chunk_len = (wd + n_chunks - 1) / n_chunks;
-  uint64_t units = rows * n_chunks;
+  const uint32_t groups = (total_windows + t->n_windows - 1) / t->n_windows;
+  uint64_t units = rows * groups * n_chunks;
   if (units == 0) return GRAPE_OK;
   uint64_t blocks = (units + MSM_THREADS / 32 - 1) / (MSM_THREADS / 32);
   if (blocks > 0x7fffffffull) return fail(ctx, GRAPE_ERR_LIMIT, "too many commitment rows for one launch");
@@ -311,7 +329,8 @@ static int launch_commit(grape_ctx* ctx, const grape_table* t, const void* d_sca
         ctx->d_status);
   }
   commit_finalize_kernel<C><<<(uint32_t)((rows + 127) / 128), 128, 0, ctx->stream>>>(
-      partials, n_chunks, rows, reinterpret_cast<JacobianT<typename C::F>*>(d_out));
+      partials, n_chunks, groups, t->window_bits * t->n_windows, rows,
+      reinterpret_cast<JacobianT<typename C::F>*>(d_out));
   ctx->launches += 2;
   GRAPE_CUDA_TRY(ctx, cudaGetLastError());
   return GRAPE_OK;
@@ -370,10 +389,11 @@ template <class C>
 static int commit_i32_impl(grape_ctx* ctx, const grape_table* t, const int32_t* d_scalars, uint64_t rows,
                            uint32_t wd, uint32_t max_bits, void* d_out) {
   uint32_t total_windows = (max_bits + t->window_bits - 1) / t->window_bits;
-  uint32_t n_chunks = pick_chunks(ctx, rows, wd);
+  const uint32_t groups = (total_windows + t->n_windows - 1) / t->n_windows;
+  uint32_t n_chunks = pick_chunks(ctx, rows, wd, groups);
   arena_reset(ctx);
   XyzzT<typename C::F>* partials = nullptr;
-  int rc = arena_alloc_t(ctx, rows * n_chunks, &partials);
+  int rc = arena_alloc_t(ctx, rows * groups * n_chunks, &partials);
   if (rc) return rc;
   return launch_commit<C, false>(ctx, t, d_scalars, rows, wd, total_windows, partials, n_chunks, d_out);
 }
@@ -385,10 +405,11 @@ static int commit_fr_impl(grape_ctx* ctx, const grape_table* t, const void* d_sc
                           uint64_t rows, uint32_t wd, void* d_out) {
   uint32_t total_windows = (C::SCALAR_BITS + t->window_bits) / t->window_bits;
   if (C::ID == Bn254::ID) total_windows = (254 + t->window_bits - 1) / t->window_bits;
-  uint32_t n_chunks = pick_chunks(ctx, rows, wd);
+  const uint32_t groups = (total_windows + t->n_windows - 1) / t->n_windows;
+  uint32_t n_chunks = pick_chunks(ctx, rows, wd, groups);
   XyzzT<typename C::F>* partials = nullptr;
   uint32_t* biased = nullptr;
-  int rc = arena_alloc_t(ctx, rows * n_chunks, &partials);
+  int rc = arena_alloc_t(ctx, rows * groups * n_chunks, &partials);
   if (rc) return rc;
   rc = arena_alloc_t(ctx, size * 8, &biased);
   if (rc) return rc;
@@ -551,7 +572,7 @@ extern "C" int grape_commit_i32_host(grape_ctx* ctx, const grape_table* t, const
 // fully handed out to other buffers.  The per-(row, chunk) partial sums that the other entry
 // points keep in the context's scratch arena live here in a fixed array inside the library image.
 // Every GPU that loads the library holds that array (GRAPE_STATIC_SCRATCH_BYTES) until exit.
-constexpr uint64_t STATIC_MAX_UNITS = 65536;  // rows x chunks per call
+constexpr uint64_t STATIC_MAX_UNITS = 65536;  // rows x window groups x chunks per call
 static __device__ __align__(256) unsigned char g_static_partials[STATIC_MAX_UNITS * sizeof(grape::Xyzz)];
 static __device__ __align__(256) uint32_t g_static_status[64];
 
@@ -601,9 +622,10 @@ extern "C" const char* grape_static_error(void) { return g_static_error; }
 // (d_table = grape_table_data, same n_gens / window_bits / n_windows), on the current device
 // and the given stream (NULL = default stream).  It calls no cudaMalloc, cudaFree or any routine
 // that allocates; inputs, outputs and the table are the caller's.
-//   * Limit: (size / wd) * chunks <= 65536 partial sums, where the number of chunks per row is
-//     what fills the GPU when there are few rows; more than 65536 rows is rejected with
-//     GRAPE_ERR_LIMIT (text in grape_static_error()).
+//   * Limit: rows * window groups * chunks <= 65536 partial sums (rows = size / wd, window groups =
+//     ceil(ceil(max_bits / window_bits) / n_windows), chunks = what fills the GPU when there are
+//     few rows); rows * window groups > 65536 is rejected with GRAPE_ERR_LIMIT (text in
+//     grape_static_error()).
 //   * The first call on a device resolves the address of the library's static scratch for that
 //     device (cudaGetSymbolAddress with that device current); make that first call outside any
 //     stream capture.
@@ -635,17 +657,20 @@ extern "C" int grape_commit_i32_static(const void* d_table, uint32_t n_gens, uin
   if (rc) return rc;
   const uint64_t rows = size / wd;
   if (rows == 0) return GRAPE_OK;
-  // chunks per row: as in the arena-backed path, but capped by the static array
+  // chunks per (row, window group): as in the arena-backed path, but capped by the static array
+  const uint32_t total_windows = (max_bits + window_bits - 1) / window_bits;
+  const uint32_t groups = (total_windows + n_windows - 1) / n_windows;
+  const uint64_t row_units = rows * groups;
   uint64_t target_warps = (uint64_t)st->sm_count * 32;
   uint64_t n_chunks = 1;
-  if (rows < target_warps) {
-    n_chunks = std::min<uint64_t>((target_warps + rows - 1) / rows, (wd + 63) / 64);
+  if (row_units < target_warps) {
+    n_chunks = std::min<uint64_t>((target_warps + row_units - 1) / row_units, (wd + 63) / 64);
     if (n_chunks < 1) n_chunks = 1;
   }
-  while (n_chunks > 1 && rows * n_chunks > STATIC_MAX_UNITS) n_chunks--;
-  if (rows * n_chunks > STATIC_MAX_UNITS) {
-    snprintf(g_static_error, sizeof g_static_error, "%llu rows exceed the static scratch limit of %llu partial sums",
-             (unsigned long long)rows, (unsigned long long)STATIC_MAX_UNITS);
+  while (n_chunks > 1 && row_units * n_chunks > STATIC_MAX_UNITS) n_chunks--;
+  if (row_units * n_chunks > STATIC_MAX_UNITS) {
+    snprintf(g_static_error, sizeof g_static_error, "%llu rows x %u window group(s) exceed the static scratch limit of %llu partial sums",
+             (unsigned long long)rows, groups, (unsigned long long)STATIC_MAX_UNITS);
     return GRAPE_ERR_LIMIT;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
@@ -657,16 +682,16 @@ extern "C" int grape_commit_i32_static(const void* d_table, uint32_t n_gens, uin
   view.half = 1u << (window_bits - 1);
   view.window_stride = (uint64_t)view.half * n_gens;
   view.first_row = 0;
-  const uint32_t total_windows = (max_bits + window_bits - 1) / window_bits;
   const uint32_t chunk_len = (uint32_t)((wd + n_chunks - 1) / n_chunks);
-  const uint64_t units = rows * n_chunks;
+  const uint64_t units = row_units * n_chunks;
   const uint64_t blocks = (units + MSM_THREADS / 32 - 1) / (MSM_THREADS / 32);
   Xyzz* partials = reinterpret_cast<Xyzz*>(st->partials);
   cudaError_t e = cudaMemsetAsync(st->status, 0, sizeof(uint32_t), s);  // must start at zero
   if (e == cudaSuccess) {
     commit_accumulate_kernel<Bn254, false><<<(uint32_t)blocks, MSM_THREADS, 0, s>>>(
         d_scalars, view, wd, total_windows, (uint32_t)n_chunks, chunk_len, units, partials, st->status);
-    commit_finalize_kernel<Bn254><<<(uint32_t)((rows + 127) / 128), 128, 0, s>>>(partials, (uint32_t)n_chunks, rows,
+    commit_finalize_kernel<Bn254><<<(uint32_t)((rows + 127) / 128), 128, 0, s>>>(partials, (uint32_t)n_chunks, groups,
+                                                                          window_bits * n_windows, rows,
                                                                           reinterpret_cast<Jacobian*>(d_out));
     e = cudaGetLastError();
   }

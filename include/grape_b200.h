@@ -270,8 +270,9 @@ int grape_g1_lincomb(grape_ctx* ctx, const void* d_points_jacobian, const void* 
  * a table as grape_table_create lays it out (grape_table_data returns the pointer), the work runs
  * on the current CUDA device and on `stream` (a cudaStream_t, NULL = default stream).
  *   - calls no cudaMalloc / cudaFree / allocating routine;
- *   - at most 65536 partial sums per call: more than 65536 rows returns GRAPE_ERR_LIMIT
- *     (message from grape_static_error());
+ *   - at most 65536 partial sums per call, one or more per (row, window group) where window
+ *     groups = ceil(ceil(max_bits / window_bits) / n_windows): rows * groups > 65536 returns
+ *     GRAPE_ERR_LIMIT (message from grape_static_error());
  *   - the first call on each device looks up the device address of the static array; issue that
  *     first call outside any stream capture;
  *   - all calls on a device share the array and it keeps the previous call's contents; each call
