@@ -175,6 +175,25 @@ def reference_cuda(rows: int, steps: int):
     return {"unavailable": (res.stderr or res.stdout)[-300:]}
 
 
+def reference_cuda_secondary(mode: str, a: int, steps: int, what: str):
+    """`ref_harness matmul-bench|lookup-bench`: the reference's own prove_matmul / tLookupRange::prove on
+    this GPU at the same sizes.  None when that build is absent."""
+    if not REF_HARNESS.exists():
+        return None
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    try:
+        res = subprocess.run([str(REF_HARNESS), mode, str(a), str(steps)], capture_output=True, text=True, env=env,
+                             timeout=900)
+    except (OSError, subprocess.TimeoutExpired) as e:
+        return {"unavailable": str(e)}
+    for ln in reversed(res.stdout.strip().splitlines()):
+        if ln.startswith("{"):
+            d = json.loads(ln)
+            d["what"] = what
+            return d
+    return {"unavailable": (res.stderr or res.stdout)[-300:]}
+
+
 def run_reference(args):
     """The reference's algorithm on the host cores (C restatement; the reference's own code for this
     path is CUDA and needs libsnark, which is not vendored, so it cannot be built)."""
@@ -249,6 +268,12 @@ def layer_proof(ctx, layers: int, window_bits: int, scope: str, seed: int = 0xC5
     else:
         shape = layer_full.LayerShape(layer_num=layers, tokens=2048, dim=4096, ffn=11008)
         t = layer_full.synthesize_layer(shape, seed=seed, x_range=1 << 13, matmul=wl.exact_matmul_cuda)
+    # the loader's buffers: page-locked, so that the uploads inside the timed region run at PCIe speed
+    for k, v in list(t.items()):
+        if isinstance(v, np.ndarray) and v.nbytes >= (1 << 20):
+            p = ctx.pinned_array(v.shape, v.dtype)
+            p[...] = v
+            t[k] = p
     gens = wl.make_generators(ctx, shape.ffn_pad * 16, 0xC5)
     t0 = time.perf_counter()
     table = g.GeneratorTable(ctx, gens, window_bits, 1)
@@ -273,7 +298,8 @@ def layer_proof(ctx, layers: int, window_bits: int, scope: str, seed: int = 0xC5
            "by_step_with_syncs": trace.seconds, "window_bits": window_bits, "table_gib": table.nbytes / 2**30,
            "table_build_s": table_s, "opens": trace.opens, "lookups": trace.lookups,
            "matmul_sumchecks": trace.matmuls,
-           "note": "host int32 tensors are uploaded inside the timed region, as the reference's driver loads them"}
+           "upload_s": getattr(prover, "upload_seconds", None),
+           "note": "host int32 tensors (page-locked) are uploaded inside the timed region, as the reference's driver loads them"}
     prover.release_pool()
     table.close()
     return out
@@ -477,6 +503,10 @@ def run_secondary(args):
                              "note": "mean over the A-fold and B-fold launches; 32 B read and one field "
                                      "multiplication per element, so the integer pipe caps it near 2.2 TB/s"},
                 "gpu_launches": int(launches)}
+        ctx.sync()
+        line["reference_cuda"] = reference_cuda_secondary(
+            "matmul-bench", args.shrink, 3, "reference CUDA prove_matmul (unmodified sources, libff stand-in), same shape, "
+            "Fr tensors resident, host wall clock around the call")
     elif args.workload == "commit-bls12-381":
         # The C4 shape over BLS12-381 G1 (the reference compiles BN254 only; reported separately).
         wd = args.gens
@@ -539,6 +569,11 @@ def run_secondary(args):
         line = {"metric": "lookup_prove_ms", "value": res["with_commitments"], "unit": "ms", "higher_is_better": False,
                 "config": {"workload": f"C3: range lookup, {D} queries into a 2^16 table, commitments of A and m over 4096 generators"},
                 "without_commitments_ms": res["without_commitments"], "gpu_launches": int(launches)}
+        if args.shrink == 1:
+            ctx.sync()
+            line["reference_cuda"] = reference_cuda_secondary(
+                "lookup-bench", 22, 3, "reference CUDA tLookupRange::prove (unmodified sources, libff stand-in): 2^22 "
+                "queries, 2^16 table, its commitments of A and m over 4096 generators; host wall clock around the call")
     line.update({"n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "data": "synthetic",
                  "dtype": "u32 limbs (381-bit base field)" if args.workload == "commit-bls12-381"
                  else "u32 limbs (254-bit fields)", "vs_baseline": None})

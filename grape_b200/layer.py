@@ -162,8 +162,9 @@ class FFNProver:
         t0 = time.perf_counter()
         d_int = self._alloc(flat.nbytes)
         self.ctx._check(self.ctx.lib.grape_h2d(self.ctx.handle, d_int.ptr, flat.ctypes.data, flat.nbytes))
-        self.ctx.sync()
-        self.upload_seconds = getattr(self, "upload_seconds", 0.0) + time.perf_counter() - t0
+        if self.timing:   # from page-locked host arrays the copy is asynchronous; wait only to attribute time
+            self.ctx.sync()
+            self.upload_seconds = getattr(self, "upload_seconds", 0.0) + time.perf_counter() - t0
         cap = flat.size
         if flat.size % self.shape.ffn == 0 and self.shape.ffn != self.shape.ffn_pad:
             cap = flat.size // self.shape.ffn * self.shape.ffn_pad

@@ -5,6 +5,8 @@
 //
 //   ref_harness parity <in.bin> <out.bin>     commit / open / prove_matmul / tLookupRange on given data
 //   ref_harness commit-bench <rows> <steps>   times Hyrax::commit(int*) on int16-range rows of 4096
+//   ref_harness matmul-bench <shrink> <steps> times prove_matmul on (2048/shrink) x 4096 . (4096/shrink) x 4096
+//   ref_harness lookup-bench <log2 D> <steps> times tLookupRange::prove on 2^D queries into a 2^16 table
 //
 // Shapes are restricted to what the reference's kernels handle without reading out of bounds
 // (they have no guards): rows a multiple of 32, power-of-two sizes.
@@ -207,9 +209,98 @@ static int commit_bench(uint32_t rows, int steps) {
   return e == cudaSuccess ? 0 : 6;
 }
 
+// C2: the reference's prove_matmul on A [N][K], B [M][K] with K = 4096 (test/matmul.cu flow; the
+// claim is formed with the reference's own folds instead of a host matrix product).
+static int matmul_bench(uint32_t shrink, int steps) {
+  const uint32_t L = 1, N = 2048 / shrink, M = 4096 / shrink, K = 4096;
+  ppT::init_public_params();
+  ref_shim_seed(0xC2);
+  std::mt19937 rng(11);
+  std::normal_distribution<float> dist(0.f, 0.02f * 65536.f);
+  std::vector<int> hA((size_t)N * K), hB((size_t)M * K);
+  for (auto& x : hA) x = (int)std::round(dist(rng));
+  for (auto& x : hB) x = (int)std::round(dist(rng));
+  int* dA = to_dev(hA.data(), hA.size());
+  int* dB = to_dev(hB.data(), hB.size());
+  std::vector<Fr> u = random_vec(Log2(L * N * M)), v = random_vec(Log2(K * L));
+  Fr claim0;
+  {
+    FrTensor a2(hA.size(), dA), b2(hB.size(), dB);
+    fr_t* U;
+    cudaMalloc(&U, sizeof(fr_t) * u.size());
+    cudaMemcpy(U, u.data(), sizeof(fr_t) * u.size(), cudaMemcpyHostToDevice);
+    a2.partial_eval(a2.size, U, N, Log2(M), K);
+    b2.partial_eval(b2.size, U, M, 0, K);
+    FrTensor a(K), b(K);
+    cudaMemcpy(a.gpu_data, a2.gpu_data, sizeof(fr_t) * K, cudaMemcpyDeviceToDevice);
+    cudaMemcpy(b.gpu_data, b2.gpu_data, sizeof(fr_t) * K, cudaMemcpyDeviceToDevice);
+    a *= b;
+    claim0 = a.sum(K);
+    cudaFree(U);
+  }
+  double total = 0;
+  for (int s = 0; s < steps + 1; s++) {
+    FrTensor x(hA.size(), dA), w(hB.size(), dB);
+    Fr claim = claim0;
+    cudaDeviceSynchronize();
+    auto t0 = std::chrono::high_resolution_clock::now();
+    auto pr = prove_matmul(x, w, L, N, M, K, u, v, claim);
+    cudaDeviceSynchronize();
+    double dt = std::chrono::duration<double>(std::chrono::high_resolution_clock::now() - t0).count();
+    if (s > 0) total += dt;  // first call is the warm-up
+    (void)pr;
+  }
+  cudaError_t e = cudaGetLastError();
+  printf("{\"N\": %u, \"M\": %u, \"K\": %u, \"steps\": %d, \"ms_per_proof\": %.4f, \"cuda_status\": \"%s\"}\n", N, M, K,
+         steps, total / steps * 1e3, cudaGetErrorString(e));
+  return e == cudaSuccess ? 0 : 6;
+}
+
+// C3: the reference's tLookupRange::prove on 2^log2_d uniform queries into a 2^16 table, with its
+// commitments of A and m over 4096 generators (test/tlookupTest.cu flow).
+static int lookup_bench(uint32_t log2_d, int steps) {
+  const uint32_t D = 1u << log2_d, len = 1u << 16, n_gens = 4096;
+  ppT::init_public_params();
+  ref_shim_seed(0xC3);
+  affine_t* points;
+  cudaMalloc(&points, sizeof(affine_t) * (size_t)n_gens * 256);
+  std::vector<bn128> cpu_points = precompute_generators(n_gens, 256, points);
+  cudaDeviceSynchronize();
+  Hyrax hyrax(1, n_gens / 16, points, cpu_points[0]);
+  std::mt19937 rng(13);
+  std::uniform_int_distribution<int> dist(-(int)(len / 2), (int)(len / 2) - 1);
+  std::vector<int> hq(D);
+  for (auto& x : hq) x = dist(rng);
+  int* dQ = to_dev(hq.data(), hq.size());
+  std::vector<Fr> v = random_vec(Log2(D));
+  double total = 0, com_total = 0;
+  for (int s = 0; s < steps + 1; s++) {
+    tLookupRange rs(-(int)(len / 2), len);
+    FrTensor x_tensor(D, dQ), A(D);
+    double com_time = 0.0;
+    cudaDeviceSynchronize();
+    auto t0 = std::chrono::high_resolution_clock::now();
+    Fr value = rs.prove(x_tensor, A, v, hyrax, n_gens / 16, com_time);
+    cudaDeviceSynchronize();
+    double dt = std::chrono::duration<double>(std::chrono::high_resolution_clock::now() - t0).count();
+    if (s > 0) {
+      total += dt;
+      com_total += com_time;
+    }
+    (void)value;
+  }
+  cudaError_t e = cudaGetLastError();
+  printf("{\"D\": %u, \"table\": %u, \"steps\": %d, \"ms_per_proof\": %.4f, \"commit_ms_reported_by_reference\": %.4f, "
+         "\"cuda_status\": \"%s\"}\n", D, len, steps, total / steps * 1e3, com_total / steps * 1e3, cudaGetErrorString(e));
+  return e == cudaSuccess ? 0 : 6;
+}
+
 int main(int argc, char** argv) {
   if (argc >= 4 && std::string(argv[1]) == "parity") return parity(argv[2], argv[3]);
   if (argc >= 4 && std::string(argv[1]) == "commit-bench") return commit_bench(atoi(argv[2]), atoi(argv[3]));
-  fprintf(stderr, "usage: ref_harness parity <in> <out> | commit-bench <rows> <steps>\n");
+  if (argc >= 4 && std::string(argv[1]) == "matmul-bench") return matmul_bench(atoi(argv[2]), atoi(argv[3]));
+  if (argc >= 4 && std::string(argv[1]) == "lookup-bench") return lookup_bench(atoi(argv[2]), atoi(argv[3]));
+  fprintf(stderr, "usage: ref_harness parity <in> <out> | commit-bench <rows> <steps> | matmul-bench <shrink> <steps> | "
+                  "lookup-bench <log2 queries> <steps>\n");
   return 2;
 }
