@@ -289,6 +289,50 @@ __global__ void __launch_bounds__(128) commit_finalize_kernel(const XyzzT<typena
   store_jacobian_normalised(out + row, a, inf);
 }
 
+// The same for commitments of FEW rows (openings commit a single row split into hundreds of chunks):
+// one block per row.  Warp k adds the chunk partials of groups k, k + 8, ... with a strided loop and a
+// shuffle tree, leaves each group sum in shared memory, and thread 0 runs the Horner recombination.
+constexpr int FIN_THREADS = 256;
+constexpr int FIN_MAX_GROUPS = 64;
+
+template <class C>
+__global__ void __launch_bounds__(FIN_THREADS) commit_finalize_block_kernel(
+    const XyzzT<typename C::F>* __restrict__ partials, uint32_t n_chunks, uint32_t groups, uint32_t group_bits,
+    JacobianT<typename C::F>* __restrict__ out) {
+  using Affine = AffineT<typename C::F>;
+  using Xyzz = XyzzT<typename C::F>;
+  __shared__ __align__(16) unsigned char sums_raw[FIN_MAX_GROUPS * sizeof(Xyzz)];
+  Xyzz* sums = reinterpret_cast<Xyzz*>(sums_raw);
+  const uint64_t row = blockIdx.x;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (uint32_t g = warp; g < groups; g += FIN_THREADS / 32) {
+    const Xyzz* p = partials + (row * groups + g) * n_chunks;
+    Xyzz acc = Xyzz::inf();
+#pragma unroll 1
+    for (uint32_t k = lane; k < n_chunks; k += 32) xyzz_add(acc, Xyzz::load(p + k));
+#pragma unroll 1
+    for (int off = 16; off > 0; off >>= 1) {
+      Xyzz other = xyzz_shfl_down(acc, off);
+      if (lane < off) xyzz_add(acc, other);
+    }
+    if (lane == 0) acc.store(sums + g);
+  }
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  Xyzz acc = Xyzz::inf();
+#pragma unroll 1
+  for (int g = (int)groups - 1; g >= 0; g--) {
+    if (g != (int)groups - 1) {
+#pragma unroll 1
+      for (uint32_t k = 0; k < group_bits; k++) acc = xyzz_dbl(acc);
+    }
+    xyzz_add(acc, Xyzz::load(sums + g));
+  }
+  bool inf = acc.is_inf();
+  Affine a = xyzz_to_affine(acc);
+  store_jacobian_normalised(out + row, a, inf);
+}
+
 // ------------------------------------------------------------------------------------------
 // Host side
 // ------------------------------------------------------------------------------------------
@@ -328,9 +372,13 @@ static int launch_commit(grape_ctx* ctx, const grape_table* t, const void* d_sca
         d_scalars, make_view<typename C::F>(t), wd, total_windows, n_chunks, chunk_len, units, partials,
         ctx->d_status);
   }
-  commit_finalize_kernel<C><<<(uint32_t)((rows + 127) / 128), 128, 0, ctx->stream>>>(
-      partials, n_chunks, groups, t->window_bits * t->n_windows, rows,
-      reinterpret_cast<JacobianT<typename C::F>*>(d_out));
+  if (n_chunks >= 8 && groups <= FIN_MAX_GROUPS && rows <= 4096)
+    commit_finalize_block_kernel<C><<<(uint32_t)rows, FIN_THREADS, 0, ctx->stream>>>(
+        partials, n_chunks, groups, t->window_bits * t->n_windows, reinterpret_cast<JacobianT<typename C::F>*>(d_out));
+  else
+    commit_finalize_kernel<C><<<(uint32_t)((rows + 127) / 128), 128, 0, ctx->stream>>>(
+        partials, n_chunks, groups, t->window_bits * t->n_windows, rows,
+        reinterpret_cast<JacobianT<typename C::F>*>(d_out));
   ctx->launches += 2;
   GRAPE_CUDA_TRY(ctx, cudaGetLastError());
   return GRAPE_OK;
