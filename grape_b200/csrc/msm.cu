@@ -185,7 +185,7 @@ __global__ void __launch_bounds__(MSM_THREADS, C::MSM_BLOCKS)
 commit_accumulate_kernel(const void* __restrict__ scalars, TableViewT<typename C::F> tab, uint32_t wd,
                          uint32_t total_windows, uint32_t n_chunks, uint32_t chunk_len,
                          uint64_t n_units, XyzzT<typename C::F>* __restrict__ partials,
-                         uint32_t* __restrict__ status) {
+                         uint32_t* __restrict__ status, uint32_t inner, uint32_t inner_pad) {
   using Affine = AffineT<typename C::F>;
   using Xyzz = XyzzT<typename C::F>;
   const uint64_t unit = (uint64_t)blockIdx.x * (MSM_THREADS / 32) + (threadIdx.x >> 5);
@@ -202,8 +202,11 @@ commit_accumulate_kernel(const void* __restrict__ scalars, TableViewT<typename C
   const uint64_t rg = unit / n_chunks;
   const uint32_t g = (uint32_t)(rg % groups);
   const uint64_t row = rg / groups;
+  // With inner != 0 (Fr scalars only) a row is sub-rows of inner_pad columns of which only the first
+  // `inner` are walked: the caller accounts for the skipped (constant) columns separately.
+  const uint32_t wd_walk = (FR && inner) ? wd / inner_pad * inner : wd;
   const uint32_t i_begin = chunk * chunk_len;
-  const uint32_t i_end = min(wd, i_begin + chunk_len);
+  const uint32_t i_end = min(wd_walk, i_begin + chunk_len);
 
   // bias for the int32 path: 2^(c-1) at every window below the top one
   uint32_t bias32 = 0;
@@ -215,7 +218,12 @@ commit_accumulate_kernel(const void* __restrict__ scalars, TableViewT<typename C
   {
     const uint32_t w_lo = g * tw;
     const uint32_t w_hi = min(total_windows, w_lo + tw);
-    for (uint32_t i = i_begin + lane; i < i_end; i += 32) {
+    for (uint32_t j = i_begin + lane; j < i_end; j += 32) {
+      uint32_t i = j;
+      if (FR && inner) {
+        const uint32_t q = j / inner;
+        i = q * inner_pad + (j - q * inner);
+      }
       const uint64_t idx = row * wd + i;
       if (FR) {
         const uint32_t* sp = reinterpret_cast<const uint32_t*>(scalars) + idx * 8;
@@ -268,7 +276,8 @@ template <class C>
 __global__ void __launch_bounds__(128) commit_finalize_kernel(const XyzzT<typename C::F>* __restrict__ partials,
                                                               uint32_t n_chunks, uint32_t groups,
                                                               uint32_t group_bits, uint64_t rows,
-                                                              JacobianT<typename C::F>* __restrict__ out) {
+                                                              JacobianT<typename C::F>* __restrict__ out,
+                                                              const JacobianT<typename C::F>* __restrict__ extra) {
   using Affine = AffineT<typename C::F>;
   using Xyzz = XyzzT<typename C::F>;
   uint64_t row = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -284,6 +293,14 @@ __global__ void __launch_bounds__(128) commit_finalize_kernel(const XyzzT<typena
 #pragma unroll 1
     for (uint32_t k = 0; k < n_chunks; k++) xyzz_add(acc, Xyzz::load(p + k));
   }
+  if (extra) {  // the same point added to every row (the constant columns skipped by the accumulation)
+    JacobianT<typename C::F> e;
+    const char* ep = reinterpret_cast<const char*>(extra);
+    e.x = C::F::load(ep);
+    e.y = C::F::load(ep + C::F::BYTES);
+    e.z = C::F::load(ep + 2 * C::F::BYTES);
+    xyzz_add(acc, xyzz_from_jacobian(e));
+  }
   bool inf = acc.is_inf();
   Affine a = xyzz_to_affine(acc);
   store_jacobian_normalised(out + row, a, inf);
@@ -298,7 +315,7 @@ constexpr int FIN_MAX_GROUPS = 64;
 template <class C>
 __global__ void __launch_bounds__(FIN_THREADS) commit_finalize_block_kernel(
     const XyzzT<typename C::F>* __restrict__ partials, uint32_t n_chunks, uint32_t groups, uint32_t group_bits,
-    JacobianT<typename C::F>* __restrict__ out) {
+    JacobianT<typename C::F>* __restrict__ out, const JacobianT<typename C::F>* __restrict__ extra) {
   using Affine = AffineT<typename C::F>;
   using Xyzz = XyzzT<typename C::F>;
   __shared__ __align__(16) unsigned char sums_raw[FIN_MAX_GROUPS * sizeof(Xyzz)];
@@ -327,6 +344,14 @@ __global__ void __launch_bounds__(FIN_THREADS) commit_finalize_block_kernel(
       for (uint32_t k = 0; k < group_bits; k++) acc = xyzz_dbl(acc);
     }
     xyzz_add(acc, Xyzz::load(sums + g));
+  }
+  if (extra) {
+    JacobianT<typename C::F> e;
+    const char* ep = reinterpret_cast<const char*>(extra);
+    e.x = C::F::load(ep);
+    e.y = C::F::load(ep + C::F::BYTES);
+    e.z = C::F::load(ep + 2 * C::F::BYTES);
+    xyzz_add(acc, xyzz_from_jacobian(e));
   }
   bool inf = acc.is_inf();
   Affine a = xyzz_to_affine(acc);
@@ -359,8 +384,10 @@ static uint32_t pick_chunks(const grape_ctx* ctx, uint64_t rows, uint32_t wd, ui
 template <class C, bool FR>
 static int launch_commit(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t rows,
                          uint32_t wd, uint32_t total_windows, XyzzT<typename C::F>* partials,
-                         uint32_t n_chunks, void* d_out) {
-  uint32_t chunk_len = (wd + n_chunks - 1) / n_chunks;
+                         uint32_t n_chunks, void* d_out, uint32_t inner = 0, uint32_t inner_pad = 0,
+                         const void* d_extra = nullptr) {
+  const uint32_t wd_walk = inner ? wd / inner_pad * inner : wd;
+  uint32_t chunk_len = (wd_walk + n_chunks - 1) / n_chunks;
   const uint32_t groups = (total_windows + t->n_windows - 1) / t->n_windows;
   uint64_t units = rows * groups * n_chunks;
   if (units == 0) return GRAPE_OK;
@@ -370,15 +397,17 @@ static int launch_commit(grape_ctx* ctx, const grape_table* t, const void* d_sca
     ProfScope prof(ctx);
     commit_accumulate_kernel<C, FR><<<(uint32_t)blocks, MSM_THREADS, 0, ctx->stream>>>(
         d_scalars, make_view<typename C::F>(t), wd, total_windows, n_chunks, chunk_len, units, partials,
-        ctx->d_status);
+        ctx->d_status, inner, inner_pad);
   }
+  const JacobianT<typename C::F>* extra = reinterpret_cast<const JacobianT<typename C::F>*>(d_extra);
   if (n_chunks >= 8 && groups <= FIN_MAX_GROUPS && rows <= 4096)
     commit_finalize_block_kernel<C><<<(uint32_t)rows, FIN_THREADS, 0, ctx->stream>>>(
-        partials, n_chunks, groups, t->window_bits * t->n_windows, reinterpret_cast<JacobianT<typename C::F>*>(d_out));
+        partials, n_chunks, groups, t->window_bits * t->n_windows, reinterpret_cast<JacobianT<typename C::F>*>(d_out),
+        extra);
   else
     commit_finalize_kernel<C><<<(uint32_t)((rows + 127) / 128), 128, 0, ctx->stream>>>(
         partials, n_chunks, groups, t->window_bits * t->n_windows, rows,
-        reinterpret_cast<JacobianT<typename C::F>*>(d_out));
+        reinterpret_cast<JacobianT<typename C::F>*>(d_out), extra);
   ctx->launches += 2;
   GRAPE_CUDA_TRY(ctx, cudaGetLastError());
   return GRAPE_OK;
@@ -450,7 +479,8 @@ static int commit_i32_impl(grape_ctx* ctx, const grape_table* t, const int32_t* 
 // window is read unsigned and then never exceeds the largest stored magnitude.
 template <class C>
 static int commit_fr_impl(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t size,
-                          uint64_t rows, uint32_t wd, void* d_out) {
+                          uint64_t rows, uint32_t wd, void* d_out, uint32_t inner = 0, uint32_t inner_pad = 0,
+                          const void* d_extra = nullptr) {
   uint32_t total_windows = (C::SCALAR_BITS + t->window_bits) / t->window_bits;
   if (C::ID == Bn254::ID) total_windows = (254 + t->window_bits - 1) / t->window_bits;
   const uint32_t groups = (total_windows + t->n_windows - 1) / t->n_windows;
@@ -464,7 +494,8 @@ static int commit_fr_impl(grape_ctx* ctx, const grape_table* t, const void* d_sc
   fr_bias_kernel<C><<<(uint32_t)((size + 255) / 256), 256, 0, ctx->stream>>>(
       reinterpret_cast<const uint32_t*>(d_scalars), biased, size, make_bias(t->window_bits, total_windows));
   ctx->launches += 1;
-  return launch_commit<C, true>(ctx, t, biased, rows, wd, total_windows, partials, n_chunks, d_out);
+  return launch_commit<C, true>(ctx, t, biased, rows, wd, total_windows, partials, n_chunks, d_out, inner, inner_pad,
+                               d_extra);
 }
 
 static size_t jacobian_bytes(const grape_table* t) {
@@ -547,6 +578,69 @@ int commit_fr_async(grape_ctx* ctx, const grape_table* t, const void* d_scalars,
   if (t->curve == Bls12381::ID) return commit_fr_impl<Bls12381>(ctx, t, d_scalars, size, rows, wd, d_out);
   return commit_fr_impl<Bn254>(ctx, t, d_scalars, size, rows, wd, d_out);
 }
+}  // namespace grape
+
+namespace grape {
+
+// ones[i] = 1 on the constant columns (i mod inner_pad >= inner), 0 elsewhere
+__global__ void k_constant_columns(int32_t* __restrict__ ones, uint32_t wd, uint32_t inner, uint32_t inner_pad) {
+  for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < wd; i += gridDim.x * blockDim.x)
+    ones[i] = (i % inner_pad) >= inner ? 1 : 0;
+}
+
+// out = [s] * P (Jacobian record in, normalised Jacobian record out), one thread: 254 doublings.
+__global__ void k_scale_point(const uint32_t* __restrict__ point_jac, const uint32_t* __restrict__ scalar,
+                              uint32_t* __restrict__ out_jac) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  Jacobian j;
+  j.x = Fp::load(point_jac);
+  j.y = Fp::load(point_jac + 8);
+  j.z = Fp::load(point_jac + 16);
+  Xyzz base = xyzz_from_jacobian(j);
+  Fr s = fe_from_mont(Fr::load(scalar));
+  Xyzz acc = Xyzz::inf();
+  for (int w = 7; w >= 0; w--) {
+    for (int b = 31; b >= 0; b--) {
+      acc = xyzz_dbl(acc);
+      if ((s.v[w] >> b) & 1u) xyzz_add(acc, base);
+    }
+  }
+  bool inf = acc.is_inf();
+  Affine a = xyzz_to_affine(acc);
+  store_jacobian_normalised(out_jac, a, inf);
+}
+
+// Row commitments of a tensor whose rows are sub-rows of inner_pad columns where every column past
+// `inner` holds the SAME scalar (the row padding of the lookup arguments: about a third of a
+// 11008 -> 16384 padded row).  The constant columns contribute  s_const * (sum of their generators),
+// one point for all rows: it is computed once (a one-row commitment of 0/1 scalars and one scalar
+// multiplication) and added to every row by the finalize kernel, while the accumulation walks the
+// first `inner` columns of each sub-row only.  d_const points at the constant scalar (Fr, device).
+int commit_fr_padded_async(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t size, uint32_t wd,
+                           uint32_t inner, uint32_t inner_pad, const void* d_const, void* d_out) {
+  if (inner == 0 || inner >= inner_pad || wd % inner_pad != 0 || t->curve != Bn254::ID)
+    return commit_fr_async(ctx, t, d_scalars, size, wd, d_out);
+  int rc = check_table(ctx, t, wd);
+  if (rc) return rc;
+  if (size % wd != 0) return fail(ctx, GRAPE_ERR_INVALID, "size is not a multiple of the row length");
+  if (size == 0) return GRAPE_OK;
+  int32_t* ones = nullptr;
+  uint32_t* pts = nullptr;  // sum of the constant columns' generators | that sum times the constant
+  if ((rc = arena_alloc_t(ctx, (size_t)wd, &ones))) return rc;
+  if ((rc = arena_alloc_t(ctx, 2 * 24 + 8, &pts))) return rc;
+  k_constant_columns<<<std::min<uint32_t>((wd + 255) / 256, 1024u), 256, 0, ctx->stream>>>(ones, wd, inner, inner_pad);
+  ctx->launches += 1;
+  {
+    const uint32_t groups = 1, n_chunks = pick_chunks(ctx, 1, wd, groups);
+    Xyzz* partials = nullptr;
+    if ((rc = arena_alloc_t(ctx, (size_t)n_chunks, &partials))) return rc;
+    if ((rc = launch_commit<Bn254, false>(ctx, t, ones, 1, wd, 1, partials, n_chunks, pts))) return rc;
+  }
+  k_scale_point<<<1, 32, 0, ctx->stream>>>(pts, reinterpret_cast<const uint32_t*>(d_const), pts + 24);
+  ctx->launches += 1;
+  return commit_fr_impl<Bn254>(ctx, t, d_scalars, size, size / wd, wd, d_out, inner, inner_pad, pts + 24);
+}
+
 }  // namespace grape
 
 extern "C" int grape_commit_fr(grape_ctx* ctx, const grape_table* t, const void* d_scalars,
@@ -737,10 +831,10 @@ extern "C" int grape_commit_i32_static(const void* d_table, uint32_t n_gens, uin
   cudaError_t e = cudaMemsetAsync(st->status, 0, sizeof(uint32_t), s);  // must start at zero
   if (e == cudaSuccess) {
     commit_accumulate_kernel<Bn254, false><<<(uint32_t)blocks, MSM_THREADS, 0, s>>>(
-        d_scalars, view, wd, total_windows, (uint32_t)n_chunks, chunk_len, units, partials, st->status);
+        d_scalars, view, wd, total_windows, (uint32_t)n_chunks, chunk_len, units, partials, st->status, 0u, 0u);
     commit_finalize_kernel<Bn254><<<(uint32_t)((rows + 127) / 128), 128, 0, s>>>(partials, (uint32_t)n_chunks, groups,
                                                                           window_bits * n_windows, rows,
-                                                                          reinterpret_cast<Jacobian*>(d_out));
+                                                                          reinterpret_cast<Jacobian*>(d_out), nullptr);
     e = cudaGetLastError();
   }
   if (e == cudaSuccess && h_status) {

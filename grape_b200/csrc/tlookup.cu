@@ -38,6 +38,8 @@ namespace grape {
 void eq_weights_async(grape_ctx* ctx, const void* d_x, uint32_t nv, uint32_t c, void* d_w);
 int fr_sum_async(grape_ctx* ctx, const void* d_in, uint64_t n, void* d_out);
 int fr_inverse_async(grape_ctx* ctx, const void* d_in, const void* d_shift, void* d_out, uint64_t n);
+int commit_fr_padded_async(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t size, uint32_t wd,
+                           uint32_t inner, uint32_t inner_pad, const void* d_const, void* d_out);
 int commit_fr_async(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t size, uint32_t wd,
                     void* d_out);
 
@@ -381,7 +383,14 @@ static int lookup_prove(grape_ctx* ctx, grape_lookup* lk, uint32_t* d_S, uint64_
       if ((rc = arena_alloc(ctx, (size_t)(N / m_wd) * 96, &tmp))) return rc;
       d_com_m = tmp;
     }
-    if ((rc = commit_fr_async(ctx, table, d_A, Dp, msm_size * GRAPE_COM_SCALE, d_com_A))) return rc;
+    const uint32_t a_wd = msm_size * GRAPE_COM_SCALE;
+    if (D != Dp && a_wd % inner_pad == 0) {
+      // the padded columns of every row hold the same value 1 / (pad + beta): element `inner` of A is one of them
+      if ((rc = commit_fr_padded_async(ctx, table, d_A, Dp, a_wd, inner, inner_pad, d_A + (size_t)inner * 8, d_com_A)))
+        return rc;
+    } else if ((rc = commit_fr_async(ctx, table, d_A, Dp, a_wd, d_com_A))) {
+      return rc;
+    }
     if ((rc = commit_fr_async(ctx, table, lk->m, N, m_wd, d_com_m))) return rc;
   }
   // working copies of B, T, m (the rounds fold in place), sum_j B_j m_j

@@ -165,3 +165,43 @@ def test_hyrax_open_and_verify(gctx, layer_num, N, rows):
     proof = {"result": got["result"], "z": got["z"], "com_d": got["com_d"], "com_ad": got["com_ad"]}
     assert pr.hyrax_verify(commitments, proof, e, c, size, N, layer_num, gens, gens[0])
     table.close()
+
+
+@pytest.mark.parametrize("inner,inner_pad,window_bits", [(11, 16, 8), (6, 8, 13), (24, 32, 16)])
+def test_lookup_commitment_of_padded_rows(gctx, inner, inner_pad, window_bits):
+    """Rows padded inner -> inner_pad: the padded columns of A all hold 1 / (pad + beta).  The prover
+    commits them through one shared point instead of one addition per column and window; the row
+    commitments must still equal a plain commitment of the padded A."""
+    import grape_b200 as g
+    from grape_b200 import host, workloads as wl
+    rng = random.Random(inner * 10 + window_bits)
+    rows_in = 256                       # sub-rows of `inner` values
+    D = rows_in * inner
+    Dp = rows_in * inner_pad            # a power of two
+    msm = 2 * inner_pad // 16 * 4       # row of msm * 16 generators = 8 sub-rows
+    wd = msm * 16
+    gens = wl.make_generators(gctx, max(wd, 256), seed=inner)   # the multiplicities are committed over 256
+    table = g.GeneratorTable(gctx, gens, window_bits, 1)
+    ctable = cport.table_build(gens)
+    gctx.seed(21)
+    draw = bn254.SplitMix64(21)
+    lk = host.Lookup(gctx, -128, 256)
+    ref = pr.LookupRange(-128, 256, draw.next_fr())
+    S = [rng.randrange(-128, 128) % R for _ in range(D)]
+    v = [rng.randrange(R) for _ in range(pr.log2ceil(Dp))]
+    u = draw.fr_vec(pr.log2ceil(Dp))
+    want = ref.prove(S, v, u, inner=inner, inner_pad=inner_pad)
+    assert len(want["A"]) == Dp
+    dS, dA = gctx.alloc(Dp * 32), gctx.alloc(Dp * 32)
+    gctx._check(gctx.lib.grape_h2d(gctx.handle, dS.ptr, host.encode_field(S).ctypes.data, D * 32))
+    comA = gctx.alloc(Dp // wd * 96)
+    claim, tr = lk.prove(dS, D, dA, v, inner=inner, inner_pad=inner_pad, table=table, msm_size=msm, d_com_A=comA)
+    assert claim == want["claim"] and tr == want["transcript"]
+    wantA = cport.commit_fr(host.encode_field(want["A"]), wd, ctable)
+    assert gctx.download(comA, wantA.nbytes).tobytes() == wantA.tobytes()
+    # and equals the plain commitment of the same padded tensor by this library
+    plain = gctx.alloc(Dp // wd * 96)
+    g.commit_fr(gctx, table, gctx.fr_upload(want["A"]), Dp, wd, plain)
+    assert gctx.download(plain, wantA.nbytes).tobytes() == wantA.tobytes()
+    lk.close()
+    table.close()
