@@ -88,15 +88,37 @@ __global__ void k_table_init(uint32_t* __restrict__ T, const uint32_t* __restric
   }
 }
 
-// hist[(S_i - low) mod 2^32]++ ; an index outside the table sets a status bit instead of writing.
-__global__ void k_histogram(const uint32_t* __restrict__ S, uint64_t n, const uint32_t* __restrict__ low,
-                            uint32_t* __restrict__ hist, uint32_t n_bins, uint32_t* __restrict__ status) {
+// The histogram and A = 1 / (S + beta) in one pass.  Every query equals a table entry T[idx], so
+// A_i = B[idx] is a gather from the table's inverses (2 MB, cache-resident) instead of a batched
+// inversion over the queries.  i runs over the PADDED layout (sub-rows of inner_pad columns of which
+// the first `inner` come from src, the rest are padding = table entry pad_bin, counted separately).
+// A query outside the table sets the status bit (the prover then fails) and gets A = 0.
+__global__ void k_hist_gather(const uint32_t* __restrict__ src, uint64_t n_padded, uint32_t inner, uint32_t inner_pad,
+                              const uint32_t* __restrict__ low, uint32_t pad_bin, const uint32_t* __restrict__ B,
+                              uint32_t* __restrict__ A, uint32_t* __restrict__ hist, uint32_t n_bins,
+                              uint32_t* __restrict__ status) {
   const Fr lo = Fr::load_nc(low);
-  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
-    Fr d = fe_from_mont(fe_sub(Fr::load_nc(S + i * 8), lo));
-    uint32_t hi = d.v[1] | d.v[2] | d.v[3] | d.v[4] | d.v[5] | d.v[6] | d.v[7];
-    if (hi != 0 || d.v[0] >= n_bins) atomicOr(status, STATUS_HIST_RANGE);
-    else atomicAdd(hist + d.v[0], 1u);
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_padded; i += (uint64_t)gridDim.x * blockDim.x) {
+    uint64_t s = i;
+    bool is_pad = false;
+    if (inner) {
+      const uint64_t row = i / inner_pad;
+      const uint32_t col = (uint32_t)(i - row * inner_pad);
+      is_pad = col >= inner;
+      s = row * inner + col;
+    }
+    uint32_t idx = pad_bin;
+    bool ok = true;
+    if (!is_pad) {
+      Fr d = fe_from_mont(fe_sub(Fr::load_nc(src + s * 8), lo));
+      uint32_t hi = d.v[1] | d.v[2] | d.v[3] | d.v[4] | d.v[5] | d.v[6] | d.v[7];
+      ok = hi == 0 && d.v[0] < n_bins;
+      idx = d.v[0];
+      if (ok) atomicAdd(hist + idx, 1u);
+      else atomicOr(status, STATUS_HIST_RANGE);
+    }
+    Fr a = ok ? Fr::load_nc(B + (uint64_t)idx * 8) : Fr::zero();
+    a.store(A + i * 8);
   }
 }
 
@@ -323,20 +345,6 @@ extern "C" const void* grape_lookup_table(const grape_lookup* lk, int which) {
 
 // Multiplicities of the queries d_S (D Fr elements) into lk->m; pad_count is added to the bin of
 // value zero (reference: prep, src/tlookup.cu:265-286).
-static int lookup_prep(grape_ctx* ctx, grape_lookup* lk, const uint32_t* d_S, uint64_t D, uint64_t pad_count,
-                       const uint32_t* d_low) {
-  GRAPE_CUDA_TRY(ctx, cudaMemsetAsync(lk->hist, 0, (size_t)lk->n * 4, ctx->stream));
-  k_histogram<<<lk_blocks(ctx, D), LT, 0, ctx->stream>>>(d_S, D, d_low, lk->hist, lk->n, ctx->d_status);
-  ctx->launches += 1;
-  if (pad_count) {
-    int64_t bin = -(int64_t)lk->low;
-    if (bin < 0 || bin >= (int64_t)lk->n) return fail(ctx, GRAPE_ERR_INVALID, "lookup: padding needs 0 inside the table range");
-    k_hist_add<<<1, 32, 0, ctx->stream>>>(lk->hist, (uint32_t)bin, (uint32_t)pad_count);
-    ctx->launches += 1;
-  }
-  return grape_fr_from_u32(ctx, lk->hist, lk->m, lk->n);
-}
-
 // The prover proper.  d_S: queries (D elements, buffer of Dpad = 2^ceil(log2 D) elements when padding
 // applies), consumed; d_A: buffer of Dpad elements that receives 1/(S+beta) and is consumed.
 static int lookup_prove(grape_ctx* ctx, grape_lookup* lk, uint32_t* d_S, uint64_t D, uint32_t* d_A,
@@ -361,13 +369,29 @@ static int lookup_prove(grape_ctx* ctx, grape_lookup* lk, uint32_t* d_S, uint64_
   if ((rc = upload(ctx, v, lD, &d_v))) return rc;
   HostFr consts[3] = {fr_from_i64(lk->low), lk->beta, pad_value};
   if ((rc = upload(ctx, consts, 3, &d_c))) return rc;
-  if ((rc = lookup_prep(ctx, lk, d_hist_src, D, Dp - D, d_c))) return rc;
-  if (D != Dp) {  // row-pad inner -> inner_pad through d_A as the temporary, like FrTensor::pad
-    if ((rc = grape_fr_pad(ctx, d_S, d_A, inner, inner_pad, Dp, d_c + 16))) return rc;
-    GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_S, d_A, Dp * 32, cudaMemcpyDeviceToDevice, ctx->stream));
+  // multiplicities, and A = 1 / (S + beta) gathered from the table's inverses in the same pass
+  // (reference: prep + the inversion of S + beta, src/tlookup.cu:250-262,296-318)
+  const int64_t pad_bin = -(int64_t)lk->low;
+  if (D != Dp && (pad_bin < 0 || pad_bin >= (int64_t)N))
+    return fail(ctx, GRAPE_ERR_INVALID, "lookup: padding needs 0 inside the table range");
+  GRAPE_CUDA_TRY(ctx, cudaMemsetAsync(lk->hist, 0, (size_t)N * 4, ctx->stream));
+  if (D == Dp) {
+    k_hist_gather<<<lk_blocks(ctx, Dp), LT, 0, ctx->stream>>>(d_hist_src, Dp, 0, 0, d_c, 0, lk->B, d_A, lk->hist, N,
+                                                              ctx->d_status);
+    ctx->launches += 1;
+  } else {
+    // row-pad inner -> inner_pad (like FrTensor::pad): the padded S is built in a scratch buffer because
+    // both d_S (dense) and d_A (gather target) are live until the gather has read the dense queries
+    uint32_t* padded = nullptr;
+    if ((rc = arena_alloc_t(ctx, (size_t)Dp * 8, &padded))) return rc;
+    if ((rc = grape_fr_pad(ctx, d_S, padded, inner, inner_pad, Dp, d_c + 16))) return rc;
+    k_hist_gather<<<lk_blocks(ctx, Dp), LT, 0, ctx->stream>>>(d_hist_src, Dp, inner, inner_pad, d_c, (uint32_t)pad_bin,
+                                                              lk->B, d_A, lk->hist, N, ctx->d_status);
+    k_hist_add<<<1, 32, 0, ctx->stream>>>(lk->hist, (uint32_t)pad_bin, (uint32_t)(Dp - D));
+    ctx->launches += 2;
+    GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_S, padded, Dp * 32, cudaMemcpyDeviceToDevice, ctx->stream));
   }
-  // A = 1 / (S + beta)
-  if ((rc = fr_inverse_async(ctx, d_S, d_c + 8, d_A, Dp))) return rc;
+  if ((rc = grape_fr_from_u32(ctx, lk->hist, lk->m, N))) return rc;
   // commitments to A and m (reference: src/tlookup.cu:319-323); optional here
   if (table) {
     if (msm_size == 0 || Dp % ((uint64_t)msm_size * GRAPE_COM_SCALE) != 0)
