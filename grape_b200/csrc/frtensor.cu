@@ -260,6 +260,23 @@ int fold_axis_async(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* 
   const uint64_t other = ntot / ((uint64_t)c * gap);
   const uint64_t n_out = other * gap;
   const uint32_t nv = log2ceil(c);
+  // A long innermost axis with few rows (a full evaluation of a big tensor is one row) would run in
+  // `other` blocks: fold its low variables first, as rows of c_lo elements, then the short rest.
+  if (gap == 1 && other < (uint64_t)ctx->sm_count * 4 && c >= 8192) {
+    uint32_t lo_bits = nv / 2, tz = 0;
+    while (tz < 31 && ((c >> tz) & 1u) == 0) tz++;
+    if (lo_bits > tz) lo_bits = tz;
+    if (lo_bits >= 6) {
+      const uint32_t c_lo = 1u << lo_bits, c_hi = c >> lo_bits;
+      void* tmp = nullptr;
+      int rc0 = arena_alloc(ctx, (size_t)other * c_hi * 32, &tmp);
+      if (rc0) return rc0;
+      rc0 = fold_axis_async<FROM_I32>(ctx, d_t, ntot, d_x, c_lo, 1, tmp);
+      if (rc0) return rc0;
+      return fold_axis_async<false>(ctx, tmp, other * c_hi, reinterpret_cast<const uint32_t*>(d_x) + (size_t)lo_bits * 8,
+                                    c_hi, 1, d_out);
+    }
+  }
   // work area: eq weights (c) + slice partials
   uint32_t n_slices = 1;
   if (gap > 1) {

@@ -97,7 +97,8 @@ def test_inverse_sum_rowsum(gctx):
         assert got[r * dim:(r + 1) * dim] == [s] * dim
 
 
-@pytest.mark.parametrize("other,c,gap", [(1, 8, 1), (3, 11, 1), (2, 6, 5), (1, 64, 300), (4, 13, 33), (1, 1, 7), (5, 2, 1)])
+@pytest.mark.parametrize("other,c,gap", [(1, 8, 1), (3, 11, 1), (2, 6, 5), (1, 64, 300), (4, 13, 33), (1, 1, 7), (5, 2, 1),
+                                         (1, 16384, 1), (2, 24576, 1), (1, 8200, 1)])
 def test_fold_matches_reference_fold(gctx, other, c, gap):
     rng = random.Random(other * 1000 + c * 10 + gap)
     n = other * c * gap

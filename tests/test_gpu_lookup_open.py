@@ -54,7 +54,9 @@ def test_lookup_range_padded_rows(gctx):
     u = draw.fr_vec(5)
     want = ref.prove(S, v, u, inner=inner, inner_pad=inner_pad)
     dS = gctx.alloc(32 * 32)
-    gctx._check(gctx.lib.grape_h2d(gctx.handle, dS.ptr, host.encode_field(S).ctypes.data, D * 32))
+    s_enc = host.encode_field(S)    # keep the host array alive across the copy
+    gctx._check(gctx.lib.grape_h2d(gctx.handle, dS.ptr, s_enc.ctypes.data, D * 32))
+    gctx.sync()
     gctx.sync()
     dA = gctx.alloc(32 * 32)
     claim, tr = lk.prove(dS, D, dA, v, inner=inner, inner_pad=inner_pad)
@@ -193,7 +195,9 @@ def test_lookup_commitment_of_padded_rows(gctx, inner, inner_pad, window_bits):
     want = ref.prove(S, v, u, inner=inner, inner_pad=inner_pad)
     assert len(want["A"]) == Dp
     dS, dA = gctx.alloc(Dp * 32), gctx.alloc(Dp * 32)
-    gctx._check(gctx.lib.grape_h2d(gctx.handle, dS.ptr, host.encode_field(S).ctypes.data, D * 32))
+    s_enc = host.encode_field(S)    # keep the host array alive across the copy
+    gctx._check(gctx.lib.grape_h2d(gctx.handle, dS.ptr, s_enc.ctypes.data, D * 32))
+    gctx.sync()
     comA = gctx.alloc(Dp // wd * 96)
     claim, tr = lk.prove(dS, D, dA, v, inner=inner, inner_pad=inner_pad, table=table, msm_size=msm, d_com_A=comA)
     assert claim == want["claim"] and tr == want["transcript"]
