@@ -169,6 +169,12 @@ extern "C" int grape_timer_end(grape_ctx* ctx, float* ms) {
   return GRAPE_OK;
 }
 
+extern "C" int grape_lookup_set_bucket_commit(grape_ctx* ctx, int mode) {
+  if (!ctx || mode < 0 || mode > 2) return GRAPE_ERR_INVALID;
+  ctx->bucket_mode = mode;
+  return GRAPE_OK;
+}
+
 extern "C" int grape_prof_enable(grape_ctx* ctx, int on) {
   if (!ctx) return GRAPE_ERR_INVALID;
   ctx->profile = on != 0;

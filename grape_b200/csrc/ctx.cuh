@@ -28,6 +28,8 @@ struct grape_ctx {
   uint32_t* d_status = nullptr;
   std::string err;
   int sm_count = 148;
+  // commitments of a lookup's A by the bucket method: 0 never, 1 when the cost model favours it, 2 whenever supported
+  int bucket_mode = 1;
   // launch counters (own kernels launched since creation), read by the benchmark
   uint64_t launches = 0;
   // wall-clock bracket on the stream (grape_timer_begin / grape_timer_end)

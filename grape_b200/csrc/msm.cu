@@ -610,12 +610,32 @@ __global__ void k_scale_point(const uint32_t* __restrict__ point_jac, const uint
   store_jacobian_normalised(out_jac, a, inf);
 }
 
+// The point  s_const * (sum of the generators of the constant columns)  of rows that are sub-rows of
+// inner_pad columns whose columns past `inner` all hold the scalar at d_const: a one-row commitment
+// of 0/1 scalars and one scalar multiplication.  *d_point: a Jacobian record in the arena.
+int constant_columns_point_async(grape_ctx* ctx, const grape_table* t, uint32_t wd, uint32_t inner, uint32_t inner_pad,
+                                 const void* d_const, uint32_t** d_point) {
+  int rc;
+  int32_t* ones = nullptr;
+  uint32_t* pts = nullptr;  // sum of the constant columns' generators | that sum times the constant
+  if ((rc = arena_alloc_t(ctx, (size_t)wd, &ones))) return rc;
+  if ((rc = arena_alloc_t(ctx, 2 * 24 + 8, &pts))) return rc;
+  k_constant_columns<<<std::min<uint32_t>((wd + 255) / 256, 1024u), 256, 0, ctx->stream>>>(ones, wd, inner, inner_pad);
+  ctx->launches += 1;
+  const uint32_t n_chunks = pick_chunks(ctx, 1, wd, 1);
+  Xyzz* partials = nullptr;
+  if ((rc = arena_alloc_t(ctx, (size_t)n_chunks, &partials))) return rc;
+  if ((rc = launch_commit<Bn254, false>(ctx, t, ones, 1, wd, 1, partials, n_chunks, pts))) return rc;
+  k_scale_point<<<1, 32, 0, ctx->stream>>>(pts, reinterpret_cast<const uint32_t*>(d_const), pts + 24);
+  ctx->launches += 1;
+  *d_point = pts + 24;
+  return GRAPE_OK;
+}
+
 // Row commitments of a tensor whose rows are sub-rows of inner_pad columns where every column past
 // `inner` holds the SAME scalar (the row padding of the lookup arguments: about a third of a
-// 11008 -> 16384 padded row).  The constant columns contribute  s_const * (sum of their generators),
-// one point for all rows: it is computed once (a one-row commitment of 0/1 scalars and one scalar
-// multiplication) and added to every row by the finalize kernel, while the accumulation walks the
-// first `inner` columns of each sub-row only.  d_const points at the constant scalar (Fr, device).
+// 11008 -> 16384 padded row).  The constant columns contribute one point for all rows, added by
+// the finalize kernel, while the accumulation walks the first `inner` columns of each sub-row only.
 int commit_fr_padded_async(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t size, uint32_t wd,
                            uint32_t inner, uint32_t inner_pad, const void* d_const, void* d_out) {
   if (inner == 0 || inner >= inner_pad || wd % inner_pad != 0 || t->curve != Bn254::ID)
@@ -624,21 +644,25 @@ int commit_fr_padded_async(grape_ctx* ctx, const grape_table* t, const void* d_s
   if (rc) return rc;
   if (size % wd != 0) return fail(ctx, GRAPE_ERR_INVALID, "size is not a multiple of the row length");
   if (size == 0) return GRAPE_OK;
-  int32_t* ones = nullptr;
-  uint32_t* pts = nullptr;  // sum of the constant columns' generators | that sum times the constant
-  if ((rc = arena_alloc_t(ctx, (size_t)wd, &ones))) return rc;
-  if ((rc = arena_alloc_t(ctx, 2 * 24 + 8, &pts))) return rc;
-  k_constant_columns<<<std::min<uint32_t>((wd + 255) / 256, 1024u), 256, 0, ctx->stream>>>(ones, wd, inner, inner_pad);
+  uint32_t* point = nullptr;
+  if ((rc = constant_columns_point_async(ctx, t, wd, inner, inner_pad, d_const, &point))) return rc;
+  return commit_fr_impl<Bn254>(ctx, t, d_scalars, size, size / wd, wd, d_out, inner, inner_pad, point);
+}
+
+// Horner recombination + normalisation of partial sums laid out [row][group][chunk] (BN254).
+int finalize_bn254_async(grape_ctx* ctx, const Xyzz* partials, uint32_t n_chunks, uint32_t groups, uint32_t group_bits,
+                         uint64_t rows, void* d_out, const void* d_extra) {
+  if (rows == 0) return GRAPE_OK;
+  const Jacobian* extra = reinterpret_cast<const Jacobian*>(d_extra);
+  if (n_chunks >= 8 && groups <= FIN_MAX_GROUPS && rows <= 4096)
+    commit_finalize_block_kernel<Bn254><<<(uint32_t)rows, FIN_THREADS, 0, ctx->stream>>>(
+        partials, n_chunks, groups, group_bits, reinterpret_cast<Jacobian*>(d_out), extra);
+  else
+    commit_finalize_kernel<Bn254><<<(uint32_t)((rows + 127) / 128), 128, 0, ctx->stream>>>(
+        partials, n_chunks, groups, group_bits, rows, reinterpret_cast<Jacobian*>(d_out), extra);
   ctx->launches += 1;
-  {
-    const uint32_t groups = 1, n_chunks = pick_chunks(ctx, 1, wd, groups);
-    Xyzz* partials = nullptr;
-    if ((rc = arena_alloc_t(ctx, (size_t)n_chunks, &partials))) return rc;
-    if ((rc = launch_commit<Bn254, false>(ctx, t, ones, 1, wd, 1, partials, n_chunks, pts))) return rc;
-  }
-  k_scale_point<<<1, 32, 0, ctx->stream>>>(pts, reinterpret_cast<const uint32_t*>(d_const), pts + 24);
-  ctx->launches += 1;
-  return commit_fr_impl<Bn254>(ctx, t, d_scalars, size, size / wd, wd, d_out, inner, inner_pad, pts + 24);
+  GRAPE_CUDA_TRY(ctx, cudaGetLastError());
+  return GRAPE_OK;
 }
 
 }  // namespace grape

@@ -40,6 +40,10 @@ int fr_sum_async(grape_ctx* ctx, const void* d_in, uint64_t n, void* d_out);
 int fr_inverse_async(grape_ctx* ctx, const void* d_in, const void* d_shift, void* d_out, uint64_t n);
 int commit_fr_padded_async(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t size, uint32_t wd,
                            uint32_t inner, uint32_t inner_pad, const void* d_const, void* d_out);
+int constant_columns_point_async(grape_ctx* ctx, const grape_table* t, uint32_t wd, uint32_t inner, uint32_t inner_pad,
+                                 const void* d_const, uint32_t** d_point);
+int commit_gathered_async(grape_ctx* ctx, const grape_table* t, const uint32_t* d_idx, const uint32_t* d_B,
+                          uint32_t n_bins, uint64_t size, uint32_t wd, const void* d_extra, void* d_out);
 int commit_fr_async(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t size, uint32_t wd,
                     void* d_out);
 
@@ -96,7 +100,7 @@ __global__ void k_table_init(uint32_t* __restrict__ T, const uint32_t* __restric
 __global__ void k_hist_gather(const uint32_t* __restrict__ src, uint64_t n_padded, uint32_t inner, uint32_t inner_pad,
                               const uint32_t* __restrict__ low, uint32_t pad_bin, const uint32_t* __restrict__ B,
                               uint32_t* __restrict__ A, uint32_t* __restrict__ hist, uint32_t n_bins,
-                              uint32_t* __restrict__ status) {
+                              uint32_t* __restrict__ status, uint32_t* __restrict__ idx_out) {
   const Fr lo = Fr::load_nc(low);
   for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_padded; i += (uint64_t)gridDim.x * blockDim.x) {
     uint64_t s = i;
@@ -119,6 +123,7 @@ __global__ void k_hist_gather(const uint32_t* __restrict__ src, uint64_t n_padde
     }
     Fr a = ok ? Fr::load_nc(B + (uint64_t)idx * 8) : Fr::zero();
     a.store(A + i * 8);
+    if (idx_out) idx_out[i] = (is_pad || !ok) ? 0xFFFFFFFFu : idx;  // table entry per element, padding left out
   }
 }
 
@@ -374,10 +379,25 @@ static int lookup_prove(grape_ctx* ctx, grape_lookup* lk, uint32_t* d_S, uint64_
   const int64_t pad_bin = -(int64_t)lk->low;
   if (D != Dp && (pad_bin < 0 || pad_bin >= (int64_t)N))
     return fail(ctx, GRAPE_ERR_INVALID, "lookup: padding needs 0 inside the table range");
+  // Commit A by the bucket method?  Cost per row in units of one mixed addition of the direct kernel:
+  // direct = elements * windows of the table; bucketed = 1.5 * elements + 120 * table entries as
+  // MEASURED for this implementation (its second stage runs at a fraction of the direct kernel's
+  // rate: 20 * entries additions in the count, uneven bucket lengths and eight warps per SM in practice),
+  // so it is chosen only for rows several times longer than the table.
+  uint32_t* d_idx = nullptr;
+  if (table && msm_size && ctx->bucket_mode != 0 && N % 8 == 0) {
+    const uint64_t a_wd0 = (uint64_t)msm_size * GRAPE_COM_SCALE;
+    const uint64_t valid = (D != Dp && a_wd0 % inner_pad == 0) ? a_wd0 / inner_pad * inner : a_wd0;
+    const double direct = (double)valid * ((254 + table->window_bits - 1) / table->window_bits);
+    const double bucketed = 1.5 * (double)valid + 120.0 * N;
+    if (ctx->bucket_mode == 2 || bucketed < 0.9 * direct) {
+      if ((rc = arena_alloc_t(ctx, (size_t)Dp, &d_idx))) return rc;
+    }
+  }
   GRAPE_CUDA_TRY(ctx, cudaMemsetAsync(lk->hist, 0, (size_t)N * 4, ctx->stream));
   if (D == Dp) {
     k_hist_gather<<<lk_blocks(ctx, Dp), LT, 0, ctx->stream>>>(d_hist_src, Dp, 0, 0, d_c, 0, lk->B, d_A, lk->hist, N,
-                                                              ctx->d_status);
+                                                              ctx->d_status, d_idx);
     ctx->launches += 1;
   } else {
     // row-pad inner -> inner_pad (like FrTensor::pad): the padded S is built in a scratch buffer because
@@ -386,7 +406,7 @@ static int lookup_prove(grape_ctx* ctx, grape_lookup* lk, uint32_t* d_S, uint64_
     if ((rc = arena_alloc_t(ctx, (size_t)Dp * 8, &padded))) return rc;
     if ((rc = grape_fr_pad(ctx, d_S, padded, inner, inner_pad, Dp, d_c + 16))) return rc;
     k_hist_gather<<<lk_blocks(ctx, Dp), LT, 0, ctx->stream>>>(d_hist_src, Dp, inner, inner_pad, d_c, (uint32_t)pad_bin,
-                                                              lk->B, d_A, lk->hist, N, ctx->d_status);
+                                                              lk->B, d_A, lk->hist, N, ctx->d_status, d_idx);
     k_hist_add<<<1, 32, 0, ctx->stream>>>(lk->hist, (uint32_t)pad_bin, (uint32_t)(Dp - D));
     ctx->launches += 2;
     GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_S, padded, Dp * 32, cudaMemcpyDeviceToDevice, ctx->stream));
@@ -408,7 +428,26 @@ static int lookup_prove(grape_ctx* ctx, grape_lookup* lk, uint32_t* d_S, uint64_
       d_com_m = tmp;
     }
     const uint32_t a_wd = msm_size * GRAPE_COM_SCALE;
-    if (D != Dp && a_wd % inner_pad == 0) {
+    bool committed = false;
+    if (d_idx) {
+      // bucket method; the padded columns (left out of d_idx) still contribute their shared point
+      uint32_t* extra = nullptr;
+      if (D != Dp) {
+        if (a_wd % inner_pad == 0) {
+          if ((rc = constant_columns_point_async(ctx, table, a_wd, inner, inner_pad, d_A + (size_t)inner * 8, &extra)))
+            return rc;
+        } else {
+          d_idx = nullptr;  // rows do not consist of whole padded sub-rows: commit directly
+        }
+      }
+      if (d_idx) {
+        rc = commit_gathered_async(ctx, table, d_idx, lk->B, N, Dp, a_wd, extra, d_com_A);
+        if (rc == GRAPE_OK) committed = true;
+        else if (rc != GRAPE_ERR_INVALID) return rc;  // INVALID: shape not supported, fall through
+      }
+    }
+    if (committed) {
+    } else if (D != Dp && a_wd % inner_pad == 0) {
       // the padded columns of every row hold the same value 1 / (pad + beta): element `inner` of A is one of them
       if ((rc = commit_fr_padded_async(ctx, table, d_A, Dp, a_wd, inner, inner_pad, d_A + (size_t)inner * 8, d_com_A)))
         return rc;

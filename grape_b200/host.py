@@ -201,6 +201,10 @@ class Context:
         self._check(self.lib.grape_measure_madd_peak(self.handle, C.byref(v)))
         return v.value
 
+    def set_bucket_commit(self, mode: int):
+        """How lookups commit A: 0 never by the bucket method, 1 when cheaper (default), 2 whenever possible."""
+        self._check(self.lib.grape_lookup_set_bucket_commit(self.handle, mode))
+
     # -- randomness seam
     def seed(self, seed: int):
         self._check(self.lib.grape_rng_seed(self.handle, seed))

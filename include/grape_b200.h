@@ -214,6 +214,15 @@ int grape_lookup_params(const grape_lookup* lk, void* h_alpha, void* h_beta, voi
 /* Device tensors of the object: 0 = T, 1 = B = 1/(T+beta), 2 = m (multiplicities of the last
  * prove), 3 = mapped values. */
 const void* grape_lookup_table(const grape_lookup* lk, int which);
+/* How the lookup provers commit A = 1/(S+beta) (no reference counterpart; the commitment is the same
+ * group element either way).  Every A_i equals the table's B[t] for the entry t that S_i hits, so a
+ * commitment row with several times more elements than the table has entries is cheaper by the
+ * bucket method: add up the generators per table entry first (one addition per element), then one
+ * variable-base multi-scalar multiplication of those sums by B per row.
+ * mode 0: never; 1 (default): when the measured cost model favours it (rows at least about seven
+ * times longer than the table has entries); 2: whenever the shape allows. */
+int grape_lookup_set_bucket_commit(grape_ctx* ctx, int mode);
+
 /* tLookupRange::prove (src/tlookup.cu:288-343).  d_S: D queries; when D is not a power of two the
  * rows of length `inner` are padded to `inner_pad` (the reference hard-codes 11008 -> 16384) and
  * d_S, d_A must hold 2^ceil(log2 D) elements.  d_A receives 1/(S+beta); both are consumed.

@@ -209,3 +209,72 @@ def test_lookup_commitment_of_padded_rows(gctx, inner, inner_pad, window_bits):
     assert gctx.download(plain, wantA.nbytes).tobytes() == wantA.tobytes()
     lk.close()
     table.close()
+
+
+def _lookup_commitment(gctx, lk, S_enc, D, Dp, v, table, msm, wd, inner, inner_pad, mode, seed):
+    """One range-lookup proof with the A-commitment path forced to `mode`; returns (claim, com_A bytes, A bytes)."""
+    gctx.set_bucket_commit(mode)
+    gctx.seed(seed)
+    dS, dA = gctx.alloc(Dp * 32), gctx.alloc(Dp * 32)
+    gctx._check(gctx.lib.grape_h2d(gctx.handle, dS.ptr, S_enc.ctypes.data, D * 32))
+    gctx.sync()
+    comA = gctx.alloc(Dp // wd * 96)
+    kw = dict(inner=inner, inner_pad=inner_pad) if inner else {}
+    l0 = gctx.launches
+    claim, tr = lk.prove(dS, D, dA, v, table=table, msm_size=msm, d_com_A=comA, **kw)
+    out = (claim, tr, gctx.download(comA, Dp // wd * 96).tobytes(), gctx.launches - l0)
+    gctx.set_bucket_commit(1)
+    return out
+
+
+@pytest.mark.parametrize("n_table,rows_in,inner,inner_pad,msm,window_bits,skew", [
+    (256, 4096, 0, 0, 64, 8, False),        # 4 rows of 1024 elements over a 256-entry table
+    (256, 512, 11, 16, 32, 13, False),      # padded rows: the padded columns go through the shared point
+    (256, 2048, 0, 0, 128, 8, True),        # one value taken by half of the elements, many entries unused
+    (65536, 1 << 18, 0, 0, 1 << 13, 8, False),  # a table wider than one block's counters: two sort parts
+])
+def test_bucket_commitment_equals_direct_commitment(gctx, n_table, rows_in, inner, inner_pad, msm, window_bits, skew):
+    """A committed by the bucket method (generators summed per table entry, then one variable-base
+    multi-scalar multiplication per row) gives byte-identical commitments, claims and transcripts."""
+    import grape_b200 as g
+    from grape_b200 import host, workloads as wl
+    rng = np.random.default_rng(n_table + rows_in)
+    low = -(n_table // 2)
+    if inner:
+        D, Dp = rows_in * inner, rows_in * inner_pad
+    else:
+        D = Dp = rows_in
+    wd = msm * 16
+    vals = rng.integers(low, low + n_table, size=D)
+    if skew:
+        vals[rng.random(D) < 0.5] = low + 3
+        vals[(vals > low + 20) & (vals < low + 40)] = low + 50
+    S_enc = host.encode_field([int(x) for x in vals]) if D <= 1 << 16 else None
+    if S_enc is None:   # large case: build the field encoding on the GPU
+        d_int = gctx.upload(vals.astype(np.int32))
+        d_fr = gctx.alloc(D * 32)
+        gctx.fr_from_i32(d_int, D, d_fr)
+        S_enc = gctx.download(d_fr, D * 32).reshape(D, 8)
+    gens = wl.make_generators(gctx, max(wd, 4096), seed=n_table)
+    table = g.GeneratorTable(gctx, gens, window_bits, 1)
+    v = [int(x) for x in rng.integers(1, 2**62, size=pr.log2ceil(Dp))]
+    results = []
+    for mode in (0, 2):
+        gctx.seed(77)
+        lk = host.Lookup(gctx, low, n_table)
+        results.append(_lookup_commitment(gctx, lk, S_enc, D, Dp, v, table, msm, wd, inner, inner_pad, mode, seed=78))
+        lk.close()
+    assert results[0][0] == results[1][0] and results[0][1] == results[1][1]
+    assert results[0][2] == results[1][2]
+    assert results[0][3] != results[1][3]   # the two modes really took different kernel sequences
+    if D <= 1 << 13:    # and both equal the C oracle's commitment of A = 1/(S + beta)
+        ctable = cport.table_build(gens)
+        gctx.seed(77)
+        draw = bn254.SplitMix64(77)
+        ref = pr.LookupRange(low, n_table, draw.next_fr())
+        draw2 = bn254.SplitMix64(78)
+        kw = dict(inner=inner, inner_pad=inner_pad) if inner else {}
+        want = ref.prove([int(x) % R for x in vals], v, draw2.fr_vec(pr.log2ceil(Dp)), **kw)
+        wantA = cport.commit_fr(host.encode_field(want["A"]), wd, ctable)
+        assert results[1][2] == wantA.tobytes()
+    table.close()
