@@ -696,31 +696,39 @@ extern "C" int grape_commit_i32_host(grape_ctx* ctx, const grape_table* t, const
   }
   int32_t* d_in = reinterpret_cast<int32_t*>(ctx->dstage);
   char* d_out = reinterpret_cast<char*>(ctx->dstage) + ((in_bytes + 255) & ~size_t(255));
-  // Row slices: slice i+1 is copied in on the copy stream while slice i is being committed.
-  const uint32_t n_slices = rows >= 4096 ? 8 : 1;
+  // Row slices: slice i+1 is copied in on the copy stream while slice i is being committed.  The
+  // copy runs about 2.4x faster than the commitment, so only the first slice's copy is exposed: it is
+  // kept small (1/32 of the rows) and the later slices grow, which keeps their launches long enough
+  // to fill whole waves of warps.
+  static const uint32_t kSliceParts[5] = {1, 3, 7, 10, 11};  // of 32
+  const uint32_t n_slices = rows >= 4096 ? 5 : 1;
   if (!ctx->copy_stream) GRAPE_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
   while (ctx->copy_events.size() < n_slices + 1) {
     cudaEvent_t e;
     GRAPE_CUDA_TRY(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
     ctx->copy_events.push_back(e);
   }
+  uint64_t bounds[6];
+  bounds[0] = 0;
+  for (uint32_t sidx = 0, acc = 0; sidx < n_slices; sidx++) {
+    acc += kSliceParts[sidx];
+    bounds[sidx + 1] = n_slices == 1 ? rows : rows * acc / 32;
+  }
+  bounds[n_slices] = rows;
   // the copy stream must not overwrite the staging buffer while earlier work still reads it
   GRAPE_CUDA_TRY(ctx, cudaEventRecord(ctx->copy_events[n_slices], ctx->stream));
   GRAPE_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->copy_events[n_slices], 0));
-  const uint64_t rows_per_slice = (rows + n_slices - 1) / n_slices;
   for (uint32_t sidx = 0; sidx < n_slices; sidx++) {
-    const uint64_t r0 = (uint64_t)sidx * rows_per_slice;
-    if (r0 >= rows) break;
-    const uint64_t r1 = std::min<uint64_t>(rows, r0 + rows_per_slice);
-    GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_in + r0 * wd, h_scalars + r0 * wd, (r1 - r0) * wd * sizeof(int32_t),
-                                        cudaMemcpyHostToDevice, ctx->copy_stream));
+    const uint64_t r0 = bounds[sidx], r1 = bounds[sidx + 1];
+    if (r1 > r0)
+      GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_in + r0 * wd, h_scalars + r0 * wd, (r1 - r0) * wd * sizeof(int32_t),
+                                          cudaMemcpyHostToDevice, ctx->copy_stream));
     GRAPE_CUDA_TRY(ctx, cudaEventRecord(ctx->copy_events[sidx], ctx->copy_stream));
   }
   for (uint32_t sidx = 0; sidx < n_slices; sidx++) {
-    const uint64_t r0 = (uint64_t)sidx * rows_per_slice;
-    if (r0 >= rows) break;
-    const uint64_t r1 = std::min<uint64_t>(rows, r0 + rows_per_slice);
+    const uint64_t r0 = bounds[sidx], r1 = bounds[sidx + 1];
     GRAPE_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->copy_events[sidx], 0));
+    if (r1 == r0) continue;
     rc = grape_commit_i32(ctx, t, d_in + r0 * wd, (r1 - r0) * wd, wd, max_bits, d_out + r0 * jac);
     if (rc) return rc;
   }
