@@ -53,7 +53,7 @@ def parse_args():
                     help="also time the proof of this many decoder layers (one batch, seq 2048)")
     ap.add_argument("--proof-window-bits", type=int, default=13)
     ap.add_argument("--proof-scope", default="layer", choices=["layer", "ffn"])
-    ap.add_argument("--workload", default="commit", choices=["commit", "matmul", "lookup", "commit-bls12-381", "matmul-sharded", "layer-proof"],
+    ap.add_argument("--workload", default="commit", choices=["commit", "matmul", "lookup", "commit-bls12-381", "matmul-sharded", "layer-proof", "fold"],
                     help="commit = C4 (the headline); matmul = C2 prove_matmul; lookup = C3 range lookup")
     ap.add_argument("--shrink", type=int, default=1, help="divide the matmul / lookup sizes (profiling cases)")
     ap.add_argument("--rows", type=int, default=0, help="commit only this many rows (reduced case for profiling)")
@@ -286,6 +286,7 @@ def layer_proof(ctx, layers: int, window_bits: int, scope: str, seed: int = 0xC5
     else:
         prover = layer_full.LayerProver(ctx, shape, table, gens[0], t["swiglu_table"], t["exp_table"])
         run = prover.prove_layer
+    prover.prefetch_inputs = True   # the inputs are page-locked: upload them behind the first proof steps
     run(t)  # warm-up (allocations)
     ctx.sync()
     t0 = time.perf_counter()
@@ -507,6 +508,48 @@ def run_secondary(args):
         line["reference_cuda"] = reference_cuda_secondary(
             "matmul-bench", args.shrink, 3, "reference CUDA prove_matmul (unmodified sources, libff stand-in), same shape, "
             "Fr tensors resident, host wall clock around the call")
+    elif args.workload == "fold":
+        # Axis fold (FrTensor::partial_eval, src/fr-tensor.cu:53-72,168-188) of an [8192][16384] tensor over its
+        # first axis, from int32 data (4 B per element) and from Fr data (32 B per element).
+        c, gap = 8192 // args.shrink, 16384
+        n = c * gap
+        t_i = ctx.upload(wl.quantised_normal(rng, n, lo=-2**31, hi=2**31 - 1))
+        ctx.seed(0xF0)
+        du = ctx.upload(ctx.random_fr((c - 1).bit_length()))
+        out = ctx.alloc(gap * 32)
+        res = {}
+        launches = 0
+        for label in ("int32", "fr"):
+            if label == "fr":
+                t_f = ctx.alloc(n * 32)
+                ctx.fr_from_i32(t_i, n, t_f)
+            ctx.prof_read()
+            for it in range(args.warmup + args.steps):
+                if it == args.warmup:
+                    ctx.prof_enable(True)
+                l0 = ctx.launches
+                if label == "int32":
+                    ctx.fold_i32(t_i, n, du, c, gap, out)
+                else:
+                    ctx.fr_fold(t_f, n, du, c, gap, out)
+                if it >= args.warmup:
+                    launches += ctx.launches - l0
+            ctx.sync()
+            k_ms, k_n = ctx.prof_read()
+            ctx.prof_enable(False)
+            per = k_ms / max(k_n, 1)
+            nbytes = n * (4 if label == "int32" else 32)
+            res[label] = {"kernel_ms": per, "bytes": nbytes, "gbs": nbytes / (per * 1e-3) / 1e9 if per else 0.0}
+        line = {"metric": "fold_axis_gbs", "value": res["int32"]["gbs"], "unit": "GB/s", "higher_is_better": True,
+                "config": {"workload": f"axis fold of a {c} x {gap} tensor over its first axis; inputs ({n * 4 >> 20} MiB int32, "
+                                       f"{n * 32 >> 20} MiB Fr) exceed L2"},
+                "roofline": {"bound": "hbm", "kernel": "k_fold_axis<int32 source>", "achieved": res["int32"]["gbs"],
+                             "peak": hbm_peak, "unit": "GB/s", "frac": res["int32"]["gbs"] / hbm_peak, "traffic": None,
+                             "note": "algorithmic bytes = 4 per element (the tensor is read once); eight multiply-adds per element"},
+                "fr_source": {"kernel": "k_fold_axis<Fr source>", "achieved_gbs": res["fr"]["gbs"],
+                              "frac_of_hbm": res["fr"]["gbs"] / hbm_peak, "kernel_ms": res["fr"]["kernel_ms"],
+                              "note": "32 B and one full field multiplication per element: bound by the multiply pipe"},
+                "kernel_ms": res["int32"]["kernel_ms"], "gpu_launches": int(launches)}
     elif args.workload == "commit-bls12-381":
         # The C4 shape over BLS12-381 G1 (the reference compiles BN254 only; reported separately).
         wd = args.gens

@@ -70,6 +70,8 @@ def _declare(lib):
     f("grape_dev_alloc", [vp, sz, C.POINTER(vp)])
     f("grape_dev_free", [vp, vp])
     f("grape_h2d", [vp, vp, vp, sz])
+    f("grape_h2d_prefetch", [vp, vp, vp, sz, C.POINTER(u32)])
+    f("grape_prefetch_wait", [vp, u32])
     f("grape_d2h", [vp, vp, vp, sz])
     f("grape_d2d", [vp, vp, vp, sz])
     f("grape_dev_zero", [vp, vp, sz])

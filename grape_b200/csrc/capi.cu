@@ -45,6 +45,7 @@ extern "C" int grape_ctx_destroy(grape_ctx* ctx) {
   if (ctx->d_status) cudaFree(ctx->d_status);
   if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
   for (auto e : ctx->copy_events) cudaEventDestroy(e);
+  for (auto e : ctx->prefetch_events) cudaEventDestroy(e);
   if (ctx->t0) { cudaEventDestroy(ctx->t0); cudaEventDestroy(ctx->t1); }
   for (auto& pr : ctx->prof_events) { cudaEventDestroy(pr.first); cudaEventDestroy(pr.second); }
   cudaStreamDestroy(ctx->stream);
@@ -113,6 +114,44 @@ extern "C" int grape_h2d(grape_ctx* ctx, void* d_dst, const void* h_src, size_t 
   GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
   // pageable sources are staged by the runtime before the call returns; pinned ones are not,
   // so callers that reuse a pinned source must grape_ctx_sync() first.
+  return GRAPE_OK;
+}
+
+// Host-to-device copy on the context's copy stream, so that it overlaps the kernels of the main
+// stream; h_src should be page-locked (a pageable source makes the call synchronous).  The copy
+// starts once the work already queued on the main stream is done (the destination may still be in
+// use by it).  *ticket identifies the copy for grape_prefetch_wait, which makes the main stream wait
+// for that copy (and releases the ticket).
+extern "C" int grape_h2d_prefetch(grape_ctx* ctx, void* d_dst, const void* h_src, size_t bytes, uint32_t* ticket) {
+  if (!ctx || !ticket) return GRAPE_ERR_INVALID;
+  if (!ctx->copy_stream) GRAPE_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+  if (ctx->copy_events.empty()) {
+    cudaEvent_t e;
+    GRAPE_CUDA_TRY(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    ctx->copy_events.push_back(e);
+  }
+  uint32_t tk;
+  if (!ctx->free_tickets.empty()) {
+    tk = ctx->free_tickets.back();
+    ctx->free_tickets.pop_back();
+  } else {
+    cudaEvent_t e;
+    GRAPE_CUDA_TRY(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+    ctx->prefetch_events.push_back(e);
+    tk = (uint32_t)ctx->prefetch_events.size() - 1;
+  }
+  GRAPE_CUDA_TRY(ctx, cudaEventRecord(ctx->copy_events[0], ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->copy_stream, ctx->copy_events[0], 0));
+  if (bytes) GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, ctx->copy_stream));
+  GRAPE_CUDA_TRY(ctx, cudaEventRecord(ctx->prefetch_events[tk], ctx->copy_stream));
+  *ticket = tk;
+  return GRAPE_OK;
+}
+
+extern "C" int grape_prefetch_wait(grape_ctx* ctx, uint32_t ticket) {
+  if (!ctx || ticket >= ctx->prefetch_events.size()) return GRAPE_ERR_INVALID;
+  GRAPE_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->prefetch_events[ticket], 0));
+  ctx->free_tickets.push_back(ticket);
   return GRAPE_OK;
 }
 

@@ -14,6 +14,9 @@ struct grape_ctx {
   // second stream + events: host-to-device copies of the host-buffer entry points overlap compute
   cudaStream_t copy_stream = nullptr;
   std::vector<cudaEvent_t> copy_events;
+  // events of grape_h2d_prefetch, indexed by ticket; free_tickets lists the ones that were waited for
+  std::vector<cudaEvent_t> prefetch_events;
+  std::vector<uint32_t> free_tickets;
   // scratch arena: a bump allocator over a few device blocks.  A top-level call resets it,
   // carves what its kernels need, and the next call on the stream reuses the same memory.
   struct ArenaBlock { void* ptr; size_t size; size_t off; };

@@ -163,6 +163,60 @@ __global__ void k_rowsum_broadcast(const uint32_t* __restrict__ in, uint32_t* __
   }
 }
 
+// ---- sums of (field element) x (32-bit integer) without a reduction per term ------------------
+// For folds that read int32 tensors.  acc += w * |x| with w a reduced residue (8 limbs) and |x| < 2^32:
+// the 288-bit products are added into two interleaved accumulators (even limbs of w at limb
+// offsets 0,2,4,6; odd limbs one limb higher), each with a 32-bit overflow word, so up to 2^32
+// terms fit.  One term costs eight 32x32->64 multiply-adds; the value is reduced once at the end.
+struct WideAcc {
+  uint32_t E[8], O[8], Et, Ot;
+  __device__ __forceinline__ void clear() {
+#pragma unroll
+    for (int i = 0; i < 8; i++) { E[i] = 0; O[i] = 0; }
+    Et = 0;
+    Ot = 0;
+  }
+  __device__ __forceinline__ void mac(const Fr& w, uint32_t ax) {
+    mad4_top(E, Et, w.v[0], w.v[2], w.v[4], w.v[6], ax);
+    mad4_top(O, Ot, w.v[1], w.v[3], w.v[5], w.v[7], ax);
+  }
+  // The accumulated integer V = E + (O << 32) (320 bits) as the residue V mod r.  Because the
+  // weights are Montgomery residues and the integers are plain, V mod r IS the Montgomery form of
+  // the weighted sum.  V is cut into 128-bit pieces that are recombined by Horner in the field.
+  __device__ __forceinline__ Fr to_fr() const {
+    uint32_t L[10];
+    uint64_t carry = 0;
+    L[0] = E[0];
+#pragma unroll
+    for (int k = 1; k < 8; k++) {
+      uint64_t s = (uint64_t)E[k] + O[k - 1] + carry;
+      L[k] = (uint32_t)s;
+      carry = s >> 32;
+    }
+    uint64_t s8 = (uint64_t)Et + O[7] + carry;
+    L[8] = (uint32_t)s8;
+    L[9] = Ot + (uint32_t)(s8 >> 32);
+    const uint32_t t128[8] = {0xef8cfeb9u, 0xb075da81u, 0xa5b6cd8cu, 0xa7f12accu,
+                              0x7957bf7bu, 0x32c47504u, 0x48ffa25eu, 0x03d581d7u};  // 2^128 in Montgomery form
+    Fr T, c2 = Fr::zero(), c1 = Fr::zero(), c0 = Fr::zero();
+#pragma unroll
+    for (int k = 0; k < 8; k++) T.v[k] = t128[k];
+    c2.v[0] = L[8];
+    c2.v[1] = L[9];
+#pragma unroll
+    for (int k = 0; k < 4; k++) { c1.v[k] = L[4 + k]; c0.v[k] = L[k]; }
+    Fr acc = fe_to_mont(c2);
+    acc = fe_add(fe_mul(acc, T), fe_to_mont(c1));
+    acc = fe_add(fe_mul(acc, T), fe_to_mont(c0));
+    return fe_from_mont(acc);
+  }
+};
+
+// wneg[j] = -w[j]: the weights a negative integer multiplies
+__global__ void k_negate(const uint32_t* __restrict__ w, uint32_t* __restrict__ wneg, uint32_t c) {
+  GRID_STRIDE(j, c) fe_neg(Fr::load_nc(w + j * 8)).store(wneg + j * 8);
+}
+
 // ---- multilinear fold ---------------------------------------------------------------------
 // eq-weights of an axis of length c under challenges x[0..nv):  w[j] = prod_k (bit_k(j) ? x_k : 1 - x_k)
 __global__ void k_eq_weights(const uint32_t* __restrict__ x, uint32_t nv, uint32_t c,
@@ -191,12 +245,32 @@ k_fold_axis(const void* __restrict__ t, const uint32_t* __restrict__ w, uint32_t
   const uint32_t j0 = blockIdx.y * slice_len;
   const uint32_t j1 = min(c, j0 + slice_len);
   Fr acc = Fr::zero();
-  for (uint32_t j = j0; j < j1; j++) {
-    const uint64_t idx = (o * c + j) * gap + g;
-    Fr v;
-    if (FROM_I32) v = fe_from_i32<FrParams>(__ldg(reinterpret_cast<const int32_t*>(t) + idx));
-    else v = Fr::load_nc(reinterpret_cast<const uint32_t*>(t) + idx * 8);
-    acc = fe_add(acc, fe_mul(v, Fr::load_nc(w + (uint64_t)j * 8)));
+  if (FROM_I32) {
+    // int32 source: 4 bytes and eight multiply-adds per element; w[c..2c) holds the negated weights
+    const int32_t* ti = reinterpret_cast<const int32_t*>(t);
+    WideAcc wide;
+    wide.clear();
+    // eight loads in flight per thread: the loop is bound by memory latency otherwise
+    constexpr int U = 8;
+    for (uint32_t jb = j0; jb < j1; jb += U) {
+      int32_t xs[U];
+#pragma unroll
+      for (int k = 0; k < U; k++) xs[k] = jb + k < j1 ? __ldg(ti + (o * c + jb + k) * gap + g) : 0;
+#pragma unroll
+      for (int k = 0; k < U; k++) {
+        const int32_t x = xs[k];
+        const uint32_t ax = x < 0 ? 0u - (uint32_t)x : (uint32_t)x;
+        const uint32_t j = min(jb + k, j1 - 1);   // a zero past the end multiplies any valid weight
+        wide.mac(Fr::load_nc(w + ((uint64_t)j + (x < 0 ? c : 0u)) * 8), ax);
+      }
+    }
+    acc = wide.to_fr();
+  } else {
+    for (uint32_t j = j0; j < j1; j++) {
+      const uint64_t idx = (o * c + j) * gap + g;
+      Fr v = Fr::load_nc(reinterpret_cast<const uint32_t*>(t) + idx * 8);
+      acc = fe_add(acc, fe_mul(v, Fr::load_nc(w + (uint64_t)j * 8)));
+    }
   }
   acc.store(dst + ((uint64_t)blockIdx.y * n_out + og) * 8);
 }
@@ -218,12 +292,29 @@ k_fold_inner(const void* __restrict__ t, const uint32_t* __restrict__ w, uint32_
              uint32_t* __restrict__ out) {
   const uint64_t o = blockIdx.x;
   Fr acc = Fr::zero();
-  for (uint32_t j = threadIdx.x; j < c; j += SUM_THREADS) {
-    const uint64_t idx = o * c + j;
-    Fr v;
-    if (FROM_I32) v = fe_from_i32<FrParams>(__ldg(reinterpret_cast<const int32_t*>(t) + idx));
-    else v = Fr::load_nc(reinterpret_cast<const uint32_t*>(t) + idx * 8);
-    acc = fe_add(acc, fe_mul(v, Fr::load_nc(w + (uint64_t)j * 8)));
+  if (FROM_I32) {
+    const int32_t* ti = reinterpret_cast<const int32_t*>(t);
+    WideAcc wide;
+    wide.clear();
+    constexpr int U = 4;
+    for (uint32_t jb = threadIdx.x; jb < c; jb += U * SUM_THREADS) {
+      int32_t xs[U];
+#pragma unroll
+      for (int k = 0; k < U; k++) xs[k] = jb + k * SUM_THREADS < c ? __ldg(ti + o * c + jb + k * SUM_THREADS) : 0;
+#pragma unroll
+      for (int k = 0; k < U; k++) {
+        const int32_t x = xs[k];
+        const uint32_t ax = x < 0 ? 0u - (uint32_t)x : (uint32_t)x;
+        const uint32_t j = min(jb + k * SUM_THREADS, c - 1);
+        wide.mac(Fr::load_nc(w + ((uint64_t)j + (x < 0 ? c : 0u)) * 8), ax);
+      }
+    }
+    acc = wide.to_fr();
+  } else {
+    for (uint32_t j = threadIdx.x; j < c; j += SUM_THREADS) {
+      Fr v = Fr::load_nc(reinterpret_cast<const uint32_t*>(t) + (o * c + j) * 8);
+      acc = fe_add(acc, fe_mul(v, Fr::load_nc(w + (uint64_t)j * 8)));
+    }
   }
   acc = block_sum(acc);
   if (threadIdx.x == 0) acc.store(out + o * 8);
@@ -285,7 +376,7 @@ int fold_axis_async(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* 
     if (out_blocks < target) n_slices = (uint32_t)std::min<uint64_t>((target + out_blocks - 1) / out_blocks, (c + 15) / 16);
     if (n_slices < 1) n_slices = 1;
   }
-  size_t w_bytes = ((size_t)c * 32 + 255) & ~size_t(255);
+  size_t w_bytes = ((size_t)c * 32 * (FROM_I32 ? 2 : 1) + 255) & ~size_t(255);
   size_t p_bytes = n_slices > 1 ? (size_t)n_slices * n_out * 32 : 0;
   void* d_work = nullptr;
   int arc = arena_alloc(ctx, w_bytes + p_bytes, &d_work);
@@ -294,6 +385,10 @@ int fold_axis_async(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* 
   uint32_t* partial = reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(d_work) + w_bytes);
   k_eq_weights<<<ew_blocks(ctx, c), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_x, nv, c, w);
   ctx->launches += 1;
+  if (FROM_I32) {
+    k_negate<<<ew_blocks(ctx, c), EW_THREADS, 0, ctx->stream>>>(w, w + (size_t)c * 8, c);
+    ctx->launches += 1;
+  }
   if (gap == 1) {
     if (other > 0x7fffffffull) return fail(ctx, GRAPE_ERR_LIMIT, "fold: too many rows");
     k_fold_inner<FROM_I32><<<(uint32_t)other, SUM_THREADS, 0, ctx->stream>>>(d_t, w, c, (uint32_t*)d_out);

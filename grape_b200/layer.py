@@ -118,6 +118,7 @@ class FFNProver:
         self.swiglu = Lookup(ctx, s.swiglu_low, s.swiglu_len, swiglu_table)
 
     timing = False  # set to True to synchronise around every step and fill FFNTrace.seconds
+    prefetch_inputs = False  # set to True (page-locked inputs) to upload all tensors behind the first steps
 
     @contextlib.contextmanager
     def _phase(self, trace, name):
@@ -156,12 +157,40 @@ class FFNProver:
         for b in self.__dict__.pop("_pool", []):
             b.free()
 
+    def prefetch(self, t: dict):
+        """Starts the upload of every large int32 tensor of `t` on the copy stream (they should be
+        page-locked), so that the copies run behind the first proof steps; `_fr` picks them up."""
+        import ctypes as C
+        staged = self.__dict__.setdefault("_staged", {})
+        # copies are issued in the order the previous walk consumed the tensors (the copy stream is a
+        # queue: a tensor needed first must not wait behind the others); first walk: dictionary order
+        seen = self.__dict__.get("_use_order", [])
+        rank = {key: i for i, key in enumerate(seen)}
+        big = [v for v in t.values() if isinstance(v, np.ndarray) and v.dtype == np.int32 and v.nbytes >= (1 << 20)
+               and v.flags.c_contiguous]
+        big.sort(key=lambda v: rank.get(v.ctypes.data, len(rank)))
+        self._use_order = []
+        for v in big:
+            key = v.ctypes.data
+            if key in staged:
+                continue
+            buf = self._alloc(v.nbytes)
+            tk = C.c_uint32()
+            self.ctx._check(self.ctx.lib.grape_h2d_prefetch(self.ctx.handle, buf.ptr, key, v.nbytes, C.byref(tk)))
+            staged[key] = (buf, tk.value, v)     # keeps the host array alive until the copy is consumed
+
     def _fr(self, ints: np.ndarray):
         """int32 host tensor -> Fr tensor on the device, sized for row padding of the ffn axis."""
         flat = np.ascontiguousarray(ints, dtype=np.int32).reshape(-1)
         t0 = time.perf_counter()
-        d_int = self._alloc(flat.nbytes)
-        self.ctx._check(self.ctx.lib.grape_h2d(self.ctx.handle, d_int.ptr, flat.ctypes.data, flat.nbytes))
+        self.__dict__.setdefault("_use_order", []).append(flat.ctypes.data)
+        hit = self.__dict__.get("_staged", {}).pop(flat.ctypes.data, None)
+        if hit is not None:
+            d_int = hit[0]
+            self.ctx._check(self.ctx.lib.grape_prefetch_wait(self.ctx.handle, hit[1]))
+        else:
+            d_int = self._alloc(flat.nbytes)
+            self.ctx._check(self.ctx.lib.grape_h2d(self.ctx.handle, d_int.ptr, flat.ctypes.data, flat.nbytes))
         if self.timing:   # from page-locked host arrays the copy is asynchronous; wait only to attribute time
             self.ctx.sync()
             self.upload_seconds = getattr(self, "upload_seconds", 0.0) + time.perf_counter() - t0
@@ -178,8 +207,20 @@ class FFNProver:
 
     def _open(self, buf, size: int, e, N: int, trace: FFNTrace):
         trace.opens += 1
+        # the z vectors of a walk land in page-locked buffers that belong to the prover and are
+        # reused by the next walk (one per opening, in order): the proof's output area
+        zbufs = self.__dict__.setdefault("_zbufs", [])
+        new_n = (1 << log2ceil(N)) * 16
+        k = trace.opens - 1
+        if k == len(zbufs) or (k < len(zbufs) and zbufs[k].shape[0] != new_n):
+            arr = self.ctx.pinned_array((new_n, 8), np.uint32)
+            if k == len(zbufs):
+                zbufs.append(arr)
+            else:
+                zbufs[k] = arr
         with self._phase(trace, "open"):
-            return host.hyrax_open(self.ctx, self.table, buf, size, N, self.shape.layer_num, e, self.c, self.G)
+            return host.hyrax_open(self.ctx, self.table, buf, size, N, self.shape.layer_num, e, self.c, self.G,
+                                   z_out=zbufs[k])
 
     def _rescale(self, lk: Lookup, rem_ints, e, msm: int, open_N: int, q_claim: int, scale: int, trace, name):
         """Remainder lookup + opening + claim algebra (test/llm.cu:98-108 pattern)."""
@@ -205,6 +246,8 @@ class FFNProver:
         L, T, d, F = s.layer_num, s.tokens, s.dim, s.ffn
         lT, ld, lF = log2ceil(T), log2ceil(d), log2ceil(F)
         trace = FFNTrace()
+        if self.prefetch_inputs:
+            self.prefetch(t)
         # output opening and the skip split (test/llm.cu:75-92)
         out, size = self._fr(t["output"])
         e1 = self._draw(log2ceil(size))

@@ -65,6 +65,13 @@ int grape_rng_fr(grape_ctx* ctx, void* h_out, uint64_t n);
 int grape_dev_alloc(grape_ctx* ctx, size_t bytes, void** d_out);
 int grape_dev_free(grape_ctx* ctx, void* d_ptr);
 int grape_h2d(grape_ctx* ctx, void* d_dst, const void* h_src, size_t bytes); /* async */
+/* The same copy on a second stream, overlapping the kernels queued on the context's main stream
+ * (h_src page-locked).  It starts after the work queued so far; grape_prefetch_wait(ticket) makes
+ * the main stream wait for that copy and releases the ticket.  Lets a driver load the tensors of
+ * later steps while the current one is proven (the reference's driver loads synchronously,
+ * src/ioutils.cu:105-124). */
+int grape_h2d_prefetch(grape_ctx* ctx, void* d_dst, const void* h_src, size_t bytes, uint32_t* ticket);
+int grape_prefetch_wait(grape_ctx* ctx, uint32_t ticket);
 int grape_d2h(grape_ctx* ctx, void* h_dst, const void* d_src, size_t bytes); /* synchronises */
 int grape_d2d(grape_ctx* ctx, void* d_dst, const void* d_src, size_t bytes);
 int grape_dev_zero(grape_ctx* ctx, void* d_dst, size_t bytes);
