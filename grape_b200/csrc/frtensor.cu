@@ -212,9 +212,21 @@ struct WideAcc {
   }
 };
 
-// wneg[j] = -w[j]: the weights a negative integer multiplies
-__global__ void k_negate(const uint32_t* __restrict__ w, uint32_t* __restrict__ wneg, uint32_t c) {
-  GRID_STRIDE(j, c) fe_neg(Fr::load_nc(w + j * 8)).store(wneg + j * 8);
+// Signed integers enter the wide sums biased: x + 2^31 is a plain 32-bit unsigned number, and
+//   sum_j w_j x_j = sum_j w_j (x_j + 2^31) - 2^31 * sum_j w_j,
+// where the last sum does not depend on the tensor: it is formed once per slice of j by this kernel
+// (corr[s] = 2^31 * sum of w over slice s, a field element) and subtracted from every output.
+__global__ void __launch_bounds__(SUM_THREADS) k_bias_correction(const uint32_t* __restrict__ w, uint32_t c,
+                                                                 uint32_t slice_len, uint32_t* __restrict__ corr) {
+  const uint32_t j0 = blockIdx.x * slice_len, j1 = min(c, j0 + slice_len);
+  Fr acc = Fr::zero();
+  for (uint32_t j = j0 + threadIdx.x; j < j1; j += SUM_THREADS) acc = fe_add(acc, Fr::load_nc(w + (uint64_t)j * 8));
+  acc = block_sum(acc);
+  if (threadIdx.x == 0) {
+    Fr two31 = Fr::zero();
+    two31.v[0] = 0x80000000u;
+    fe_mul(acc, fe_to_mont(two31)).store(corr + (uint64_t)blockIdx.x * 8);
+  }
 }
 
 // ---- multilinear fold ---------------------------------------------------------------------
@@ -238,7 +250,7 @@ constexpr int FOLD_THREADS = 128;
 template <bool FROM_I32>
 __global__ void __launch_bounds__(FOLD_THREADS)
 k_fold_axis(const void* __restrict__ t, const uint32_t* __restrict__ w, uint32_t c, uint64_t gap,
-            uint64_t n_out, uint32_t slice_len, uint32_t* __restrict__ dst) {
+            uint64_t n_out, uint32_t slice_len, uint32_t* __restrict__ dst, const uint32_t* __restrict__ corr) {
   const uint64_t og = (uint64_t)blockIdx.x * FOLD_THREADS + threadIdx.x;
   if (og >= n_out) return;
   const uint64_t o = og / gap, g = og % gap;
@@ -246,25 +258,28 @@ k_fold_axis(const void* __restrict__ t, const uint32_t* __restrict__ w, uint32_t
   const uint32_t j1 = min(c, j0 + slice_len);
   Fr acc = Fr::zero();
   if (FROM_I32) {
-    // int32 source: 4 bytes and eight multiply-adds per element; w[c..2c) holds the negated weights
-    const int32_t* ti = reinterpret_cast<const int32_t*>(t);
+    // int32 source: 4 bytes and eight multiply-adds per element (biased to unsigned, see k_bias_correction)
+    const int32_t* tp = reinterpret_cast<const int32_t*>(t) + (o * c + j0) * gap + g;
+    const uint32_t* wp = w + (uint64_t)j0 * 8;
     WideAcc wide;
     wide.clear();
-    // eight loads in flight per thread: the loop is bound by memory latency otherwise
-    constexpr int U = 8;
-    for (uint32_t jb = j0; jb < j1; jb += U) {
-      int32_t xs[U];
+    constexpr int U = 8;  // loads in flight per thread
+    uint32_t j = j0;
+    for (; j + U <= j1; j += U) {
+      uint32_t xs[U];
 #pragma unroll
-      for (int k = 0; k < U; k++) xs[k] = jb + k < j1 ? __ldg(ti + (o * c + jb + k) * gap + g) : 0;
+      for (int k = 0; k < U; k++) xs[k] = (uint32_t)__ldg(tp + (uint64_t)k * gap) ^ 0x80000000u;
 #pragma unroll
-      for (int k = 0; k < U; k++) {
-        const int32_t x = xs[k];
-        const uint32_t ax = x < 0 ? 0u - (uint32_t)x : (uint32_t)x;
-        const uint32_t j = min(jb + k, j1 - 1);   // a zero past the end multiplies any valid weight
-        wide.mac(Fr::load_nc(w + ((uint64_t)j + (x < 0 ? c : 0u)) * 8), ax);
-      }
+      for (int k = 0; k < U; k++) wide.mac(Fr::load_nc(wp + k * 8), xs[k]);
+      tp += (uint64_t)U * gap;
+      wp += U * 8;
     }
-    acc = wide.to_fr();
+    for (; j < j1; j++) {
+      wide.mac(Fr::load_nc(wp), (uint32_t)__ldg(tp) ^ 0x80000000u);
+      tp += gap;
+      wp += 8;
+    }
+    acc = fe_sub(wide.to_fr(), Fr::load_nc(corr + (uint64_t)blockIdx.y * 8));
   } else {
     for (uint32_t j = j0; j < j1; j++) {
       const uint64_t idx = (o * c + j) * gap + g;
@@ -289,24 +304,23 @@ __global__ void k_sum_slices(const uint32_t* __restrict__ partial, uint32_t n_sl
 template <bool FROM_I32>
 __global__ void __launch_bounds__(SUM_THREADS)
 k_fold_inner(const void* __restrict__ t, const uint32_t* __restrict__ w, uint32_t c,
-             uint32_t* __restrict__ out) {
+             uint32_t* __restrict__ out, const uint32_t* __restrict__ corr) {
   const uint64_t o = blockIdx.x;
   Fr acc = Fr::zero();
   if (FROM_I32) {
-    const int32_t* ti = reinterpret_cast<const int32_t*>(t);
+    // biased integers; the correction 2^31 * sum_j w_j is the same for every row (corr[0])
+    const int32_t* ti = reinterpret_cast<const int32_t*>(t) + o * c;
     WideAcc wide;
     wide.clear();
     constexpr int U = 4;
     for (uint32_t jb = threadIdx.x; jb < c; jb += U * SUM_THREADS) {
-      int32_t xs[U];
+      uint32_t xs[U];
 #pragma unroll
-      for (int k = 0; k < U; k++) xs[k] = jb + k * SUM_THREADS < c ? __ldg(ti + o * c + jb + k * SUM_THREADS) : 0;
+      for (int k = 0; k < U; k++) xs[k] = jb + k * SUM_THREADS < c ? (uint32_t)__ldg(ti + jb + k * SUM_THREADS) ^ 0x80000000u : 0u;
 #pragma unroll
       for (int k = 0; k < U; k++) {
-        const int32_t x = xs[k];
-        const uint32_t ax = x < 0 ? 0u - (uint32_t)x : (uint32_t)x;
-        const uint32_t j = min(jb + k * SUM_THREADS, c - 1);
-        wide.mac(Fr::load_nc(w + ((uint64_t)j + (x < 0 ? c : 0u)) * 8), ax);
+        const uint32_t j = min(jb + k * SUM_THREADS, c - 1);   // a zero past the end multiplies any valid weight
+        wide.mac(Fr::load_nc(w + (uint64_t)j * 8), xs[k]);
       }
     }
     acc = wide.to_fr();
@@ -317,7 +331,10 @@ k_fold_inner(const void* __restrict__ t, const uint32_t* __restrict__ w, uint32_
     }
   }
   acc = block_sum(acc);
-  if (threadIdx.x == 0) acc.store(out + o * 8);
+  if (threadIdx.x == 0) {
+    if (FROM_I32) acc = fe_sub(acc, Fr::load_nc(corr));
+    acc.store(out + o * 8);
+  }
 }
 
 void eq_weights_async(grape_ctx* ctx, const void* d_x, uint32_t nv, uint32_t c, void* d_w) {
@@ -376,7 +393,7 @@ int fold_axis_async(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* 
     if (out_blocks < target) n_slices = (uint32_t)std::min<uint64_t>((target + out_blocks - 1) / out_blocks, (c + 15) / 16);
     if (n_slices < 1) n_slices = 1;
   }
-  size_t w_bytes = ((size_t)c * 32 * (FROM_I32 ? 2 : 1) + 255) & ~size_t(255);
+  size_t w_bytes = ((size_t)c * 32 + 255) & ~size_t(255);
   size_t p_bytes = n_slices > 1 ? (size_t)n_slices * n_out * 32 : 0;
   void* d_work = nullptr;
   int arc = arena_alloc(ctx, w_bytes + p_bytes, &d_work);
@@ -385,21 +402,24 @@ int fold_axis_async(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* 
   uint32_t* partial = reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(d_work) + w_bytes);
   k_eq_weights<<<ew_blocks(ctx, c), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_x, nv, c, w);
   ctx->launches += 1;
+  uint32_t* corr = nullptr;
+  const uint32_t slice_len = gap == 1 ? c : (c + n_slices - 1) / n_slices;
   if (FROM_I32) {
-    k_negate<<<ew_blocks(ctx, c), EW_THREADS, 0, ctx->stream>>>(w, w + (size_t)c * 8, c);
+    int crc = arena_alloc_t(ctx, (size_t)n_slices * 8 + 8, &corr);
+    if (crc) return crc;
+    k_bias_correction<<<gap == 1 ? 1 : n_slices, SUM_THREADS, 0, ctx->stream>>>(w, c, slice_len, corr);
     ctx->launches += 1;
   }
   if (gap == 1) {
     if (other > 0x7fffffffull) return fail(ctx, GRAPE_ERR_LIMIT, "fold: too many rows");
-    k_fold_inner<FROM_I32><<<(uint32_t)other, SUM_THREADS, 0, ctx->stream>>>(d_t, w, c, (uint32_t*)d_out);
+    k_fold_inner<FROM_I32><<<(uint32_t)other, SUM_THREADS, 0, ctx->stream>>>(d_t, w, c, (uint32_t*)d_out, corr);
     ctx->launches += 1;
   } else {
-    uint32_t slice_len = (c + n_slices - 1) / n_slices;
     dim3 grid((uint32_t)((n_out + FOLD_THREADS - 1) / FOLD_THREADS), n_slices);
+    uint32_t* fold_dst = n_slices > 1 ? partial : (uint32_t*)d_out;
     {
       ProfScope prof(ctx);
-      k_fold_axis<FROM_I32><<<grid, FOLD_THREADS, 0, ctx->stream>>>(
-          d_t, w, c, gap, n_out, slice_len, n_slices > 1 ? partial : (uint32_t*)d_out);
+      k_fold_axis<FROM_I32><<<grid, FOLD_THREADS, 0, ctx->stream>>>(d_t, w, c, gap, n_out, slice_len, fold_dst, corr);
     }
     ctx->launches += 1;
     if (n_slices > 1) {
