@@ -263,7 +263,7 @@ k_fold_axis(const void* __restrict__ t, const uint32_t* __restrict__ w, uint32_t
     const uint32_t* wp = w + (uint64_t)j0 * 8;
     WideAcc wide;
     wide.clear();
-    constexpr int U = 8;  // loads in flight per thread
+    constexpr int U = 8;  // loads in flight per thread (16 was slower)
     uint32_t j = j0;
     for (; j + U <= j1; j += U) {
       uint32_t xs[U];
