@@ -113,6 +113,7 @@ def _declare(lib):
     f("grape_prof_read", [vp, C.POINTER(C.c_float), C.POINTER(u32)])
     f("grape_prove_matmul", [vp, vp, vp, u32, u32, u32, u32, vp, u32, vp, u32, vp, vp, vp, u32, C.POINTER(u32)])
     f("grape_lookup_set_bucket_commit", [vp, C.c_int])
+    f("grape_prove_matmul_i32", [vp, vp, vp, u32, u32, u32, u32, vp, u32, vp, u32, vp, vp, vp, u32, C.POINTER(u32)])
     f("grape_prove_matmul_partial", [vp, vp, vp, u32, u32, u32, u32, vp, u32, vp, u32, vp, C.POINTER(u32)])
     f("grape_prove_matmul_finish", [vp, vp, u32, u32, u32, u32, u32, vp, u32, vp, u32, vp, vp, vp, u32, C.POINTER(u32)])
     f("grape_prove_elemul", [vp, vp, vp, u32, u32, u32, vp, u32, vp, u32, vp, vp, vp, u32, C.POINTER(u32)])

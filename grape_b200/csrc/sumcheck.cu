@@ -262,7 +262,8 @@ struct MatmulRun {
   std::vector<RoundInfo> rounds;
 };
 
-static int matmul_enqueue(grape_ctx* ctx, void* d_A, void* d_B, uint32_t L, uint32_t N, uint32_t M, uint32_t K,
+template <bool FROM_I32 = false>
+static int matmul_enqueue(grape_ctx* ctx, const void* d_A, const void* d_B, uint32_t L, uint32_t N, uint32_t M, uint32_t K,
                           const HostFr* u, uint32_t n_u, const HostFr* v, uint32_t n_v, MatmulRun& run) {
   if (!L || !N || !M || !K) return fail(ctx, GRAPE_ERR_INVALID, "prove_matmul: zero dimension");
   const uint32_t lL = log2ceil(L), lN = log2ceil(N), lM = log2ceil(M), lK = log2ceil(K);
@@ -287,8 +288,8 @@ static int matmul_enqueue(grape_ctx* ctx, void* d_A, void* d_B, uint32_t L, uint
   if ((rc = arena_alloc_t(ctx, (size_t)L * 8 + 8, &run.wl))) return rc;
   uint32_t *d_u = run.d_u, *d_v = run.d_v, *a_ = run.a_, *b_ = run.b_;
   // a_[l][k] = sum_n eq(u_N, n) A[l][n][k],  b_[l][k] = sum_m eq(u_M, m) B[l][m][k]
-  if ((rc = fold_axis_async<false>(ctx, d_A, (uint64_t)L * N * K, d_u + (size_t)lM * 8, N, K, a_))) return rc;
-  if ((rc = fold_axis_async<false>(ctx, d_B, (uint64_t)L * M * K, d_u, M, K, b_))) return rc;
+  if ((rc = fold_axis_async<FROM_I32>(ctx, d_A, (uint64_t)L * N * K, d_u + (size_t)lM * 8, N, K, a_))) return rc;
+  if ((rc = fold_axis_async<FROM_I32>(ctx, d_B, (uint64_t)L * M * K, d_u, M, K, b_))) return rc;
 
   std::vector<RoundInfo>& rounds = run.rounds;
   uint64_t in_size = LK, out_size = LK / 2;
@@ -349,6 +350,31 @@ extern "C" int grape_prove_matmul(grape_ctx* ctx, void* d_A, void* d_B, uint32_t
   MatmulRun run;
   int rc = matmul_enqueue(ctx, d_A, d_B, L, N, M, K, reinterpret_cast<const HostFr*>(h_u), n_u,
                           reinterpret_cast<const HostFr*>(h_v), n_v, run);
+  if (rc) return rc;
+  std::vector<HostFr> transcript;
+  rc = finish_two(ctx, run.rounds, run.sums, run.a_, run.b_, reinterpret_cast<HostFr*>(h_claim),
+                  reinterpret_cast<HostFr*>(h_out_claims), &transcript, "prove_matmul");
+  if (n_rounds) *n_rounds = (uint32_t)(transcript.size() / 4);
+  if (h_transcript) {
+    size_t n = std::min<size_t>(transcript.size(), (size_t)transcript_capacity * 4);
+    memcpy(h_transcript, transcript.data(), n * 32);
+  }
+  return rc;
+}
+
+// prove_matmul on the int32 tensors the reference builds its FrTensors from (FrTensor(uint, int*),
+// src/fr-tensor.cu:30-46,190-197, immediately before every prove_matmul of its drivers).  Same
+// claims and transcript as converting to Fr first and calling grape_prove_matmul; the two axis
+// folds, which dominate the proof, then read 4 bytes per element instead of 32 and skip the field
+// multiplication per element.  The inputs are left intact.
+extern "C" int grape_prove_matmul_i32(grape_ctx* ctx, const int32_t* d_A, const int32_t* d_B, uint32_t L, uint32_t N,
+                                      uint32_t M, uint32_t K, const void* h_u, uint32_t n_u, const void* h_v,
+                                      uint32_t n_v, void* h_claim, void* h_out_claims, void* h_transcript,
+                                      uint32_t transcript_capacity, uint32_t* n_rounds) {
+  if (!ctx || !d_A || !d_B || !h_u || !h_v || !h_claim || !h_out_claims) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
+  MatmulRun run;
+  int rc = matmul_enqueue<true>(ctx, d_A, d_B, L, N, M, K, reinterpret_cast<const HostFr*>(h_u), n_u,
+                                reinterpret_cast<const HostFr*>(h_v), n_v, run);
   if (rc) return rc;
   std::vector<HostFr> transcript;
   rc = finish_two(ctx, run.rounds, run.sums, run.a_, run.b_, reinterpret_cast<HostFr*>(h_claim),

@@ -379,6 +379,22 @@ def prove_matmul(ctx: Context, d_A, d_B, L: int, N: int, M: int, K: int, u, v, c
     return a, b, decode_field(hc)[0], polys
 
 
+def prove_matmul_i32(ctx: Context, d_A_i32, d_B_i32, L: int, N: int, M: int, K: int, u, v, claim: int):
+    """:func:`prove_matmul` on the int32 device tensors the Fr tensors would be built from (inputs kept)."""
+    hu, hv = _fr_host(u), _fr_host(v)
+    hc = _fr_host([claim])
+    out = np.zeros((2, 8), dtype=np.uint32)
+    cap = len(u) + len(v) + 4
+    tr = np.zeros((cap, 4, 8), dtype=np.uint32)
+    nr = C.c_uint32()
+    ctx._check(ctx.lib.grape_prove_matmul_i32(ctx.handle, _p(d_A_i32), _p(d_B_i32), L, N, M, K, hu.ctypes.data, len(u),
+                                              hv.ctypes.data, len(v), hc.ctypes.data, out.ctypes.data,
+                                              tr.ctypes.data, cap, C.byref(nr)))
+    a, b = decode_field(out)
+    polys = [decode_field(tr[i]) for i in range(nr.value)]
+    return a, b, decode_field(hc)[0], polys
+
+
 def matmul_partial_elems(L: int, K_local: int) -> int:
     """Field elements one prover contributes to the exchange of the sharded ``prove_matmul``."""
     rounds = max(L - 1, 0).bit_length() + max(K_local - 1, 0).bit_length()

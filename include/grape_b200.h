@@ -175,6 +175,15 @@ int grape_prove_matmul(grape_ctx* ctx, void* d_A, void* d_B, uint32_t L, uint32_
                        void* h_out_claims, void* h_transcript, uint32_t transcript_capacity,
                        uint32_t* n_rounds);
 
+/* prove_matmul straight from the int32 tensors that the reference turns into FrTensors right before
+ * the call (FrTensor(uint size, int* data), src/fr-tensor.cu:190-197; e.g. test/matmul.cu).  Same
+ * outputs as grape_fr_from_i32 on both tensors followed by grape_prove_matmul; d_A and d_B are
+ * left intact.  A veneer FrTensor that still holds its int32 source can bind prove_matmul here. */
+int grape_prove_matmul_i32(grape_ctx* ctx, const int32_t* d_A, const int32_t* d_B, uint32_t L, uint32_t N,
+                           uint32_t M, uint32_t K, const void* h_u, uint32_t n_u, const void* h_v,
+                           uint32_t n_v, void* h_claim, void* h_out_claims, void* h_transcript,
+                           uint32_t transcript_capacity, uint32_t* n_rounds);
+
 /* prove_matmul split over P = 2^p provers (GPUs), one exchange in total.  No reference counterpart:
  * the reference proves on one GPU (src/prove.cu:175-210); the result and the transcript are
  * bit-identical to grape_prove_matmul on the unsharded tensors.

@@ -40,6 +40,11 @@ def test_prove_matmul(gctx, L, N, M, K):
     got = host.prove_matmul(gctx, dA, dB, L, N, M, K, u, v, claim)
     assert got[0] == want[0] and got[1] == want[1] and got[2] == want[2]
     assert got[3] == _pad4(want[3])
+    # the same proof straight from the int32 tensors
+    import numpy as np
+    to_i32 = lambda X: np.array([x if x < R // 2 else x - R for x in X], dtype=np.int32)
+    got_i = host.prove_matmul_i32(gctx, gctx.upload(to_i32(A)), gctx.upload(to_i32(B)), L, N, M, K, u, v, claim)
+    assert got_i == got
 
 
 def test_prove_matmul_rejects_wrong_claim(gctx):
