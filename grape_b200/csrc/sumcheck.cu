@@ -117,6 +117,43 @@ k_round_two(uint32_t* __restrict__ A, uint32_t* __restrict__ B, uint64_t in_size
   block_reduce_store<3>(acc, partial + (uint64_t)blockIdx.x * 3 * 8);
 }
 
+// The last rounds of an unweighted two-tensor sumcheck in ONE launch: once the tensors are short
+// (a few thousand elements) a round is far shorter than a kernel launch, so a single block runs
+// round after round with a block barrier in between.  Round r folds by v[v_first - r] and leaves its
+// three sums in sums[r]; sizes follow the reference's rule (in_size, then halving powers of two).
+constexpr uint32_t TAIL_MAX = 8192;
+__global__ void __launch_bounds__(RT)
+k_rounds_tail(uint32_t* __restrict__ A, uint32_t* __restrict__ B, uint64_t in_size, uint64_t out_size, uint32_t n_rounds,
+              const uint32_t* __restrict__ v, uint32_t v_first, uint32_t* __restrict__ sums) {
+  for (uint32_t r = 0; r < n_rounds; r++) {
+    const Fr vv = Fr::load_nc(v + (uint64_t)(v_first - r) * 8);
+    Fr acc[3] = {Fr::zero(), Fr::zero(), Fr::zero()};
+    for (uint64_t g = threadIdx.x; g < out_size; g += RT) {
+      Fr Ab = Fr::load(A + g * 8), Bb = Fr::load(B + g * 8);
+      Fr Aa, Ba;
+      if (g + out_size < in_size) {
+        Aa = fe_sub(Fr::load(A + (g + out_size) * 8), Ab);
+        Ba = fe_sub(Fr::load(B + (g + out_size) * 8), Bb);
+      } else {
+        Aa = fe_neg(Ab);
+        Ba = fe_neg(Bb);
+      }
+      fe_add(Ab, fe_mul(Aa, vv)).store(A + g * 8);
+      fe_add(Bb, fe_mul(Ba, vv)).store(B + g * 8);
+      Fr c0 = fe_mul(Ab, Bb);
+      Fr c2 = fe_mul(Aa, Ba);
+      Fr mid = fe_mul(fe_add(Aa, Ab), fe_add(Ba, Bb));
+      acc[0] = fe_add(acc[0], c0);
+      acc[1] = fe_add(acc[1], fe_sub(fe_sub(mid, c0), c2));
+      acc[2] = fe_add(acc[2], c2);
+    }
+    block_reduce_store<3>(acc, sums + (uint64_t)r * 3 * 8);
+    __syncthreads();  // the folded values and the shared scratch are settled before the next round
+    in_size = out_size;
+    out_size /= 2;
+  }
+}
+
 // One round over one tensor with J weight sets (combine_claims; reference: the three-pointer
 // sumcheck_kernel, src/prove.cu:14-27, plus two full evaluations per claim).  For every pair:
 //   X(t) = Xb + t*Xa; per claim j accumulate w_j*Xb and w_j*Xa with w_j = whi_j[g >> lo_bits] * wlo_j[g & mask];
@@ -307,6 +344,13 @@ static int matmul_enqueue(grape_ctx* ctx, const void* d_A, const void* d_B, uint
   in_size = K;
   out_size = lK ? (uint64_t(1) << (lK - 1)) : 0;
   for (uint32_t i = 0; i < lK; i++) {  // phase 2: inner-product variables, top first
+    if (in_size <= TAIL_MAX) {  // all remaining rounds in one launch
+      k_rounds_tail<<<1, RT, 0, ctx->stream>>>(a_, b_, in_size, out_size, lK - i, d_v, lK - i - 1,
+                                               run.sums + (size_t)rounds.size() * 3 * 8);
+      ctx->launches += 1;
+      for (; i < lK; i++) rounds.push_back({false, fr_zero(), v[lK - i - 1]});
+      break;
+    }
     PairWeights pw{nullptr, nullptr, 1};
     launch_round_two<false, false>(ctx, a_, b_, in_size, out_size, d_v + (size_t)(lK - i - 1) * 8, pw, run.partial,
                                    run.sums + (size_t)rounds.size() * 3 * 8);

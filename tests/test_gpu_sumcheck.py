@@ -19,7 +19,8 @@ def _pad4(polys):
     return [list(p) + [0] * (4 - len(p)) for p in polys]
 
 
-@pytest.mark.parametrize("L,N,M,K", [(1, 4, 8, 6), (2, 4, 2, 6), (4, 2, 4, 11), (1, 2, 2, 8), (1, 16, 8, 300), (2, 4, 8, 64), (1, 3, 8, 33)])
+@pytest.mark.parametrize("L,N,M,K", [(1, 4, 8, 6), (2, 4, 2, 6), (4, 2, 4, 11), (1, 2, 2, 8), (1, 16, 8, 300), (2, 4, 8, 64), (1, 3, 8, 33),
+                                     (1, 2, 2, 9000), (2, 2, 2, 16384)])  # the last two start above the fused-tail size
 def test_prove_matmul(gctx, L, N, M, K):
     from grape_b200 import host
     rng = random.Random(L * 1000 + N * 100 + M * 10 + K)
