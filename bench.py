@@ -306,6 +306,11 @@ def layer_proof(ctx, layers: int, window_bits: int, scope: str, seed: int = 0xC5
     return out
 
 
+def layer_weight_rows() -> int:
+    from grape_b200 import workloads as wl
+    return wl.layer_weight_elements() // WD
+
+
 def run_own(args):
     import grape_b200 as g
     from grape_b200 import workloads as wl
@@ -319,6 +324,12 @@ def run_own(args):
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    # The reference's own kernels are timed first, while this process holds nothing on the GPU
+    # (timed after this library's runs, with its context and 8 GiB table alive, the other process
+    # measured up to three times slower).
+    ref_cuda = None
+    if world == 1 and args.gens == WD and not args.rows:
+        ref_cuda = reference_cuda(layer_weight_rows(), 2)
     ctx = g.Context(local_rank)
 
     wd = args.gens
@@ -438,8 +449,8 @@ def run_own(args):
             "gpu_launches": int(launches), "roofline": roofline, "device_status": status,
             "table_bytes": table.nbytes}
 
-    if wd == WD and not args.rows:
-        line["reference_cuda"] = reference_cuda(rows, 2)
+    if ref_cuda is not None:
+        line["reference_cuda"] = ref_cuda
     if args.proof_layers:
         line["layer_proof"] = layer_proof(ctx, args.proof_layers, args.proof_window_bits, args.proof_scope)
     if not args.no_cpu_baseline and wd == WD:
