@@ -527,6 +527,22 @@ def run_secondary(args):
                 "from_int32_ms": float(np.mean(times_i32)),
                 "from_int32_note": "grape_prove_matmul_i32 on the int32 tensors the Fr tensors are built from: same "
                                    "claims and transcript, no conversion pass, folds at 4 B per element"}
+        # host-core baseline and full-size parity: the C restatement of the reference's prove_matmul on all
+        # host cores, same tensors, same challenges; its claims and round polynomials must equal the GPU's
+        if not args.no_cpu_baseline:
+            from oracle import cport
+            cport.build()
+            enc = lambda xs: host.encode_field(xs)
+            t0 = time.perf_counter()
+            rc, ca, cb, cfinal, ctr = cport.prove_matmul_l1(A, B, N, M, K, enc(u), enc(v), enc([claim]))
+            cpu_s = time.perf_counter() - t0
+            same = (rc == 0 and host.decode_field(ca.reshape(1, 8))[0] == r_i32[0]
+                    and host.decode_field(cb.reshape(1, 8))[0] == r_i32[1]
+                    and host.decode_field(cfinal.reshape(1, 8))[0] == r_i32[2]
+                    and [host.decode_field(ctr[i]) for i in range(ctr.shape[0])] == [p[:3] for p in r_i32[3]])
+            line["cpu_baseline"] = {"value": cpu_s * 1e3, "unit": "ms", "cores": cport.threads(), "kind": "port",
+                                    "sample": "the full C2 proof once (int32 -> Fr, two folds, 12 rounds)",
+                                    "matches_gpu_claims_and_transcript": bool(same)}
         ctx.sync()
         line["reference_cuda"] = reference_cuda_secondary(
             "matmul-bench", args.shrink, 3, "reference CUDA prove_matmul (unmodified sources, libff stand-in), same shape, "

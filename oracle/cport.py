@@ -101,5 +101,24 @@ def fr_fold(t: np.ndarray, ntot: int, x: np.ndarray, c: int, idx: int, gap: int)
     return t[: ntot // c]
 
 
+def prove_matmul_l1(A: np.ndarray, B: np.ndarray, N: int, M: int, K: int, u: np.ndarray, v: np.ndarray, claim: np.ndarray):
+    """``prove_matmul`` for one layer on int32 tensors A [N][K], B [M][K]; u, v, claim are uint32[*, 8]
+    Montgomery records.  Returns (rc, a_claim, b_claim, final_claim, transcript[rounds, 3, 8])."""
+    A = np.ascontiguousarray(A, dtype=np.int32).reshape(-1)
+    B = np.ascontiguousarray(B, dtype=np.int32).reshape(-1)
+    u = np.ascontiguousarray(u, dtype=np.uint32).reshape(-1, 8)
+    v = np.ascontiguousarray(v, dtype=np.uint32).reshape(-1, 8)
+    cl = np.array(claim, dtype=np.uint32).reshape(8).copy()
+    rounds = max(K - 1, 0).bit_length()
+    a, b = np.zeros(8, dtype=np.uint32), np.zeros(8, dtype=np.uint32)
+    tr = np.zeros((max(rounds, 1), 3, 8), dtype=np.uint32)
+    f = lib().oracle_prove_matmul_l1
+    f.restype = C.c_int
+    rc = f(C.c_void_p(A.ctypes.data), C.c_void_p(B.ctypes.data), C.c_uint32(N), C.c_uint32(M), C.c_uint32(K),
+           C.c_void_p(u.ctypes.data), C.c_void_p(v.ctypes.data), C.c_void_p(cl.ctypes.data), C.c_void_p(a.ctypes.data),
+           C.c_void_p(b.ctypes.data), C.c_void_p(tr.ctypes.data))
+    return rc, a, b, cl, tr[:rounds]
+
+
 if __name__ == "__main__":
     print(build(force=True))

@@ -443,6 +443,103 @@ void oracle_fr_fold(fe* t, uint64_t ntot, const fe* x, uint32_t c, uint32_t id, 
   for (uint64_t o = 1; o < other; o++) memmove(&t[o * gap], &t[o * dim], gap * sizeof(fe));
 }
 
+/* prove_matmul (src/prove.cu:175-210 with matmul_sumcheck_phase2, :85-117) for one layer (L = 1):
+ * A is [N][K], B is [M][K], both int32.  u and v are the challenge vectors, *claim the claimed value of
+ * the product's multilinear extension at u.  Writes the two final claims, the claim after the last
+ * round, and three coefficients per round.  Returns 0, or 1 + the index of the first round whose
+ * check p(0) + p(1) == claim fails (the reference throws there), or -1 when A*B*eq != claim at the end. */
+static uint32_t log2ceil_u32(uint64_t n) {
+  uint32_t r = 0;
+  if (n == 0) return 0;
+  n--;
+  while (n) { n >>= 1; r++; }
+  return r;
+}
+
+int oracle_prove_matmul_l1(const int32_t* A, const int32_t* B, uint32_t N, uint32_t M, uint32_t K, const fe* u,
+                           const fe* v, fe* claim, fe* out_a, fe* out_b, fe* transcript) {
+  fe* a = (fe*)malloc((size_t)N * K * sizeof(fe));
+  fe* b = (fe*)malloc((size_t)M * K * sizeof(fe));
+  if (!a || !b) { free(a); free(b); return -2; }
+  oracle_fr_from_i32(A, a, (uint64_t)N * K);
+  oracle_fr_from_i32(B, b, (uint64_t)M * K);
+  oracle_fr_fold(a, (uint64_t)N * K, u, N, log2ceil_u32(M), K);
+  oracle_fr_fold(b, (uint64_t)M * K, u, M, 0, K);
+  const uint32_t rounds = log2ceil_u32(K);
+  uint64_t in_size = K, out_size = rounds ? ((uint64_t)1 << (rounds - 1)) : 0;
+  int rc = 0;
+  const int nt = oracle_threads();
+  fe* part = (fe*)calloc((size_t)nt * 3, sizeof(fe));
+  for (uint32_t i = 0; i < rounds && rc == 0; i++) {
+    const fe* vn = &v[rounds - i - 1];
+    memset(part, 0, (size_t)nt * 3 * sizeof(fe));
+#pragma omp parallel num_threads(nt)
+    {
+      int tid = 0;
+#ifdef _OPENMP
+      tid = omp_get_thread_num();
+#endif
+      fe s0, s1, s2;
+      memset(&s0, 0, sizeof s0);
+      memset(&s1, 0, sizeof s1);
+      memset(&s2, 0, sizeof s2);
+#pragma omp for
+      for (int64_t g = 0; g < (int64_t)out_size; g++) {
+        fe Aa, Ba, Ab = a[g], Bb = b[g], t0, t1;
+        if ((uint64_t)g + out_size < in_size) {
+          fe_sub(&FR, &Aa, &a[g + out_size], &Ab);
+          fe_sub(&FR, &Ba, &b[g + out_size], &Bb);
+        } else {
+          fe_neg(&FR, &Aa, &Ab);
+          fe_neg(&FR, &Ba, &Bb);
+        }
+        fe_mul(&FR, &t0, &Aa, vn);
+        fe_add(&FR, &a[g], &t0, &Ab);
+        fe_mul(&FR, &t0, &Ba, vn);
+        fe_add(&FR, &b[g], &t0, &Bb);
+        fe_mul(&FR, &t0, &Ab, &Bb);
+        fe_add(&FR, &s0, &s0, &t0);
+        fe_mul(&FR, &t0, &Aa, &Bb);
+        fe_mul(&FR, &t1, &Ab, &Ba);
+        fe_add(&FR, &t0, &t0, &t1);
+        fe_add(&FR, &s1, &s1, &t0);
+        fe_mul(&FR, &t0, &Aa, &Ba);
+        fe_add(&FR, &s2, &s2, &t0);
+      }
+      part[3 * tid] = s0;
+      part[3 * tid + 1] = s1;
+      part[3 * tid + 2] = s2;
+    }
+    fe p[3];
+    memset(p, 0, sizeof p);
+    for (int t = 0; t < nt; t++)
+      for (int k = 0; k < 3; k++) fe_add(&FR, &p[k], &p[k], &part[3 * t + k]);
+    for (int k = 0; k < 3; k++) transcript[3 * i + k] = p[k];
+    fe s, t2;
+    fe_add(&FR, &s, &p[0], &p[0]);   /* p(0) + p(1) = 2 c0 + c1 + c2 */
+    fe_add(&FR, &s, &s, &p[1]);
+    fe_add(&FR, &s, &s, &p[2]);
+    if (!fe_eq(&s, claim)) { rc = 1 + (int)i; break; }
+    fe_mul(&FR, &t2, &p[2], vn);     /* claim = (c2 v + c1) v + c0 */
+    fe_add(&FR, &t2, &t2, &p[1]);
+    fe_mul(&FR, &t2, &t2, vn);
+    fe_add(&FR, claim, &t2, &p[0]);
+    in_size = out_size;
+    out_size /= 2;
+  }
+  if (rc == 0) {
+    fe prod;
+    fe_mul(&FR, &prod, &a[0], &b[0]);
+    if (!fe_eq(&prod, claim)) rc = -1;
+    *out_a = a[0];
+    *out_b = b[0];
+  }
+  free(part);
+  free(a);
+  free(b);
+  return rc;
+}
+
 /* ------------------------------------------------------------------------------------------ */
 /* Host scalar / group operations and the seeded random stream, exported for the libff stand-in */
 /* that lets the reference's own sources compile (oracle/ref_shim).                              */

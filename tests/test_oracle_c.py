@@ -64,3 +64,32 @@ def test_fold_matches_bigint():
         x = [rng.randrange(R) for _ in range(6)]
         got = _dec(cport.fr_fold(_enc(t, R), n, _enc(x, R), c, 1, gap), R)
         assert got == pr.partial_eval(t, n, x, c, 1, gap)
+
+
+def test_c_prove_matmul_matches_python_oracle():
+    """The C restatement of prove_matmul (one layer) against the Python one: claims, every round
+    polynomial, and the failing-round report on a wrong claim."""
+    import random
+    from oracle import protocols as pr
+    R = bn254.R
+    rnd = random.Random(8)
+    for N, M, K in ((4, 8, 6), (3, 2, 11), (2, 2, 64)):
+        A = [rnd.randrange(-2**15, 2**15) for _ in range(N * K)]
+        B = [rnd.randrange(-2**15, 2**15) for _ in range(M * K)]
+        u = [rnd.randrange(R) for _ in range(pr.log2ceil(N * M) + 1)]
+        v = [rnd.randrange(R) for _ in range(pr.log2ceil(K))]
+        a_ = pr.partial_eval([x % R for x in A], N * K, u, N, pr.log2ceil(M), K)
+        b_ = pr.partial_eval([x % R for x in B], M * K, u, M, 0, K)
+        claim = sum(x * y for x, y in zip(a_, b_)) % R
+        want = pr.prove_matmul([x % R for x in A], [x % R for x in B], 1, N, M, K, u, v, claim)
+        enc = lambda xs: np.frombuffer(bn254.fr_vec_to_bytes(xs), dtype=np.uint32).reshape(-1, 8)
+        rc, a, b, final, tr = cport.prove_matmul_l1(np.array(A, dtype=np.int32), np.array(B, dtype=np.int32), N, M, K,
+                                                    enc(u), enc(v), enc([claim]))
+        assert rc == 0
+        assert bn254.fr_from_bytes(a.tobytes()) == want[0] and bn254.fr_from_bytes(b.tobytes()) == want[1]
+        assert bn254.fr_from_bytes(final.tobytes()) == want[2]
+        got_tr = [bn254.fr_vec_from_bytes(tr[i].tobytes()) for i in range(tr.shape[0])]
+        assert got_tr == [list(p) for p in want[3]]
+        rc_bad = cport.prove_matmul_l1(np.array(A, dtype=np.int32), np.array(B, dtype=np.int32), N, M, K, enc(u), enc(v),
+                                       enc([(claim + 1) % R]))[0]
+        assert rc_bad == 1   # the first round's check fails, where the reference throws
