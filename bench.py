@@ -665,6 +665,27 @@ def run_secondary(args):
                              "kernel_ms_per_proof": acc_ms, "traffic": None,
                              "note": f"{(254 + wbits - 1) // wbits} additions per query ({wbits}-bit signed windows over "
                                      "254-bit scalars); peak = the same addition looped on registers, measured in this run"}}
+        # host-core baseline and full-size parity: the C restatement of tLookupRange::prove on all host cores
+        # with the same queries, alpha, u and v; multiplicities, claims and round polynomials must equal the GPU's
+        if not args.no_cpu_baseline:
+            from oracle import cport
+            cport.build()
+            lD = (D - 1).bit_length()
+            ctx.seed(0xC33)
+            u_enc = ctx.random_fr(lD)              # what the prover will draw inside the next call
+            ctx.seed(0xC33)
+            ctx.fr_from_i32(dqi, D, dS)
+            g_claim, g_tr = lk.prove(dS, D, dAq, vv)
+            g_m = lk.table("m")
+            t0 = time.perf_counter()
+            rc, c_m, c_claim, c_final, c_tr = cport.lookup_range(q, -(1 << 15), Nt, host.encode_field([lk.alpha])[0],
+                                                                 u_enc, host.encode_field(vv))
+            cpu_s = time.perf_counter() - t0
+            same = (rc == 0 and [int(x) for x in c_m] == g_m and host.decode_field(c_claim.reshape(1, 8))[0] == g_claim
+                    and [host.decode_field(c_tr[i]) for i in range(c_tr.shape[0])] == g_tr)
+            line["cpu_baseline"] = {"value": cpu_s * 1e3, "unit": "ms", "cores": cport.threads(), "kind": "port",
+                                    "sample": "the full C3 lookup proof once, without the two commitments",
+                                    "matches_gpu_multiplicities_claim_and_transcript": bool(same)}
         if args.shrink == 1:
             ctx.sync()
             line["reference_cuda"] = reference_cuda_secondary(

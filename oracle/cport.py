@@ -120,5 +120,26 @@ def prove_matmul_l1(A: np.ndarray, B: np.ndarray, N: int, M: int, K: int, u: np.
     return rc, a, b, cl, tr[:rounds]
 
 
+def lookup_range(q: np.ndarray, low: int, n_table: int, alpha: np.ndarray, u: np.ndarray, v: np.ndarray):
+    """``tLookupRange::prove`` on a power-of-two number of int32 queries.  alpha, u, v: uint32[*, 8]
+    Montgomery records.  Returns (rc, multiplicities uint32[n_table], S~(v), final claim, transcript[rounds, 4, 8])."""
+    q = np.ascontiguousarray(q, dtype=np.int32).reshape(-1)
+    lD, lN = (q.size - 1).bit_length(), (n_table - 1).bit_length()
+    assert q.size == 1 << lD and n_table == 1 << lN and lN <= lD
+    alpha = np.ascontiguousarray(alpha, dtype=np.uint32).reshape(8)
+    u = np.ascontiguousarray(u, dtype=np.uint32).reshape(-1, 8)
+    v = np.ascontiguousarray(v, dtype=np.uint32).reshape(-1, 8)
+    assert u.shape[0] == lD and v.shape[0] == lD
+    m = np.zeros(n_table, dtype=np.uint32)
+    s_claim, final = np.zeros(8, dtype=np.uint32), np.zeros(8, dtype=np.uint32)
+    tr = np.zeros((max(lD, 1), 4, 8), dtype=np.uint32)
+    f = lib().oracle_lookup_range
+    f.restype = C.c_int
+    rc = f(C.c_void_p(q.ctypes.data), C.c_uint32(lD), C.c_int32(low), C.c_uint32(lN), C.c_void_p(alpha.ctypes.data),
+           C.c_void_p(u.ctypes.data), C.c_void_p(v.ctypes.data), C.c_void_p(m.ctypes.data), C.c_void_p(s_claim.ctypes.data),
+           C.c_void_p(final.ctypes.data), C.c_void_p(tr.ctypes.data))
+    return rc, m, s_claim, final, tr[:lD]
+
+
 if __name__ == "__main__":
     print(build(force=True))

@@ -541,6 +541,284 @@ int oracle_prove_matmul_l1(const int32_t* A, const int32_t* B, uint32_t N, uint3
 }
 
 /* ------------------------------------------------------------------------------------------ */
+/* tLookupRange::prove (src/tlookup.cu:288-343 with tLookup_phase1 / phase2, :192-244, and the     */
+/* step polynomials, :117-190) for a power-of-two number of int32 queries.                         */
+/* ------------------------------------------------------------------------------------------ */
+static void fr_set_u64(fe* r, uint64_t v) {
+  fe t;
+  memset(&t, 0, sizeof t);
+  t.w[0] = v;
+  fe_to_mont(&FR, r, &t);
+}
+static void fr_set_i64(fe* r, int64_t v) {
+  if (v >= 0) {
+    fr_set_u64(r, (uint64_t)v);
+  } else {
+    fe t;
+    fr_set_u64(&t, (uint64_t)(-v));
+    fe_neg(&FR, r, &t);
+  }
+}
+/* sum of n elements (parallel) */
+static void fr_sum(fe* out, const fe* x, uint64_t n) {
+  const int nt = oracle_threads();
+  fe* part = (fe*)calloc((size_t)nt, sizeof(fe));
+#pragma omp parallel num_threads(nt)
+  {
+    int tid = 0;
+#ifdef _OPENMP
+    tid = omp_get_thread_num();
+#endif
+    fe acc;
+    memset(&acc, 0, sizeof acc);
+#pragma omp for
+    for (int64_t i = 0; i < (int64_t)n; i++) fe_add(&FR, &acc, &acc, &x[i]);
+    part[tid] = acc;
+  }
+  memset(out, 0, sizeof *out);
+  for (int t = 0; t < nt; t++) fe_add(&FR, out, out, &part[t]);
+  free(part);
+}
+/* multilinear evaluation of t[0..2^nv) at u[0..nv), lowest variable first, destroying t
+ * (FrTensor::operator()(vector<Fr>), src/fr-tensor.cu:346-369) */
+static void mle_eval(fe* out, fe* t, uint32_t nv, const fe* u, fe* tmp) {
+  uint64_t n = (uint64_t)1 << nv;
+  fe* src = t;
+  fe* dst = tmp;   /* ping-pong: a pass never writes the buffer it reads (tmp holds 2^(nv-1) elements) */
+  for (uint32_t k = 0; k < nv; k++) {
+    const uint64_t h = n / 2;
+#pragma omp parallel for if (h > 4096)
+    for (int64_t j = 0; j < (int64_t)h; j++) {
+      fe d, m;
+      fe_sub(&FR, &d, &src[2 * j + 1], &src[2 * j]);
+      fe_mul(&FR, &m, &u[k], &d);
+      fe_add(&FR, &dst[j], &src[2 * j], &m);
+    }
+    fe* sw = src;
+    src = dst;
+    dst = sw;
+    n = h;
+  }
+  *out = src[0];
+}
+/* tLookup_poly_kernel (src/tlookup.cu:64-78) followed by the three evaluations at u_: p[k] = t_k~(u_) */
+static void poly_terms_eval(fe p[3], const fe* X, const fe* Y, const fe* shift, uint64_t h, uint32_t nv, const fe* u,
+                            fe* t0, fe* t1, fe* t2, fe* tmp) {
+#pragma omp parallel for if (h > 4096)
+  for (int64_t t = 0; t < (int64_t)h; t++) {
+    fe c01, c10, c11, a, b;
+    fe_sub(&FR, &c01, &X[t + h], &X[t]);
+    fe_add(&FR, &c10, &Y[t], shift);
+    fe_sub(&FR, &c11, &Y[t + h], &Y[t]);
+    fe_mul(&FR, &t0[t], &X[t], &c10);
+    fe_mul(&FR, &a, &c01, &c10);
+    fe_mul(&FR, &b, &X[t], &c11);
+    fe_add(&FR, &t1[t], &a, &b);
+    fe_mul(&FR, &t2[t], &c01, &c11);
+  }
+  if (u) {
+    mle_eval(&p[0], t0, nv, u, tmp);
+    mle_eval(&p[1], t1, nv, u, tmp);
+    mle_eval(&p[2], t2, nv, u, tmp);
+  } else {
+    fr_sum(&p[0], t0, h);
+    fr_sum(&p[1], t1, h);
+    fr_sum(&p[2], t2, h);
+  }
+}
+static void fold_msb(fe* X, uint64_t h, const fe* v) {
+#pragma omp parallel for if (h > 4096)
+  for (int64_t g = 0; g < (int64_t)h; g++) {
+    fe d, m;
+    fe_sub(&FR, &d, &X[g + h], &X[g]);
+    fe_mul(&FR, &m, v, &d);
+    fe_add(&FR, &X[g], &X[g], &m);
+  }
+}
+static void poly_eval4(fe* out, const fe p[4], const fe* x) {
+  fe acc = p[3];
+  for (int k = 2; k >= 0; k--) {
+    fe_mul(&FR, &acc, &acc, x);
+    fe_add(&FR, &acc, &acc, &p[k]);
+  }
+  *out = acc;
+}
+static void eq2_fr(fe* out, const fe* u, const fe* v, const fe* one) {  /* uv + (1-u)(1-v) */
+  fe uv, a, b;
+  fe_mul(&FR, &uv, u, v);
+  fe_sub(&FR, &a, one, u);
+  fe_sub(&FR, &b, one, v);
+  fe_mul(&FR, &a, &a, &b);
+  fe_add(&FR, out, &uv, &a);
+}
+
+/* q: D = 2^lD int32 queries in [low, low + N), N = 2^lN <= D.  alpha: the lookup's random scalar, u, v:
+ * lD challenges each (u is what the reference draws inside prove).  Outputs: multiplicities m_out[N],
+ * S~(v), the claim after the last round, four coefficients per round.  Returns 0, 1 + round index
+ * of a failed check, or -3 when a query lies outside the table. */
+int oracle_lookup_range(const int32_t* q, uint32_t lD, int32_t low, uint32_t lN, const fe* alpha_in, const fe* u_in,
+                        const fe* v, uint32_t* m_out, fe* s_claim, fe* final_claim, fe* transcript) {
+  const uint64_t D = (uint64_t)1 << lD, N = (uint64_t)1 << lN;
+  fe one, beta, alpha = *alpha_in, alpha_sq, C, ratio, two_inv, claim;
+  fr_set_u64(&one, 1);
+  fr_set_u64(&beta, N);
+  memset(m_out, 0, N * sizeof(uint32_t));
+  for (uint64_t i = 0; i < D; i++) {
+    int64_t k = (int64_t)q[i] - low;
+    if (k < 0 || (uint64_t)k >= N) return -3;
+    m_out[k]++;
+  }
+  fe* T = (fe*)malloc(N * sizeof(fe));
+  fe* B = (fe*)malloc(N * sizeof(fe));
+  fe* Mf = (fe*)malloc(N * sizeof(fe));
+  fe* S = (fe*)malloc(D * sizeof(fe));
+  fe* A = (fe*)malloc(D * sizeof(fe));
+  fe* t0 = (fe*)malloc(D / 2 * sizeof(fe));
+  fe* t1 = (fe*)malloc(D / 2 * sizeof(fe));
+  fe* t2 = (fe*)malloc(D / 2 * sizeof(fe));
+  fe* u = (fe*)malloc((lD + 1) * sizeof(fe));
+  fe* tmp = (fe*)malloc((D / 4 + 1) * sizeof(fe));
+  memcpy(u, u_in, lD * sizeof(fe));
+#pragma omp parallel for
+  for (int64_t t = 0; t < (int64_t)N; t++) {
+    fe s;
+    fr_set_i64(&T[t], (int64_t)low + t);
+    fe_add(&FR, &s, &T[t], &beta);
+    fe_inv(&FR, &B[t], &s);
+    fr_set_u64(&Mf[t], m_out[t]);
+  }
+  oracle_fr_from_i32(q, S, D);
+#pragma omp parallel for
+  for (int64_t i = 0; i < (int64_t)D; i++) A[i] = B[(int64_t)q[i] - low];   /* = 1 / (S_i + beta) */
+  /* C = alpha^2 - sum B m;  ratio = N / D;  claim = alpha + alpha^2 */
+  fe_mul(&FR, &alpha_sq, &alpha, &alpha);
+  {
+    fe acc, prod;
+    memset(&acc, 0, sizeof acc);
+    for (uint64_t t = 0; t < N; t++) {
+      fe_mul(&FR, &prod, &B[t], &Mf[t]);
+      fe_add(&FR, &acc, &acc, &prod);
+    }
+    fe_sub(&FR, &C, &alpha_sq, &acc);
+    fe dfe, dinv, nfe;
+    fr_set_u64(&dfe, D);
+    fr_set_u64(&nfe, N);
+    fe_inv(&FR, &dinv, &dfe);
+    fe_mul(&FR, &ratio, &nfe, &dinv);
+    fe two;
+    fr_set_u64(&two, 2);
+    fe_inv(&FR, &two_inv, &two);
+  }
+  fe_add(&FR, &claim, &alpha, &alpha_sq);
+  int rc = 0;
+  uint32_t nu = lD, round = 0;
+  uint64_t n = D;
+  /* phase 1: the variables beyond the table's, last challenge first */
+  for (uint32_t i = 0; i < lD - lN && rc == 0; i++, round++) {
+    const uint64_t h = n / 2;
+    const fe* ul = &u[nu - 1];
+    const fe* vb = &v[lD - 1 - i];
+    fe p0[3], p[4], e0, e1, sl, sh, half_c;
+    poly_terms_eval(p0, A, S, &beta, h, nu - 1, u, t0, t1, t2, tmp);
+    for (int k = 0; k < 3; k++) fe_mul(&FR, &p0[k], &p0[k], &alpha);
+    fe_sub(&FR, &e0, &one, ul);            /* eq(u)(t) = (1-u) + (2u-1) t */
+    fe_add(&FR, &e1, ul, ul);
+    fe_sub(&FR, &e1, &e1, &one);
+    fe a, b;
+    fe_mul(&FR, &p[0], &p0[0], &e0);
+    fe_mul(&FR, &a, &p0[1], &e0);
+    fe_mul(&FR, &b, &p0[0], &e1);
+    fe_add(&FR, &p[1], &a, &b);
+    fe_mul(&FR, &a, &p0[2], &e0);
+    fe_mul(&FR, &b, &p0[1], &e1);
+    fe_add(&FR, &p[2], &a, &b);
+    fe_mul(&FR, &p[3], &p0[2], &e1);
+    fr_sum(&sl, A, h);
+    fr_sum(&sh, A + h, h);
+    fe_add(&FR, &p[0], &p[0], &sl);
+    fe_sub(&FR, &sh, &sh, &sl);
+    fe_add(&FR, &p[1], &p[1], &sh);
+    fe_mul(&FR, &half_c, &C, &two_inv);
+    fe_add(&FR, &p[0], &p[0], &half_c);
+    for (int k = 0; k < 4; k++) transcript[4 * round + k] = p[k];
+    fe s01 = p[0];
+    for (int k = 0; k < 4; k++) fe_add(&FR, &s01, &s01, &p[k]);
+    if (!fe_eq(&s01, &claim)) { rc = 1 + (int)round; break; }
+    fold_msb(A, h, vb);
+    fold_msb(S, h, vb);
+    poly_eval4(&claim, p, vb);
+    fe e;
+    eq2_fr(&e, ul, vb, &one);
+    fe_mul(&FR, &alpha, &alpha, &e);
+    C = half_c;
+    nu--;
+    n = h;
+  }
+  /* phase 2: the table's variables */
+  uint64_t nt = N;
+  for (uint32_t i = 0; i < lN && rc == 0; i++, round++) {
+    const uint64_t h = nt / 2;
+    const fe* ul = &u[nu - 1];
+    const fe* vb = &v[lN - 1 - i];
+    fe pa[3], pb[3], pm[3], p0[3], p[4], e0, e1, coef, sl, sh, zero, nratio;
+    memset(&zero, 0, sizeof zero);
+    poly_terms_eval(pa, A, S, &beta, h, nu - 1, u, t0, t1, t2, tmp);
+    poly_terms_eval(pb, B, T, &beta, h, nu - 1, u, t0, t1, t2, tmp);
+    poly_terms_eval(pm, Mf, B, &zero, h, 0, NULL, t0, t1, t2, tmp);
+    fe_mul(&FR, &coef, &ratio, &alpha_sq);
+    for (int k = 0; k < 3; k++) {
+      fe x, y;
+      fe_mul(&FR, &x, &pa[k], &alpha);
+      fe_mul(&FR, &y, &pb[k], &coef);
+      fe_add(&FR, &p0[k], &x, &y);
+    }
+    fe_sub(&FR, &e0, &one, ul);
+    fe_add(&FR, &e1, ul, ul);
+    fe_sub(&FR, &e1, &e1, &one);
+    fe a, b;
+    fe_mul(&FR, &p[0], &p0[0], &e0);
+    fe_mul(&FR, &a, &p0[1], &e0);
+    fe_mul(&FR, &b, &p0[0], &e1);
+    fe_add(&FR, &p[1], &a, &b);
+    fe_mul(&FR, &a, &p0[2], &e0);
+    fe_mul(&FR, &b, &p0[1], &e1);
+    fe_add(&FR, &p[2], &a, &b);
+    fe_mul(&FR, &p[3], &p0[2], &e1);
+    fr_sum(&sl, A, h);
+    fr_sum(&sh, A + h, h);
+    fe_add(&FR, &p[0], &p[0], &sl);
+    fe_sub(&FR, &sh, &sh, &sl);
+    fe_add(&FR, &p[1], &p[1], &sh);
+    fe_neg(&FR, &nratio, &ratio);
+    for (int k = 0; k < 3; k++) {
+      fe x;
+      fe_mul(&FR, &x, &pm[k], &nratio);
+      fe_add(&FR, &p[k], &p[k], &x);
+    }
+    for (int k = 0; k < 4; k++) transcript[4 * round + k] = p[k];
+    fe s01 = p[0];
+    for (int k = 0; k < 4; k++) fe_add(&FR, &s01, &s01, &p[k]);
+    if (!fe_eq(&s01, &claim)) { rc = 1 + (int)round; break; }
+    fold_msb(A, h, vb);
+    fold_msb(S, h, vb);
+    fold_msb(B, h, vb);
+    fold_msb(T, h, vb);
+    fold_msb(Mf, h, vb);
+    poly_eval4(&claim, p, vb);
+    fe e;
+    eq2_fr(&e, ul, vb, &one);
+    fe_mul(&FR, &alpha, &alpha, &e);
+    fe_mul(&FR, &alpha_sq, &alpha_sq, &e);
+    nu--;
+    nt = h;
+  }
+  *s_claim = S[0];
+  *final_claim = claim;
+  free(T); free(B); free(Mf); free(S); free(A); free(t0); free(t1); free(t2); free(u); free(tmp);
+  return rc;
+}
+
+/* ------------------------------------------------------------------------------------------ */
 /* Host scalar / group operations and the seeded random stream, exported for the libff stand-in */
 /* that lets the reference's own sources compile (oracle/ref_shim).                              */
 /* ------------------------------------------------------------------------------------------ */

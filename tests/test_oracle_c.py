@@ -93,3 +93,29 @@ def test_c_prove_matmul_matches_python_oracle():
         rc_bad = cport.prove_matmul_l1(np.array(A, dtype=np.int32), np.array(B, dtype=np.int32), N, M, K, enc(u), enc(v),
                                        enc([(claim + 1) % R]))[0]
         assert rc_bad == 1   # the first round's check fails, where the reference throws
+
+
+def test_c_lookup_range_matches_python_oracle():
+    """The C restatement of tLookupRange::prove against the Python one: multiplicities, S~(v), the
+    final claim and every round polynomial; a query outside the table is reported."""
+    import random
+    from oracle import protocols as pr
+    R = bn254.R
+    rnd = random.Random(12)
+    enc = lambda xs: np.frombuffer(bn254.fr_vec_to_bytes(xs), dtype=np.uint32).reshape(-1, 8)
+    for low, N, D in ((-8, 16, 64), (0, 4, 4), (-128, 256, 1024)):
+        q = [rnd.randrange(low, low + N) for _ in range(D)]
+        alpha = rnd.randrange(R)
+        lD = pr.log2ceil(D)
+        u = [rnd.randrange(R) for _ in range(lD)]
+        v = [rnd.randrange(R) for _ in range(lD)]
+        want = pr.LookupRange(low, N, alpha).prove([x % R for x in q], v, u)
+        rc, m, s_claim, final, tr = cport.lookup_range(np.array(q, dtype=np.int32), low, N, enc([alpha])[0], enc(u), enc(v))
+        assert rc == 0
+        assert [int(x) for x in m] == want["m"]
+        assert bn254.fr_from_bytes(s_claim.tobytes()) == want["claim"]
+        assert bn254.fr_from_bytes(final.tobytes()) == want["final"]
+        got = [bn254.fr_vec_from_bytes(tr[i].tobytes()) for i in range(tr.shape[0])]
+        assert got == [list(p) + [0] * (4 - len(p)) for p in want["transcript"]]
+    q = np.array([0, 1, 2, 99], dtype=np.int32)
+    assert cport.lookup_range(q, 0, 4, enc([5])[0], enc([1, 2]), enc([3, 4]))[0] == -3
