@@ -278,3 +278,27 @@ def test_bucket_commitment_equals_direct_commitment(gctx, n_table, rows_in, inne
         wantA = cport.commit_fr(host.encode_field(want["A"]), wd, ctable)
         assert results[1][2] == wantA.tobytes()
     table.close()
+
+
+def test_lookup_mid_size_equals_c_oracle(gctx):
+    """2^18 queries into a 2^12-entry table: multiplicities, claim and every round polynomial against
+    the C restatement of tLookupRange::prove."""
+    from grape_b200 import host
+    D, N, low = 1 << 18, 1 << 12, -(1 << 11)
+    rng = np.random.default_rng(18)
+    q = rng.integers(low, low + N, size=D).astype(np.int32)
+    gctx.seed(40)
+    lk = host.Lookup(gctx, low, N)
+    v = host.decode_field(gctx.random_fr(18))
+    gctx.seed(41)
+    u_enc = gctx.random_fr(18)     # what the prover draws inside the call below
+    gctx.seed(41)
+    dS = gctx.alloc(D * 32)
+    gctx.fr_from_i32(gctx.upload(q), D, dS)
+    claim, tr = lk.prove(dS, D, gctx.alloc(D * 32), v)
+    rc, m, s_claim, final, ctr = cport.lookup_range(q, low, N, host.encode_field([lk.alpha])[0], u_enc, host.encode_field(v))
+    assert rc == 0
+    assert [int(x) for x in m] == lk.table("m")
+    assert host.decode_field(s_claim.reshape(1, 8))[0] == claim
+    assert [host.decode_field(ctr[i]) for i in range(ctr.shape[0])] == tr
+    lk.close()

@@ -143,3 +143,39 @@ def test_sharded_prove_matmul_equals_unsharded(gctx, L, N, M, K, P):
     with pytest.raises(g.GrapeError) as e:
         host.prove_matmul_finish(gctx, gathered, P, L, N, M, K, u, v, (claim + 1) % R)
     assert e.value.code == 3
+
+
+def test_prove_matmul_mid_size_equals_c_oracle(gctx):
+    """256 x 2048 . 512 x 2048 (1.5 M elements): the GPU proof from Fr tensors and from int32 tensors
+    against the C restatement -- claims and every round polynomial."""
+    import numpy as np
+    from grape_b200 import host
+    from oracle import cport
+    rng = np.random.default_rng(5)
+    N, M, K = 256, 512, 2048
+    A = rng.integers(-2**15, 2**15, size=N * K).astype(np.int32)
+    B = rng.integers(-2**15, 2**15, size=M * K).astype(np.int32)
+    gctx.seed(15)
+    u = host.decode_field(gctx.random_fr(pr.log2ceil(N * M)))
+    v = host.decode_field(gctx.random_fr(pr.log2ceil(K)))
+    dAi, dBi = gctx.upload(A), gctx.upload(B)
+    dA, dB = gctx.alloc(N * K * 32), gctx.alloc(M * K * 32)
+    gctx.fr_from_i32(dAi, N * K, dA)
+    gctx.fr_from_i32(dBi, M * K, dB)
+    # the claim: <fold(A), fold(B)>, by the library's own fold and sum
+    du = gctx.fr_upload(u)
+    a_, b_, one = gctx.alloc(K * 32), gctx.alloc(K * 32), gctx.alloc(32)
+    gctx.fr_fold(dA, N * K, du.at(pr.log2ceil(M) * 32), N, K, a_)
+    gctx.fr_fold(dB, M * K, du, M, K, b_)
+    gctx.fr_binary("mul", a_, b_, a_, K)
+    gctx.fr_sum(a_, K, one)
+    claim = gctx.fr_download(one, 1)[0]
+    got_i = host.prove_matmul_i32(gctx, dAi, dBi, 1, N, M, K, u, v, claim)
+    got = host.prove_matmul(gctx, dA, dB, 1, N, M, K, u, v, claim)
+    assert got == got_i
+    rc, ca, cb, cfinal, ctr = cport.prove_matmul_l1(A, B, N, M, K, host.encode_field(u), host.encode_field(v),
+                                                    host.encode_field([claim]))
+    assert rc == 0
+    dec = lambda x: host.decode_field(x.reshape(-1, 8))
+    assert (dec(ca)[0], dec(cb)[0], dec(cfinal)[0]) == got[:3]
+    assert [dec(ctr[i]) for i in range(ctr.shape[0])] == [p[:3] for p in got[3]]
