@@ -203,8 +203,8 @@ def run_reference(args):
     ref = reference_cuda(workload_config()["rows_per_step"], max(args.steps, 1))
     if ref and "points_per_s" in ref and ref.get("cuda_status") == "no error":
         cfg = workload_config()
-        line = {"impl": "reference", "metric": METRIC, "value": ref["points_per_s"], "unit": UNIT, "n_gpus": 1,
-                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ref["ms_per_step"],
+        line = {"impl": "reference", "metric": METRIC, "value": ref["points_per_s"], "unit": UNIT, "n_gpus": args.gpus,
+                "gpus_used": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ref["ms_per_step"],
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "u32 limbs (254-bit fields)", "data": "synthetic", "config": cfg,
                 "cpu_baseline": {"value": ref["points_per_s"], "unit": UNIT, "cores": 1, "kind": "reference",
@@ -213,7 +213,8 @@ def run_reference(args):
                 "e2e": {"value": ref["e2e_points_per_s"], "unit": UNIT, "h2d_bytes_per_step": 0,
                         "d2h_bytes_per_step": 0, "ms_per_step": ref["e2e_ms_per_step"],
                         "note": "the reference's own data movement (cudaMemcpy from pageable memory) is inside"},
-                "gpu_launches": 0, "reference_build": ref["what"]}
+                "gpu_launches": 0, "reference_build": ref["what"],
+                "multi_gpu_note": "the reference has no multi-GPU path: at any N its kernels run on one GPU"}
         print(json.dumps(line))
         return
     from oracle import bn254, cport
@@ -453,7 +454,7 @@ def run_own(args):
         line["reference_cuda"] = ref_cuda
     if args.proof_layers:
         line["layer_proof"] = layer_proof(ctx, args.proof_layers, args.proof_window_bits, args.proof_scope)
-    if not args.no_cpu_baseline and wd == WD:
+    if not args.no_cpu_baseline and wd == WD and world == 1:   # host-core baseline: N = 1 only
         base, rows_used, rec = cpu_baseline(gens, np.asarray(h_scalars), args.cpu_seconds)
         base["matches_gpu_rows"] = bool(np.array_equal(rec, dev_records[:rows_used]))
         line["cpu_baseline"] = base
