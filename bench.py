@@ -1,16 +1,19 @@
 #!/usr/bin/env python
-"""Benchmark of the Hyrax commitment hot path: MSM points/s on one LLaMA-2-7B-shaped layer.
+"""Benchmark of the Hyrax commitment hot path: MSM points/s on one LLaMA-2-7B-shaped layer, and the
+proof time per layer of the same model shape.
 
     python bench.py --gpus N --steps K --warmup W [--impl reference]
 
 One step commits the seven weight matrices of one decoder layer (4 x 4096x4096, 2 x 11008x4096,
 1 x 4096x11008, int16-range entries held as int32, flattened into rows of 4096 scalars over 4096
-generators): 49 408 row commitments, 202 375 168 (scalar, generator) pairs.  With N > 1 every rank
-commits its own layer (weak scaling, no data-path collective; the 32 layers of the model are
-independent).  Rank 0 prints one JSON line.
+generators): 49 408 row commitments, 202 375 168 (scalar, generator) pairs.  With N > 1 the rows of
+that ONE layer are dealt to the ranks in contiguous blocks, every rank commits its block and one NCCL
+all-gather hands every rank all the commitments (strong scaling; the time includes the gather).  The
+line also carries `layer_proof`: every rank proves its own batch of four decoder layers (seq 2048), the
+second half of the headline metric.  Rank 0 prints one JSON line.
 
---impl reference times the host-core restatement of the reference's algorithm (oracle/) on a bounded
-row sample of the same workload, on all host cores.
+--impl reference times the reference's own commit kernels (its unmodified sources built into
+oracle/_ref) on the same workload; it never loads this repository's library.
 """
 from __future__ import annotations
 
@@ -31,11 +34,14 @@ sys.path.insert(0, str(ROOT))
 
 WD = 4096                      # scalars (= generators) per commitment row
 SEED = 0xC4
-MUL_INSTR_PER_FIELD_MUL = 264  # 8-limb Montgomery product in 32-bit lo/hi multiply instructions
-FIELD_MUL_PER_ADD = 10         # mixed XYZZ += affine addition
+LAYER_PAIRS = 4 * 4096 * 4096 + 3 * 4096 * 11008   # elements of the seven weight matrices of one layer
+MUL_INSTR_PER_FIELD_MUL = 264  # 8-limb Montgomery product: 128 lo/hi multiply-add pairs + 8 single multiplies
+MUL_INSTR_PER_FIELD_SQR = 208  # dedicated squaring: 100 pairs + 8
+FIELD_MUL_PER_ADD = 10         # mixed XYZZ += affine addition: 8 products + 2 squarings
 ADDS_PER_PAIR_INT16 = 2        # byte windows of a 16-bit magnitude (the reference's cost model)
 ALGO_MUL_INSTR_PER_PAIR = MUL_INSTR_PER_FIELD_MUL * FIELD_MUL_PER_ADD * ADDS_PER_PAIR_INT16  # 5280
-NCU_DRAM_BYTES_PER_PAIR = 69.8  # profiles/commit_accumulate_c4_int16_w16.md
+EXEC_MUL_INSTR_PER_ADD = 8 * MUL_INSTR_PER_FIELD_MUL + 2 * MUL_INSTR_PER_FIELD_SQR              # 2528
+NCU_DRAM_BYTES_PER_PAIR = 69.8  # measured with ncu on a reduced case: 585 MB read+write for 8.4 M pairs
 METRIC = "hyrax_msm_points_per_s"
 UNIT = "points/s"
 
@@ -49,8 +55,8 @@ def parse_args():
     ap.add_argument("--window-bits", type=int, default=16, choices=[8, 16])
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target length of the CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--proof-layers", type=int, default=0,
-                    help="also time the proof of this many decoder layers (one batch, seq 2048)")
+    ap.add_argument("--proof-layers", type=int, default=4,
+                    help="layers per batch of the proof timing carried in `layer_proof` (seq 2048); 0 = skip it")
     ap.add_argument("--proof-window-bits", type=int, default=13)
     ap.add_argument("--proof-scope", default="layer", choices=["layer", "ffn"])
     ap.add_argument("--workload", default="commit", choices=["commit", "matmul", "lookup", "commit-bls12-381", "matmul-sharded", "layer-proof", "fold"],
@@ -61,15 +67,23 @@ def parse_args():
     return ap.parse_args()
 
 
-def workload_config(window_bits=None):
-    from grape_b200 import workloads as wl
-    n = wl.layer_weight_elements()
-    cfg = {"workload": "C4: Hyrax commit of one LLaMA-2-7B-shaped layer (4x4096x4096 + 3x4096x11008 int16-range "
-                       "weights, 4096 generators)", "pairs_per_step": n, "rows_per_step": n // WD, "row_len": WD,
-           "curve": "BN254 G1 (the curve the reference compiles)", "l2_policy": "inputs (809 MB) exceed L2"}
-    if window_bits is not None:
-        cfg["window_bits"] = window_bits
-    return cfg
+def workload_config():
+    """The same dictionary in both arms (the window width of this library's table is a top-level key)."""
+    return {"workload": "C4: Hyrax commit of one LLaMA-2-7B-shaped layer (4x4096x4096 + 3x4096x11008 int16-range "
+                        "weights, 4096 generators)", "pairs_per_step": LAYER_PAIRS, "rows_per_step": LAYER_PAIRS // WD,
+            "row_len": WD, "curve": "BN254 G1 (the curve the reference compiles)",
+            "l2_policy": "inputs (809 MB) exceed L2"}
+
+
+def quantised_normal_np(rng, n, std=0.02, scale=1 << 16, lo=-(1 << 15), hi=(1 << 15) - 1):
+    """clip(round(N(0, std) * scale), lo, hi) as int32 (numpy only: the reference arm imports nothing of the package)."""
+    out = np.empty(n, dtype=np.int32)
+    step = 1 << 24
+    for a in range(0, n, step):
+        b = min(n, a + step)
+        x = rng.standard_normal(b - a, dtype=np.float32) * np.float32(std * scale)
+        out[a:b] = np.clip(np.rint(x), lo, hi).astype(np.int32)
+    return out
 
 
 class ClockSampler:
@@ -155,57 +169,52 @@ def cpu_baseline(gens: np.ndarray, scalars: np.ndarray, target_seconds: float, c
 REF_HARNESS = ROOT / "oracle" / "_ref" / "ref_harness"
 
 
-def reference_cuda(rows: int, steps: int):
+def _run_harness(argv, timeout):
+    if not REF_HARNESS.exists():
+        return None
+    env = dict(os.environ, OMP_NUM_THREADS="1")
+    try:
+        res = subprocess.run([str(REF_HARNESS), *map(str, argv)], capture_output=True, text=True, env=env, timeout=timeout)
+    except (OSError, subprocess.TimeoutExpired) as e:
+        return {"unavailable": str(e)}
+    for ln in reversed(res.stdout.strip().splitlines()):
+        if ln.startswith("{"):
+            return json.loads(ln)
+    return {"unavailable": (res.stderr or res.stdout)[-300:]}
+
+
+def reference_cuda(rows: int, steps: int, warmup: int = 1):
     """The reference's own commit kernels (its unmodified src/*.cu built into oracle/_ref by
     `make -C oracle ref`), timed on this GPU by oracle/ref_harness.cu.  None when that build is absent."""
-    if not REF_HARNESS.exists():
-        return None
-    env = dict(os.environ, OMP_NUM_THREADS="1")
-    try:
-        res = subprocess.run([str(REF_HARNESS), "commit-bench", str(rows), str(steps)], capture_output=True,
-                             text=True, env=env, timeout=600)
-    except (OSError, subprocess.TimeoutExpired) as e:
-        return {"unavailable": str(e)}
-    for ln in reversed(res.stdout.strip().splitlines()):
-        if ln.startswith("{"):
-            d = json.loads(ln)
-            d["what"] = ("reference CUDA (fixed-base 8-bit windows, one warp per row), unmodified sources, "
-                         "libff replaced by a stand-in; same rows x 4096 int16-range workload")
-            return d
-    return {"unavailable": (res.stderr or res.stdout)[-300:]}
+    d = _run_harness(["commit-bench", rows, steps, warmup], 900)
+    if d is not None and "unavailable" not in d:
+        d["what"] = ("reference CUDA (fixed-base 8-bit windows, one warp per row), unmodified sources, "
+                     "libff replaced by a stand-in; same rows x 4096 int16-range workload")
+    return d
 
 
-def reference_cuda_secondary(mode: str, a: int, steps: int, what: str):
+def reference_cuda_secondary(mode: str, a: int, steps: int, what: str, extra=()):
     """`ref_harness matmul-bench|lookup-bench`: the reference's own prove_matmul / tLookupRange::prove on
     this GPU at the same sizes.  None when that build is absent."""
-    if not REF_HARNESS.exists():
-        return None
-    env = dict(os.environ, OMP_NUM_THREADS="1")
-    try:
-        res = subprocess.run([str(REF_HARNESS), mode, str(a), str(steps)], capture_output=True, text=True, env=env,
-                             timeout=900)
-    except (OSError, subprocess.TimeoutExpired) as e:
-        return {"unavailable": str(e)}
-    for ln in reversed(res.stdout.strip().splitlines()):
-        if ln.startswith("{"):
-            d = json.loads(ln)
-            d["what"] = what
-            return d
-    return {"unavailable": (res.stderr or res.stdout)[-300:]}
+    d = _run_harness([mode, a, steps, *extra], 900)
+    if d is not None and "unavailable" not in d:
+        d["what"] = what
+    return d
 
 
 def run_reference(args):
-    """The reference's algorithm on the host cores (C restatement; the reference's own code for this
-    path is CUDA and needs libsnark, which is not vendored, so it cannot be built)."""
+    """The reference arm: the reference's own CUDA commit kernels on GPU 0 (the reference has no CPU
+    implementation of this path); the C restatement on the host cores only when that build is absent.
+    Nothing of the grape_b200 package is imported here."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    ref = reference_cuda(workload_config()["rows_per_step"], max(args.steps, 1))
+    cfg = workload_config()
+    ref = reference_cuda(cfg["rows_per_step"], max(args.steps, 1), max(args.warmup, 1))
     if ref and "points_per_s" in ref and ref.get("cuda_status") == "no error":
-        cfg = workload_config()
         line = {"impl": "reference", "metric": METRIC, "value": ref["points_per_s"], "unit": UNIT, "n_gpus": args.gpus,
-                "gpus_used": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ref["ms_per_step"],
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "gpus_used": 1, "steps": args.steps, "warmup": ref.get("warmup", 1), "ms_per_step": ref["ms_per_step"],
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "u32 limbs (254-bit fields)", "data": "synthetic", "config": cfg,
                 "cpu_baseline": {"value": ref["points_per_s"], "unit": UNIT, "cores": 1, "kind": "reference",
                                  "sample": "whole layer (49 408 rows); the reference's implementation of this path is "
@@ -217,12 +226,11 @@ def run_reference(args):
                 "multi_gpu_note": "the reference has no multi-GPU path: at any N its kernels run on one GPU"}
         print(json.dumps(line))
         return
-    from oracle import bn254, cport
-    from grape_b200 import workloads as wl  # shapes only; the arithmetic below is the oracle's
+    from oracle import bn254, cport   # the one other place bench.py may execute oracle/
     cport.build()
     rng = np.random.default_rng(SEED)
     rows_avail = 4096
-    scalars = wl.quantised_normal(rng, rows_avail * WD)
+    scalars = quantised_normal_np(rng, rows_avail * WD)
     # generators [rho_i](1,2): computed with the oracle's own table code from one base point
     base = np.frombuffer(bn254.jacobian_to_bytes(bn254.G1_GEN), dtype=np.uint32).reshape(1, 24)
     base_table = cport.table_build(base)
@@ -244,10 +252,9 @@ def run_reference(args):
         cport.commit_i32(scalars, WD, table, 0, rows)
     dt = time.perf_counter() - t
     value = rows * WD * args.steps / dt
-    cfg = workload_config()
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u32 limbs (254-bit fields)",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "u32 limbs (254-bit fields)",
             "data": "synthetic", "config": cfg,
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
                              "sample": f"each step = first {rows} rows ({rows * WD} pairs) of the layer"},
@@ -256,13 +263,15 @@ def run_reference(args):
     print(json.dumps(line))
 
 
-def layer_proof(ctx, layers: int, window_bits: int, scope: str, seed: int = 0xC5):
+def layer_proof(ctx, layers: int, window_bits: int, scope: str, seed: int = 0xC5, pieces: bool = False):
     """Proof of `layers` LLaMA-2-7B-shaped decoder layers in one batch (seq 2048, dim 4096, ffn 11008) in
     the call order of the reference's end-to-end driver test/llm.cu:73-611.  scope "layer": everything
     (11 matmul sumchecks, 3 Hadamard sumchecks, 14 range and 2 mapping lookups, 3 claim batchings and the
-    openings); scope "ffn": the feed-forward half only (test/llm.cu:73-239)."""
+    openings); scope "ffn": the feed-forward half only (test/llm.cu:73-239).  The timed region is what the
+    reference's own timer brackets (test/llm.cu:69-75, 613-614: total_prove_time over the batch)."""
     import grape_b200 as g
-    from grape_b200 import layer, layer_full, workloads as wl
+    from grape_b200 import host, layer, layer_full, workloads as wl
+    t_syn = time.perf_counter()
     if scope == "ffn":
         shape = layer.FFNShape(layer_num=layers, tokens=2048, dim=4096, ffn=11008)
         t = layer.synthesize_ffn(shape, seed=seed, x_range=1 << 13, matmul=wl.exact_matmul_cuda)
@@ -275,6 +284,7 @@ def layer_proof(ctx, layers: int, window_bits: int, scope: str, seed: int = 0xC5
             p = ctx.pinned_array(v.shape, v.dtype)
             p[...] = v
             t[k] = p
+    synth_s = time.perf_counter() - t_syn
     gens = wl.make_generators(ctx, shape.ffn_pad * 16, 0xC5)
     t0 = time.perf_counter()
     table = g.GeneratorTable(ctx, gens, window_bits, 1)
@@ -297,24 +307,39 @@ def layer_proof(ctx, layers: int, window_bits: int, scope: str, seed: int = 0xC5
     prover.timing = True
     trace = run(t)
     out = {"scope": scope, "layers": layers, "seconds": dt, "seconds_per_layer": dt / layers,
-           "by_step_with_syncs": trace.seconds, "window_bits": window_bits, "table_gib": table.nbytes / 2**30,
-           "table_build_s": table_s, "opens": trace.opens, "lookups": trace.lookups,
+           "by_step_with_syncs": trace.seconds,
+           "lookup_ms_in_walk_order": [round(dt * 1e3, 1) for kind, dt in trace.steps if kind == "lookup"],
+           "window_bits": window_bits, "table_gib": table.nbytes / 2**30,
+           "table_build_s": table_s, "synthesis_s": synth_s, "opens": trace.opens, "lookups": trace.lookups,
            "matmul_sumchecks": trace.matmuls,
            "upload_s": getattr(prover, "upload_seconds", None),
            "note": "host int32 tensors (page-locked) are uploaded inside the timed region, as the reference's driver loads them"}
     prover.release_pool()
+    if pieces:
+        # one piece of the walk alone, at the shape the reference build is timed on beside it: the range
+        # lookup of a 4 x 2048 x 4096 remainder tensor (2^25 queries, 2^16 table, rows of 65 536 generators)
+        D = 1 << 25
+        rng = np.random.default_rng(7)
+        q = rng.integers(-(1 << 15), 1 << 15, size=D).astype(np.int32)
+        dq, dS, dA = ctx.upload(q), ctx.alloc(D * 32), ctx.alloc(D * 32)
+        lk = host.Lookup(ctx, -(1 << 15), 1 << 16)
+        vv = host.decode_field(ctx.random_fr(25))
+        ms = []
+        for it in range(3):
+            ctx.fr_from_i32(dq, D, dS)
+            ctx.timer_begin()
+            lk.prove(dS, D, dA, vv, table=table, msm_size=4096)
+            ms.append(ctx.timer_end())
+        out["piece_range_lookup_2p25_ms"] = float(np.mean(ms[1:]))
+        for b in (dq, dS, dA):
+            b.free()
     table.close()
     return out
 
 
-def layer_weight_rows() -> int:
-    from grape_b200 import workloads as wl
-    return wl.layer_weight_elements() // WD
-
-
 def run_own(args):
     import grape_b200 as g
-    from grape_b200 import workloads as wl
+    from grape_b200 import parallel, workloads as wl
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -325,35 +350,60 @@ def run_own(args):
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    headline = args.gens == WD and not args.rows
     # The reference's own kernels are timed first, while this process holds nothing on the GPU
-    # (timed after this library's runs, with its context and 8 GiB table alive, the other process
+    # (timed after this library's runs, with its context and tables alive, the other process
     # measured up to three times slower).
-    ref_cuda = None
-    if world == 1 and args.gens == WD and not args.rows:
-        ref_cuda = reference_cuda(layer_weight_rows(), 2)
+    ref_cuda = ref_pieces = None
+    if world == 1 and headline:
+        ref_cuda = reference_cuda(LAYER_PAIRS // WD, 2, 1)
+        if args.proof_layers:
+            ref_pieces = {
+                "range_lookup_2p25": reference_cuda_secondary(
+                    "lookup-bench", 25, 1, "reference CUDA tLookupRange::prove: 2^25 queries (a 4 x 2048 x 4096 remainder "
+                    "tensor), 2^16 table, commitments over rows of 65 536 generators; host wall clock around the call",
+                    extra=(65536,)),
+                "matmul_c2": reference_cuda_secondary(
+                    "matmul-bench", 1, 2, "reference CUDA prove_matmul, A 2048x4096 . B 4096x4096, Fr tensors resident")}
     ctx = g.Context(local_rank)
 
     wd = args.gens
-    n = wl.layer_weight_elements() if not args.rows else args.rows * wd
+    n = LAYER_PAIRS if not args.rows else args.rows * wd
     rows = n // wd
+    if rows % world:
+        raise SystemExit(f"{rows} rows do not divide over {world} ranks")
     gens = wl.make_generators(ctx, wd, SEED)                  # same generators on every rank
     bits = 16
     n_windows = 1 if args.window_bits == 16 else 2
+    adds_per_pair = 1 if args.window_bits == 16 else 2
     table = g.GeneratorTable(ctx, gens, args.window_bits, n_windows)
     ctx.sync()
 
-    rng = np.random.default_rng(SEED + 1000 * rank)           # every rank commits its own layer
+    # the layer is the same on every rank; rank r owns the contiguous row block [r0, r1)
+    rng = np.random.default_rng(SEED)
     h_scalars = ctx.pinned_array((n,), np.int32)
     wl.quantised_normal(rng, n, out=h_scalars)
+    r0, r1 = parallel.row_block(rows, rank, world)
+    block = r1 - r0
     h_out = ctx.pinned_array((rows, 24), np.uint32)
-    d_scalars = ctx.upload(h_scalars)
-    d_out = ctx.alloc(rows * 96)
+    d_scalars = ctx.upload(h_scalars)                         # whole layer resident (the block is a slice of it)
+    d_out = ctx.alloc(rows * 96)                              # all commitments, rank order = row order
+    d_local = ctx.alloc(block * 96) if world > 1 else d_out
+    d_stage = ctx.alloc(block * wd * 4) if world > 1 else None
+    lib = ctx.lib
 
     def step_device():
-        g.commit_i32(ctx, table, d_scalars, n, wd, d_out, max_bits=bits)
+        parallel.commit_rows_sharded_device(ctx, table, d_scalars.at(r0 * wd * 4), block, wd, d_local, d_out, dist,
+                                            max_bits=bits)
 
     def step_host():
-        g.commit_i32_host(ctx, table, h_scalars, wd, max_bits=bits, out=h_out)
+        if world == 1:
+            g.commit_i32_host(ctx, table, h_scalars, wd, max_bits=bits, out=h_out)
+            return
+        # this rank's block from page-locked host memory, all commitments back to every rank's host
+        ctx._check(lib.grape_h2d(ctx.handle, d_stage.ptr, h_scalars[r0 * wd:r1 * wd].ctypes.data, block * wd * 4))
+        parallel.commit_rows_sharded_device(ctx, table, d_stage, block, wd, d_local, d_out, dist, max_bits=bits)
+        ctx._check(lib.grape_d2h(ctx.handle, h_out.ctypes.data, d_out.ptr, rows * 96))
 
     def barrier():
         ctx.sync()
@@ -390,7 +440,8 @@ def run_own(args):
     clocks = sampler.stop() if rank == 0 else None
     ms = max_over_ranks(ms)
     status = ctx.status()
-    value = world * n * args.steps / (ms * 1e-3)
+    value = n * args.steps / (ms * 1e-3)        # the ONE layer's pairs over the slowest rank's time, gather included
+    dev_records = ctx.download(d_out, rows * 96).reshape(rows, 24)
 
     # ---- end to end through host buffers -----------------------------------------------------
     for _ in range(max(1, min(args.warmup, 2))):
@@ -401,60 +452,114 @@ def run_own(args):
         step_host()
     e2e_ms = max_over_ranks(ctx.timer_end())
     barrier()
-    e2e_value = world * n * args.steps / (e2e_ms * 1e-3)
-    dev_records = ctx.download(d_out, rows * 96).reshape(rows, 24)
+    e2e_value = n * args.steps / (e2e_ms * 1e-3)
     host_path_matches = bool(np.array_equal(dev_records, h_out))
+
+    # ---- N > 1: every rank commits the whole layer alone (the check of the sharded result, and the
+    # weak-scaling figure: N layers on N GPUs, no collective) --------------------------------------
+    multi = None
+    if world > 1:
+        d_full = ctx.alloc(rows * 96)
+        g.commit_i32(ctx, table, d_scalars, n, wd, d_full, max_bits=bits)
+        barrier()
+        ctx.timer_begin()
+        for _ in range(3):
+            g.commit_i32(ctx, table, d_scalars, n, wd, d_full, max_bits=bits)
+        weak_ms = max_over_ranks(ctx.timer_end()) / 3
+        full = ctx.download(d_full, rows * 96).reshape(rows, 24)
+        same = bool(np.array_equal(full, dev_records))
+        import torch
+        flag = torch.tensor([1 if same else 0], device="cuda")
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        multi = {"sharding": f"rows dealt to {world} ranks in contiguous blocks of {block}; one NCCL all-gather of "
+                             f"{block * 96} B per rank on the library's stream inside every step",
+                 "gathered_equals_unsharded_on_every_rank": bool(flag.item()),
+                 "weak_scaling": {"value": world * n / (weak_ms * 1e-3), "unit": UNIT, "ms_per_step": weak_ms,
+                                  "what": "every rank commits a whole layer, no collective"},
+                 "single_gpu_ms_per_layer": weak_ms}
+        d_full.free()
+
+    # ---- roofline of the dominant kernel (commit_accumulate), rank 0's launches -------------------
+    roofline = None
+    if rank == 0:
+        peak_instr = ctx.measure_int_peak(2)        # lo/hi multiply-add instructions per second, measured now
+        peak_fmul = ctx.measure_int_peak(3)
+        peak_fsqr = ctx.measure_int_peak(5)
+        peak_madd = ctx.measure_madd_peak()         # mixed additions/s on register-resident operands
+        k_ms = kernel_ms / max(kernel_launches, 1)
+        pairs_per_launch = block * wd
+        adds_per_launch = pairs_per_launch * adds_per_pair
+        achieved = adds_per_launch * EXEC_MUL_INSTR_PER_ADD / (k_ms * 1e-3)
+        cost_model = pairs_per_launch * ALGO_MUL_INSTR_PER_PAIR / (k_ms * 1e-3)
+        peaks_file = ROOT / "MEASURED_PEAKS.json"
+        hbm_peak = json.loads(peaks_file.read_text())["hbm_gbs"] if peaks_file.exists() else 6650.0
+        algo_bytes = pairs_per_launch * 4 + adds_per_launch * 64 + block * 128   # scalars + gathered table points + partial sums
+        roofline = {"bound": "int32-multiply pipe (not hbm, not tensor: no dense contraction on this path)",
+                    "kernel": "commit_accumulate_kernel", "achieved": achieved / 1e12, "peak": peak_instr / 1e12,
+                    "unit": "T multiply-instr/s", "frac": achieved / peak_instr,
+                    "frac_of": "measured peak (this run: dependent-free mad.lo.cc/madc.hi loop at full occupancy)",
+                    "executed_instr_per_add": EXEC_MUL_INSTR_PER_ADD, "adds_per_pair": adds_per_pair,
+                    "cost_model_frac": cost_model / peak_instr,
+                    "cost_model_note": "the reference's algorithm as the unit: 2 byte-window additions x 10 field "
+                                       "multiplications x 264 multiply instructions = 5280 per int16 pair; this kernel "
+                                       "executes one addition per pair, so this figure can exceed 1",
+                    "kernel_ms": k_ms, "pairs_per_launch": pairs_per_launch,
+                    "field_mul_peak_per_s": peak_fmul, "field_sqr_peak_per_s": peak_fsqr,
+                    "adds_per_s": adds_per_launch / (k_ms * 1e-3), "register_resident_add_peak_per_s": peak_madd,
+                    "frac_of_add_peak": adds_per_launch / (k_ms * 1e-3) / peak_madd,
+                    "traffic": int(pairs_per_launch * NCU_DRAM_BYTES_PER_PAIR),
+                    "traffic_source": "ncu dram bytes of a reduced case (8.4 M pairs: 585 MB read+write = 69.8 B/pair) "
+                                      "scaled by pairs; algorithmic 68 B/pair",
+                    "hbm": {"achieved_gbs": algo_bytes / (k_ms * 1e-3) / 1e9, "peak_gbs": hbm_peak,
+                            "frac": algo_bytes / (k_ms * 1e-3) / 1e9 / hbm_peak,
+                            "peak_source": "MEASURED_PEAKS.json" if peaks_file.exists() else "fallback"}}
+
+    # ---- the other half of the metric: proof seconds per layer (every rank proves its own batch) -----
+    proof = None
+    if args.proof_layers and headline:
+        table.close()
+        for b in (d_scalars, d_out, d_stage, d_local if world > 1 else None):
+            if b is not None:
+                b.free()
+        barrier()
+        res = layer_proof(ctx, args.proof_layers, args.proof_window_bits, args.proof_scope, seed=0xC5 + rank,
+                          pieces=(world == 1))
+        slowest = max_over_ranks(res["seconds"] * 1e3) / 1e3
+        proof = {"metric": "proof_seconds_per_layer", "seconds_per_layer": slowest / (args.proof_layers * world),
+                 "unit": "s/layer", "layers_per_rank": args.proof_layers, "layers_total": args.proof_layers * world,
+                 "slowest_batch_s": slowest, "scaling": "weak (one batch of layers per GPU, no data-path collective)",
+                 "timing": "host wall clock around the batch on each rank, synchronised on both sides, max over ranks",
+                 "rank0": res}
+        if ref_pieces is not None:
+            proof["reference_pieces"] = ref_pieces
+            proof["reference_note"] = ("the reference's whole-layer driver needs the model's tensor dumps and cannot run "
+                                       "here; these are its provers on pieces of the same shapes, same GPU, timed before "
+                                       "this library created its context")
 
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
 
-    # ---- roofline of the dominant kernel (commit_accumulate) ----------------------------------
-    peak_instr = ctx.measure_int_peak(2)        # lo/hi multiply-add instructions per second, measured now
-    peak_fmul = ctx.measure_int_peak(3)
-    peak_madd = ctx.measure_madd_peak()         # mixed additions/s on register-resident operands
-    k_ms = kernel_ms / max(kernel_launches, 1)
-    achieved = n * ALGO_MUL_INSTR_PER_PAIR / (k_ms * 1e-3)
-    peaks_file = ROOT / "MEASURED_PEAKS.json"
-    hbm_peak = json.loads(peaks_file.read_text())["hbm_gbs"] if peaks_file.exists() else 6650.0
-    algo_bytes = n * 4 + n * 64 + rows * 128   # scalars + one gathered table point per pair + partial sums
-    roofline = {"bound": "int32-multiply pipe (not hbm, not tensor: no dense contraction on this path)",
-                "kernel": "commit_accumulate_kernel", "achieved": achieved / 1e12, "peak": peak_instr / 1e12,
-                "unit": "T multiply-instr/s", "frac": achieved / peak_instr,
-                "peak_source": "measured in this run: dependent-free mad.lo.cc/madc.hi loop at full occupancy",
-                "algorithmic_instr_per_pair": ALGO_MUL_INSTR_PER_PAIR,
-                "kernel_ms": k_ms, "field_mul_peak_per_s": peak_fmul,
-                "executed": {"adds_per_pair": 1 if args.window_bits == 16 else 2,
-                             "adds_per_s": n * (1 if args.window_bits == 16 else 2) / (k_ms * 1e-3),
-                             "register_resident_add_peak_per_s": peak_madd,
-                             "frac_of_add_peak": n * (1 if args.window_bits == 16 else 2) / (k_ms * 1e-3) / peak_madd,
-                             "note": "the same mixed addition looped on registers, no table or scalar traffic: "
-                                     "what the kernel could reach if memory were free"},
-                "traffic": int(n * NCU_DRAM_BYTES_PER_PAIR), "traffic_source": "ncu dram bytes of a reduced case "
-                "(8.4 M pairs: 585 MB read+write = 69.8 B/pair) scaled by pairs; algorithmic 68 B/pair",
-                "hbm": {"achieved_gbs": algo_bytes / (k_ms * 1e-3) / 1e9, "peak_gbs": hbm_peak,
-                        "frac": algo_bytes / (k_ms * 1e-3) / 1e9 / hbm_peak,
-                        "peak_source": "MEASURED_PEAKS.json" if peaks_file.exists() else "fallback"},
-                }
-
+    assert roofline["frac"] <= 1.0 or args.rows, "executed-work fraction above the measured peak: check the instruction count"
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "u32 limbs (254-bit fields)", "data": "synthetic",
-            "config": workload_config(args.window_bits) if not args.rows else
-            {"workload": f"reduced case for profiling: {rows} rows x {wd} generators", "window_bits": args.window_bits},
-            "clocks": clocks,
+            "config": workload_config() if headline else
+            {"workload": f"reduced case for profiling: {rows} rows x {wd} generators"},
+            "window_bits": args.window_bits, "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": int(n * 4),
-                    "d2h_bytes_per_step": int(rows * 96), "ms_per_step": e2e_ms / args.steps,
+                    "d2h_bytes_per_step": int(world * rows * 96), "ms_per_step": e2e_ms / args.steps,
                     "matches_device_path": host_path_matches},
             "gpu_launches": int(launches), "roofline": roofline, "device_status": status,
-            "table_bytes": table.nbytes}
-
+            "table_bytes": int(2 ** (args.window_bits - 1) * n_windows * wd * 64)}
+    if multi is not None:
+        line["multi_gpu"] = multi
     if ref_cuda is not None:
         line["reference_cuda"] = ref_cuda
-    if args.proof_layers:
-        line["layer_proof"] = layer_proof(ctx, args.proof_layers, args.proof_window_bits, args.proof_scope)
-    if not args.no_cpu_baseline and wd == WD and world == 1:   # host-core baseline: N = 1 only
+    if proof is not None:
+        line["layer_proof"] = proof
+    if not args.no_cpu_baseline and headline and world == 1:   # host-core baseline: N = 1 only
         base, rows_used, rec = cpu_baseline(gens, np.asarray(h_scalars), args.cpu_seconds)
         base["matches_gpu_rows"] = bool(np.array_equal(rec, dev_records[:rows_used]))
         line["cpu_baseline"] = base
@@ -593,7 +698,7 @@ def run_secondary(args):
     elif args.workload == "commit-bls12-381":
         # The C4 shape over BLS12-381 G1 (the reference compiles BN254 only; reported separately).
         wd = args.gens
-        n = wl.layer_weight_elements() // args.shrink if not args.rows else args.rows * wd
+        n = LAYER_PAIRS // args.shrink if not args.rows else args.rows * wd
         n -= n % wd
         rows = n // wd
         gens = wl.make_generators_bls12_381(ctx, wd, SEED)

@@ -107,6 +107,7 @@ def _declare(lib):
     f("grape_fold_i32", [vp, vp, u64, vp, u32, u64, vp])
     f("grape_measure_int_peak", [vp, C.c_int, C.POINTER(C.c_double)])
     f("grape_measure_madd_peak", [vp, C.POINTER(C.c_double)])
+    f("grape_diag_field_check", [vp, C.c_int, vp, u64, C.POINTER(u32)])
     f("grape_timer_begin", [vp])
     f("grape_timer_end", [vp, C.POINTER(C.c_float)])
     f("grape_prof_enable", [vp, C.c_int])
@@ -123,6 +124,7 @@ def _declare(lib):
     f("grape_lookup_destroy", [vp])
     f("grape_lookup_params", [vp, vp, vp, vp, C.POINTER(u32)])
     f("grape_lookup_table", [vp, C.c_int], vp)
+    f("grape_lookup_last_proof", [vp, vp, vp, u32, C.POINTER(u32)])
     f("grape_lookup_prove_range", [vp, vp, vp, u64, vp, vp, u32, u32, u32, vp, u32, vp, vp, vp, vp, u32, C.POINTER(u32)])
     f("grape_lookup_prove_mapping", [vp, vp, vp, vp, u64, vp, vp, vp, u32, u32, u32, vp, u32, vp, vp, vp, vp, u32,
                                      C.POINTER(u32)])

@@ -54,6 +54,7 @@ using namespace grape;
 
 extern "C" int grape_bls12_381_field_binary(grape_ctx* ctx, int field, int op, const void* d_a, const void* d_b,
                                             void* d_out, uint64_t n) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx) return GRAPE_ERR_INVALID;
   if (field < 0 || field > 1 || op < 0 || op > 2)
     return fail(ctx, GRAPE_ERR_INVALID, "field must be 0 (Fr) or 1 (Fp), op 0 (add), 1 (sub) or 2 (mul)");
@@ -78,6 +79,7 @@ extern "C" int grape_bls12_381_field_binary(grape_ctx* ctx, int field, int op, c
 }
 
 extern "C" int grape_bls12_381_fr_from_i32(grape_ctx* ctx, const int32_t* d_in, void* d_out, uint64_t n) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx) return GRAPE_ERR_INVALID;
   if (n == 0) return GRAPE_OK;
   k_bls_from_i32<<<bls_blocks(ctx, n), BLS_THREADS, 0, ctx->stream>>>(d_in, reinterpret_cast<uint32_t*>(d_out), n);
@@ -87,6 +89,7 @@ extern "C" int grape_bls12_381_fr_from_i32(grape_ctx* ctx, const int32_t* d_in, 
 }
 
 extern "C" int grape_bls12_381_measure_mul_peak(grape_ctx* ctx, double* muls_per_second) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !muls_per_second) return GRAPE_ERR_INVALID;
   arena_reset(ctx);
   uint32_t* sink = nullptr;

@@ -8,19 +8,27 @@
 //   C_row = sum_i B[idx_i] * G_i = sum_t B[t] * P_t,      P_t = sum of the G_i of the row with idx_i = t.
 //
 //   stage 1  per row: counting sort of the row's elements by table entry in shared memory
-//            (k_row_sort), then one thread per 8 consecutive entries adds the generators of each
-//            entry and normalises the 8 sums with one shared inversion (k_bucket_points)
-//            -- ONE addition per element;
+//            (k_row_sort); one thread per 32 consecutive entries walks their elements in ONE flat loop
+//            and stores the sum of every entry as it completes (k_bucket_sums) -- one addition per
+//            element, lanes of a warp differ only by the spread of 32-entry totals; the sums are then
+//            normalised to affine, 16 to an inversion (k_normalise);
 //   stage 2  per row a variable-base multi-scalar multiplication of the n_bins points P_t by the
 //            scalars B[t], which are the SAME for every row: their signed 13-bit digits are sorted
-//            once per window (k_digit_keys + k_row_sort again), and one block per (row, window)
-//            walks the magnitudes from the top with the running-sum rule, every thread taking a
-//            contiguous range of magnitudes (k_window_sums) -- n_bins additions per window;
+//            by magnitude once per window (k_digit_keys + k_row_sort + k_pack_entries).
+//            2a (k_window_buckets): the sorted list of a window is cut into slices of about equal
+//            length that end on magnitude boundaries; a lane walks one slice, adds the +-P_t of one
+//            magnitude after the other and stores each magnitude's sum when it is complete.  Every
+//            lane executes one mixed addition per step; a change of magnitude costs a store, not a
+//            divergent general addition.
+//            2b (k_window_running_sums): one warp per (row, window): lane l takes the magnitudes
+//            (128 l, 128 l + 128] from the top with the running-sum rule (run += bucket, tot += run),
+//            adds 128 l * run, and the warp adds up its 32 totals;
 //   stage 3  the finalize kernel of the fixed-base path recombines the windows (Horner) and adds
 //            the shared point of the padded columns.
 //
-// Cost per row: elements + n_bins * (windows + ~3) additions instead of elements * windows.  The
-// result is the same group element, so the normalised record is bit-identical.
+// Cost per row in mixed-addition times: about 1.2 * elements (stage 1) + n_bins * (1.3 + 20 * 1.27)
+// instead of elements * windows.  The result is the same group element, so the normalised record is
+// bit-identical.
 #include <algorithm>
 
 #include "ctx.cuh"
@@ -103,47 +111,65 @@ __global__ void __launch_bounds__(SORT_THREADS) k_row_sort(const uint32_t* __res
   }
 }
 
-// Stage 1 sums.  One thread: 8 consecutive table entries of one row; P[row][t] = sum of the
-// generators of the row's elements with index t, affine ((0,0) when the entry does not occur).
-constexpr int BUCKET_BATCH = 8;
-__global__ void __launch_bounds__(128) k_bucket_points(const Affine* __restrict__ gens, const uint32_t* __restrict__ offs,
-                                                       const uint32_t* __restrict__ sorted, uint32_t wd, uint32_t n_bins,
-                                                       uint64_t n_threads, Affine* __restrict__ P) {
+// Stage 1 sums.  One thread: BS_ENTRIES consecutive table entries of one row, walked as one flat
+// list of elements; Px[row][t] = sum of the generators of the row's elements with index t (XYZZ,
+// infinity when the entry does not occur).
+constexpr int BS_ENTRIES = 32;
+__global__ void __launch_bounds__(128, 4) k_bucket_sums(const Affine* __restrict__ gens, const uint32_t* __restrict__ offs,
+                                                     const uint32_t* __restrict__ sorted, uint32_t wd, uint32_t n_bins,
+                                                     uint64_t n_threads, Xyzz* __restrict__ Px) {
   const uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= n_threads) return;
-  const uint32_t per_row = n_bins / BUCKET_BATCH;
+  const uint32_t per_row = n_bins / BS_ENTRIES;
   const uint64_t row = gid / per_row;
-  const uint32_t t0 = (uint32_t)(gid % per_row) * BUCKET_BATCH;
+  const uint32_t t0 = (uint32_t)(gid % per_row) * BS_ENTRIES, t1 = t0 + BS_ENTRIES;
   const uint32_t* orow = offs + row * (uint64_t)(n_bins + 1);
   const uint32_t* srow = sorted + row * wd;
-  Xyzz e[BUCKET_BATCH];
-  Fp pref[BUCKET_BATCH];
+  Xyzz* prow = Px + row * n_bins;
+  uint32_t t = t0;
+  uint32_t pos = orow[t0];
+  uint32_t next = orow[t0 + 1];  // one past the last element of entry t
+  Xyzz acc = Xyzz::inf();
+  for (;;) {
+    while (pos == next) {  // entry t is complete (possibly empty)
+      acc.store(prow + t);
+      acc = Xyzz::inf();
+      t++;
+      if (t == t1) return;
+      next = orow[t + 1];
+    }
+    xyzz_madd(acc, Affine::load_nc(gens + srow[pos]));
+    pos++;
+  }
+}
+
+// Px (XYZZ) -> P (affine, (0,0) for infinity), NORM_BATCH consecutive points per inversion.
+constexpr int NORM_BATCH = 16;
+__global__ void __launch_bounds__(128) k_normalise(const Xyzz* __restrict__ Px, uint64_t n, Affine* __restrict__ P) {
+  const uint64_t i0 = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * NORM_BATCH;
+  if (i0 >= n) return;
+  const int cnt = (int)min((uint64_t)NORM_BATCH, n - i0);
+  Fp pref[NORM_BATCH];
   Fp run = Fp::one();
 #pragma unroll 1
-  for (int k = 0; k < BUCKET_BATCH; k++) {
-    const uint32_t s = orow[t0 + k], en = orow[t0 + k + 1];
-    Xyzz acc = Xyzz::inf();
-#pragma unroll 1
-    for (uint32_t j = s; j < en; j++) xyzz_madd(acc, Affine::load_nc(gens + srow[j]));
-    e[k] = acc;
-    Fp zp = acc.is_inf() ? Fp::one() : fe_mul(acc.zz, acc.zzz);
-    run = fe_mul(run, zp);
+  for (int k = 0; k < cnt; k++) {
+    const char* e = reinterpret_cast<const char*>(Px + i0 + k);
+    const Fp zzz = Fp::load(e + 2 * Fp::BYTES), zz = Fp::load(e + 3 * Fp::BYTES);
+    if (!zz.is_zero()) run = fe_mul(run, fe_mul(zz, zzz));
     pref[k] = run;
   }
   Fp inv = fe_inv(run);
 #pragma unroll 1
-  for (int k = BUCKET_BATCH - 1; k >= 0; k--) {
-    Fp zp = e[k].is_inf() ? Fp::one() : fe_mul(e[k].zz, e[k].zzz);
-    Fp zinv = (k == 0) ? inv : fe_mul(inv, pref[k - 1]);
-    inv = fe_mul(inv, zp);
-    Affine out;
-    if (e[k].is_inf()) {
-      out = Affine::inf();
-    } else {
-      out.x = fe_mul(e[k].x, fe_mul(zinv, e[k].zzz));
-      out.y = fe_mul(e[k].y, fe_mul(zinv, e[k].zz));
+  for (int k = cnt - 1; k >= 0; k--) {
+    const Xyzz e = Xyzz::load(Px + i0 + k);
+    Affine out = Affine::inf();
+    if (!e.is_inf()) {
+      const Fp zinv = (k == 0) ? inv : fe_mul(inv, pref[k - 1]);  // 1 / (zz * zzz) of point k
+      inv = fe_mul(inv, fe_mul(e.zz, e.zzz));
+      out.x = fe_mul(e.x, fe_mul(zinv, e.zzz));
+      out.y = fe_mul(e.y, fe_mul(zinv, e.zz));
     }
-    out.store(P + row * n_bins + t0 + k);
+    out.store(P + i0 + k);
   }
 }
 
@@ -169,61 +195,106 @@ __global__ void k_digit_keys(const uint32_t* __restrict__ B, uint32_t n_bins, Bi
   }
 }
 
-// Stage 2.  One block per (row, window): sum over magnitudes m of m * (sum of the +-P_t whose digit
-// has magnitude m).  Thread k takes the magnitudes (k*per, (k+1)*per] from the top down with the
-// running-sum rule (run += bucket, tot += run), corrects by (k*per) * run, and the block adds up.
-constexpr int WS_THREADS = 256;
-__global__ void __launch_bounds__(WS_THREADS) k_window_sums(const Affine* __restrict__ P, uint32_t n_bins,
-                                                            const uint32_t* __restrict__ offs2,
-                                                            const uint32_t* __restrict__ sorted2,
-                                                            const uint8_t* __restrict__ neg, Xyzz* __restrict__ partial) {
-  __shared__ __align__(16) unsigned char red_raw[(WS_THREADS / 32) * sizeof(Xyzz)];
-  Xyzz* red = reinterpret_cast<Xyzz*>(red_raw);
-  const uint64_t row = blockIdx.x;
-  const uint32_t w = blockIdx.y;
-  const uint32_t tid = threadIdx.x;
-  constexpr uint32_t per = STAGE2_HALF / WS_THREADS;
-  const uint32_t base = tid * per;  // this thread's magnitudes are base + 1 .. base + per
+// ent[w][pos] = (table entry | sign << 31, magnitude) of the pos-th entry of window w in ascending
+// order of magnitude: what a lane of stage 2a needs for one step, in one 8-byte load.
+__global__ void k_pack_entries(const uint32_t* __restrict__ sorted2, const uint32_t* __restrict__ mags,
+                               const uint8_t* __restrict__ neg, uint32_t n_bins, uint2* __restrict__ ent) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (uint64_t)STAGE2_WINDOWS * n_bins) return;
+  const uint64_t w = i / n_bins;
+  const uint32_t t = sorted2[i];
+  ent[i] = make_uint2(t | ((uint32_t)neg[w * n_bins + t] << 31), mags[w * n_bins + t]);
+}
+
+// Stage 2a.  One lane: slice k of window w of one row.  The slice covers whole magnitudes: it starts
+// after the first magnitude at which the running count of the window's entries reaches k * L and ends
+// at the first at which it reaches (k + 1) * L, so every magnitude belongs to exactly one lane and a
+// slice is within one bucket length of L entries.  S[row][w][m - 1] = sum of the +-P_t of magnitude m;
+// magnitudes that no entry has keep the zeros (= infinity) the buffer was cleared to.
+constexpr int WB_THREADS = 128;
+__global__ void __launch_bounds__(WB_THREADS, 4)
+k_window_buckets(const Affine* __restrict__ P, uint32_t n_bins, const uint32_t* __restrict__ offs2,
+                 const uint2* __restrict__ ent, uint32_t slices, uint32_t slice_len, uint64_t n_threads,
+                 Xyzz* __restrict__ S) {
+  const uint64_t gid = (uint64_t)blockIdx.x * WB_THREADS + threadIdx.x;
+  if (gid >= n_threads) return;
+  const uint32_t k = (uint32_t)(gid % slices);
+  const uint64_t rw = gid / slices;
+  const uint32_t w = (uint32_t)(rw % STAGE2_WINDOWS);
+  const uint64_t row = rw / STAGE2_WINDOWS;
   const uint32_t* o2 = offs2 + (uint64_t)w * (STAGE2_HALF + 2);
-  const uint32_t* s2 = sorted2 + (uint64_t)w * n_bins;
-  const uint8_t* ng = neg + (uint64_t)w * n_bins;
+  const uint32_t first = __ldg(o2 + 1);                  // entries with a zero digit come first
+  const uint32_t cnt = __ldg(o2 + STAGE2_HALF + 1) - first;
+  // smallest magnitude m in [0, HALF] with (number of entries of magnitude 1..m) >= target
+  auto bound = [&](uint64_t target) -> uint32_t {
+    if (target >= cnt) target = cnt;
+    uint32_t lo = 0, hi = STAGE2_HALF;
+    while (lo < hi) {
+      const uint32_t mid = (lo + hi) >> 1;
+      if ((uint64_t)(__ldg(o2 + mid + 1) - first) >= target) hi = mid;
+      else lo = mid + 1;
+    }
+    return lo;
+  };
+  const uint32_t m_lo = bound((uint64_t)k * slice_len);
+  const uint32_t m_hi = (k + 1 == slices) ? STAGE2_HALF : bound((uint64_t)(k + 1) * slice_len);
+  uint32_t pos = __ldg(o2 + m_lo + 1);
+  const uint32_t end = __ldg(o2 + m_hi + 1);
+  if (pos >= end) return;
+  const uint2* e = ent + (uint64_t)w * n_bins;
   const Affine* prow = P + row * n_bins;
+  Xyzz* srow = S + (row * STAGE2_WINDOWS + w) * STAGE2_HALF;
+  uint32_t m_cur = 0;
+  Xyzz run = Xyzz::inf();
+  for (; pos < end; pos++) {
+    const uint2 en = __ldg(e + pos);
+    if (en.y != m_cur) {
+      if (m_cur) run.store(srow + (m_cur - 1));
+      run = Xyzz::inf();
+      m_cur = en.y;
+    }
+    Affine p = Affine::load_nc(prow + (en.x & 0x7fffffffu));
+    if (en.x >> 31) p.y = fe_neg(p.y);  // the point at infinity is (0, 0) and stays so
+    xyzz_madd(run, p);
+  }
+  run.store(srow + (m_cur - 1));
+}
+
+// Stage 2b.  One warp per (row, window): sum over magnitudes m of m * S_m.  Lane l takes the magnitudes
+// (base, base + 128], base = 128 l, from the top with the running-sum rule, which leaves
+// tot = sum (m - base) * S_m and run = sum S_m; base * run is added by double-and-add over the five
+// bits of l followed by seven doublings; a shuffle tree adds the 32 totals.
+constexpr int RS_THREADS = 128;
+constexpr uint32_t RS_PER_LANE = STAGE2_HALF / 32;
+__global__ void __launch_bounds__(RS_THREADS)
+k_window_running_sums(const Xyzz* __restrict__ S, uint64_t n_units, Xyzz* __restrict__ partial) {
+  const uint64_t unit = (uint64_t)blockIdx.x * (RS_THREADS / 32) + (threadIdx.x >> 5);
+  if (unit >= n_units) return;  // whole warps leave together
+  const uint32_t lane = threadIdx.x & 31;
+  const Xyzz* s = S + unit * STAGE2_HALF + (uint64_t)lane * RS_PER_LANE;
   Xyzz run = Xyzz::inf(), tot = Xyzz::inf();
 #pragma unroll 1
-  for (uint32_t m = base + per; m > base; m--) {
-    const uint32_t s = o2[m], en = o2[m + 1];
-#pragma unroll 1
-    for (uint32_t j = s; j < en; j++) {
-      const uint32_t t = s2[j];
-      Affine p = Affine::load_nc(prow + t);
-      if (ng[t]) p.y = fe_neg(p.y);  // the point at infinity is (0, 0) and stays so
-      xyzz_madd(run, p);
-    }
+  for (int m = (int)RS_PER_LANE - 1; m >= 0; m--) {
+    xyzz_add(run, Xyzz::load(s + m));
     xyzz_add(tot, run);
   }
-  // tot = sum (m - base) * bucket_m; add base * run by double-and-add over the bits of base
-  if (base != 0 && !run.is_inf()) {
+  if (lane != 0 && !run.is_inf()) {
     Xyzz acc = Xyzz::inf();
 #pragma unroll 1
-    for (int bit = 31 - __clz(base); bit >= 0; bit--) {
+    for (int bit = 4; bit >= 0; bit--) {
       acc = xyzz_dbl(acc);
-      if ((base >> bit) & 1u) xyzz_add(acc, run);
+      if ((lane >> bit) & 1u) xyzz_add(acc, run);
     }
+#pragma unroll 1
+    for (uint32_t v = RS_PER_LANE; v > 1; v >>= 1) acc = xyzz_dbl(acc);
     xyzz_add(tot, acc);
   }
 #pragma unroll 1
   for (int off = 16; off > 0; off >>= 1) {
     Xyzz other = xyzz_shfl_down(tot, off);
-    if ((tid & 31) < (uint32_t)off) xyzz_add(tot, other);
+    if (lane < (uint32_t)off) xyzz_add(tot, other);
   }
-  if ((tid & 31) == 0) tot.store(red + (tid >> 5));
-  __syncthreads();
-  if (tid == 0) {
-    Xyzz acc = Xyzz::load(red);
-#pragma unroll 1
-    for (int k = 1; k < WS_THREADS / 32; k++) xyzz_add(acc, Xyzz::load(red + k));
-    acc.store(partial + row * STAGE2_WINDOWS + w);
-  }
+  if (lane == 0) tot.store(partial + unit);
 }
 
 // Row commitments  C_row = sum_i B[idx[row][i]] * G_i  (+ extra, the same point for every row).
@@ -231,8 +302,9 @@ __global__ void __launch_bounds__(WS_THREADS) k_window_sums(const Affine* __rest
 // Returns GRAPE_ERR_INVALID when the shape is not supported (the caller then commits directly).
 int commit_gathered_async(grape_ctx* ctx, const grape_table* t, const uint32_t* d_idx, const uint32_t* d_B,
                           uint32_t n_bins, uint64_t size, uint32_t wd, const void* d_extra, void* d_out) {
-  if (!t || t->curve != Bn254::ID || wd == 0 || wd > t->n_gens || size % wd != 0 || n_bins < BUCKET_BATCH ||
-      n_bins % BUCKET_BATCH != 0 || n_bins > (1u << 24) || STAGE2_HALF % WS_THREADS != 0)
+  static_assert(STAGE2_HALF % 32 == 0 && (RS_PER_LANE & (RS_PER_LANE - 1)) == 0, "stage 2b lane ranges");
+  if (!t || t->curve != Bn254::ID || wd == 0 || wd > t->n_gens || size % wd != 0 || n_bins < BS_ENTRIES ||
+      n_bins % BS_ENTRIES != 0 || n_bins > (1u << 24))
     return GRAPE_ERR_INVALID;
   const uint64_t rows = size / wd;
   if (rows == 0) return GRAPE_OK;
@@ -240,15 +312,21 @@ int commit_gathered_async(grape_ctx* ctx, const grape_table* t, const uint32_t* 
   int rc;
   uint32_t *offs, *sorted, *mags, *offs2, *sorted2;
   uint8_t* neg;
+  uint2* ent;
   Affine* P;
-  Xyzz* partial;
+  Xyzz *Px, *S, *partial;
+  // rows per pass of stage 2: bounds the bucket-sum buffer (10.5 MB per row) to about 1.3 GB
+  const uint64_t batch = std::min<uint64_t>(rows, 128);
   if ((rc = arena_alloc_t(ctx, rows * (uint64_t)(n_bins + 1), &offs))) return rc;
   if ((rc = arena_alloc_t(ctx, rows * (uint64_t)wd, &sorted))) return rc;
   if ((rc = arena_alloc_t(ctx, rows * (uint64_t)n_bins, &P))) return rc;
+  if ((rc = arena_alloc_t(ctx, rows * (uint64_t)n_bins, &Px))) return rc;
   if ((rc = arena_alloc_t(ctx, (uint64_t)STAGE2_WINDOWS * n_bins, &mags))) return rc;
   if ((rc = arena_alloc_t(ctx, (uint64_t)STAGE2_WINDOWS * n_bins, &neg))) return rc;
   if ((rc = arena_alloc_t(ctx, (uint64_t)STAGE2_WINDOWS * (STAGE2_HALF + 2), &offs2))) return rc;
   if ((rc = arena_alloc_t(ctx, (uint64_t)STAGE2_WINDOWS * n_bins, &sorted2))) return rc;
+  if ((rc = arena_alloc_t(ctx, (uint64_t)STAGE2_WINDOWS * n_bins, &ent))) return rc;
+  if ((rc = arena_alloc_t(ctx, batch * STAGE2_WINDOWS * STAGE2_HALF, &S))) return rc;
   if ((rc = arena_alloc_t(ctx, rows * STAGE2_WINDOWS, &partial))) return rc;
   GRAPE_CUDA_TRY(ctx, cudaFuncSetAttribute(k_row_sort, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)(SORT_PART_BINS * sizeof(uint32_t))));
@@ -258,10 +336,13 @@ int commit_gathered_async(grape_ctx* ctx, const grape_table* t, const uint32_t* 
     const size_t smem = (size_t)std::min(n_bins, SORT_PART_BINS) * sizeof(uint32_t);
     k_row_sort<<<dim3((uint32_t)rows, parts), SORT_THREADS, smem, ctx->stream>>>(d_idx, wd, n_bins, offs, sorted);
     const Affine* gens = reinterpret_cast<const Affine*>(t->data) + (uint64_t)t->first_digit_row * t->n_gens;
-    const uint64_t n_threads = rows * (n_bins / BUCKET_BATCH);
-    k_bucket_points<<<(uint32_t)((n_threads + 127) / 128), 128, 0, ctx->stream>>>(gens, offs, sorted, wd, n_bins,
-                                                                                   n_threads, P);
-    ctx->launches += 2;
+    const uint64_t n_threads = rows * (n_bins / BS_ENTRIES);
+    k_bucket_sums<<<(uint32_t)((n_threads + 127) / 128), 128, 0, ctx->stream>>>(gens, offs, sorted, wd, n_bins,
+                                                                                 n_threads, Px);
+    const uint64_t n_pts = rows * (uint64_t)n_bins;
+    const uint64_t norm_threads = (n_pts + NORM_BATCH - 1) / NORM_BATCH;
+    k_normalise<<<(uint32_t)((norm_threads + 127) / 128), 128, 0, ctx->stream>>>(Px, n_pts, P);
+    ctx->launches += 3;
   }
   // stage 2: digits of the shared scalars, sorted by magnitude per window (keys 0 .. STAGE2_HALF)
   {
@@ -274,9 +355,27 @@ int commit_gathered_async(grape_ctx* ctx, const grape_table* t, const uint32_t* 
     k_digit_keys<<<(n_bins + 255) / 256, 256, 0, ctx->stream>>>(d_B, n_bins, bias, mags, neg);
     k_row_sort<<<dim3(STAGE2_WINDOWS, 1), SORT_THREADS, (STAGE2_HALF + 1) * sizeof(uint32_t), ctx->stream>>>(
         mags, n_bins, STAGE2_HALF + 1, offs2, sorted2);
-    k_window_sums<<<dim3((uint32_t)rows, STAGE2_WINDOWS), WS_THREADS, 0, ctx->stream>>>(P, n_bins, offs2, sorted2, neg,
-                                                                                        partial);
+    const uint64_t n_ent = (uint64_t)STAGE2_WINDOWS * n_bins;
+    k_pack_entries<<<(uint32_t)((n_ent + 255) / 256), 256, 0, ctx->stream>>>(sorted2, mags, neg, n_bins, ent);
     ctx->launches += 3;
+    // slices of about 256 entries: long enough that a lane's last partial step and the spread of slice
+    // lengths inside a warp stay small, short enough that one row fills 20 * n_bins / 256 lanes
+    const uint32_t slice_len = 256;
+    const uint32_t slices = (n_bins + slice_len - 1) / slice_len;
+    for (uint64_t r0 = 0; r0 < rows; r0 += batch) {
+      const uint64_t nr = std::min<uint64_t>(batch, rows - r0);
+      GRAPE_CUDA_TRY(ctx, cudaMemsetAsync(S, 0, nr * STAGE2_WINDOWS * STAGE2_HALF * sizeof(Xyzz), ctx->stream));
+      const uint64_t n_threads = nr * STAGE2_WINDOWS * slices;
+      {
+        ProfScope prof(ctx);
+        k_window_buckets<<<(uint32_t)((n_threads + WB_THREADS - 1) / WB_THREADS), WB_THREADS, 0, ctx->stream>>>(
+            P + r0 * n_bins, n_bins, offs2, ent, slices, slice_len, n_threads, S);
+      }
+      const uint64_t n_units = nr * STAGE2_WINDOWS;
+      k_window_running_sums<<<(uint32_t)((n_units + RS_THREADS / 32 - 1) / (RS_THREADS / 32)), RS_THREADS, 0,
+                              ctx->stream>>>(S, n_units, partial + r0 * STAGE2_WINDOWS);
+      ctx->launches += 2;
+    }
   }
   GRAPE_CUDA_TRY(ctx, cudaGetLastError());
   // stage 3: Horner over the windows, extra point, normalisation

@@ -2,12 +2,33 @@
 #include <cstring>
 #include <vector>
 
+#include <sys/random.h>
+#include <cstdio>
+
 #include "ctx.cuh"
 #include "hostfr.hpp"
 
 using namespace grape;
 
-extern "C" int grape_version(void) { return 1; }
+extern "C" int grape_version(void) { return 2; }
+
+namespace grape {
+bool rng_os_key(RngKey* key) {
+  unsigned char* p = reinterpret_cast<unsigned char*>(key->k);
+  size_t got = 0;
+  while (got < sizeof key->k) {
+    ssize_t r = getrandom(p + got, sizeof key->k - got, 0);
+    if (r <= 0) break;
+    got += (size_t)r;
+  }
+  if (got == sizeof key->k) return true;
+  FILE* f = fopen("/dev/urandom", "rb");
+  if (!f) return false;
+  const size_t n = fread(p, 1, sizeof key->k, f);
+  fclose(f);
+  return n == sizeof key->k;
+}
+}  // namespace grape
 
 extern "C" int grape_ctx_create(int device, grape_ctx** out) {
   if (!out) return GRAPE_ERR_INVALID;
@@ -30,12 +51,19 @@ extern "C" int grape_ctx_create(int device, grape_ctx** out) {
     return GRAPE_ERR_NOMEM;
   }
   cudaMemsetAsync(ctx->d_status, 0, 64, ctx->stream);
-  ctx->rng_state = splitmix_init(0, 0);
+  // blinders and challenges come from ChaCha20 under an OS-drawn key unless grape_rng_seed is called
+  if (!rng_os_key(&ctx->rng.key)) {
+    cudaFree(ctx->d_status);
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return GRAPE_ERR_INVALID;  // no entropy source: refuse rather than fall back to a fixed stream
+  }
   *out = ctx;
   return GRAPE_OK;
 }
 
 extern "C" int grape_ctx_destroy(grape_ctx* ctx) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx) return GRAPE_OK;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
@@ -56,6 +84,7 @@ extern "C" int grape_ctx_destroy(grape_ctx* ctx) {
 extern "C" const char* grape_ctx_error(const grape_ctx* ctx) { return ctx ? ctx->err.c_str() : "null context"; }
 
 extern "C" int grape_ctx_sync(grape_ctx* ctx) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx) return GRAPE_ERR_INVALID;
   GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
   return GRAPE_OK;
@@ -66,6 +95,7 @@ extern "C" void* grape_ctx_stream(grape_ctx* ctx) { return ctx ? (void*)ctx->str
 extern "C" uint64_t grape_ctx_launches(const grape_ctx* ctx) { return ctx ? ctx->launches : 0; }
 
 extern "C" int grape_ctx_status(grape_ctx* ctx, uint32_t* flags) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !flags) return GRAPE_ERR_INVALID;
   uint32_t h = 0;
   GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(&h, ctx->d_status, 4, cudaMemcpyDeviceToHost, ctx->stream));
@@ -76,19 +106,23 @@ extern "C" int grape_ctx_status(grape_ctx* ctx, uint32_t* flags) {
 }
 
 extern "C" int grape_rng_seed(grape_ctx* ctx, uint64_t seed) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx) return GRAPE_ERR_INVALID;
-  ctx->rng_state = splitmix_init(seed, 0);
+  ctx->rng.seeded = true;   // the replayable 64-bit test stream (see rng.cuh): not for production proofs
+  ctx->rng.splitmix = splitmix_init(seed, 0);
   return GRAPE_OK;
 }
 
 extern "C" int grape_rng_fr(grape_ctx* ctx, void* h_out, uint64_t n) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || (!h_out && n)) return GRAPE_ERR_INVALID;
   HostFr* o = reinterpret_cast<HostFr*>(h_out);
-  for (uint64_t i = 0; i < n; i++) o[i] = rng_next_fr(ctx->rng_state);
+  for (uint64_t i = 0; i < n; i++) o[i] = rng_draw_fr(ctx->rng);
   return GRAPE_OK;
 }
 
 extern "C" int grape_dev_alloc(grape_ctx* ctx, size_t bytes, void** d_out) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !d_out) return GRAPE_ERR_INVALID;
   *d_out = nullptr;
   if (bytes == 0) return GRAPE_OK;
@@ -101,6 +135,7 @@ extern "C" int grape_dev_alloc(grape_ctx* ctx, size_t bytes, void** d_out) {
 }
 
 extern "C" int grape_dev_free(grape_ctx* ctx, void* d_ptr) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx) return GRAPE_ERR_INVALID;
   if (!d_ptr) return GRAPE_OK;
   GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
@@ -109,6 +144,7 @@ extern "C" int grape_dev_free(grape_ctx* ctx, void* d_ptr) {
 }
 
 extern "C" int grape_h2d(grape_ctx* ctx, void* d_dst, const void* h_src, size_t bytes) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx) return GRAPE_ERR_INVALID;
   if (bytes == 0) return GRAPE_OK;
   GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_dst, h_src, bytes, cudaMemcpyHostToDevice, ctx->stream));
@@ -123,6 +159,7 @@ extern "C" int grape_h2d(grape_ctx* ctx, void* d_dst, const void* h_src, size_t 
 // use by it).  *ticket identifies the copy for grape_prefetch_wait, which makes the main stream wait
 // for that copy (and releases the ticket).
 extern "C" int grape_h2d_prefetch(grape_ctx* ctx, void* d_dst, const void* h_src, size_t bytes, uint32_t* ticket) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !ticket) return GRAPE_ERR_INVALID;
   if (!ctx->copy_stream) GRAPE_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
   if (ctx->copy_events.empty()) {
@@ -149,6 +186,7 @@ extern "C" int grape_h2d_prefetch(grape_ctx* ctx, void* d_dst, const void* h_src
 }
 
 extern "C" int grape_prefetch_wait(grape_ctx* ctx, uint32_t ticket) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || ticket >= ctx->prefetch_events.size()) return GRAPE_ERR_INVALID;
   GRAPE_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->prefetch_events[ticket], 0));
   ctx->free_tickets.push_back(ticket);
@@ -156,6 +194,7 @@ extern "C" int grape_prefetch_wait(grape_ctx* ctx, uint32_t ticket) {
 }
 
 extern "C" int grape_d2h(grape_ctx* ctx, void* h_dst, const void* d_src, size_t bytes) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx) return GRAPE_ERR_INVALID;
   if (bytes)
     GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(h_dst, d_src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
@@ -164,6 +203,7 @@ extern "C" int grape_d2h(grape_ctx* ctx, void* h_dst, const void* d_src, size_t 
 }
 
 extern "C" int grape_d2d(grape_ctx* ctx, void* d_dst, const void* d_src, size_t bytes) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx) return GRAPE_ERR_INVALID;
   if (bytes)
     GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_dst, d_src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
@@ -171,12 +211,14 @@ extern "C" int grape_d2d(grape_ctx* ctx, void* d_dst, const void* d_src, size_t 
 }
 
 extern "C" int grape_dev_zero(grape_ctx* ctx, void* d_dst, size_t bytes) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx) return GRAPE_ERR_INVALID;
   if (bytes) GRAPE_CUDA_TRY(ctx, cudaMemsetAsync(d_dst, 0, bytes, ctx->stream));
   return GRAPE_OK;
 }
 
 extern "C" int grape_host_alloc_pinned(grape_ctx* ctx, size_t bytes, void** h_out) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !h_out) return GRAPE_ERR_INVALID;
   cudaError_t e = cudaMallocHost(h_out, bytes);
   if (e != cudaSuccess) return fail(ctx, GRAPE_ERR_NOMEM, "cudaMallocHost failed");
@@ -184,6 +226,7 @@ extern "C" int grape_host_alloc_pinned(grape_ctx* ctx, size_t bytes, void** h_ou
 }
 
 extern "C" int grape_host_free_pinned(grape_ctx* ctx, void* h_ptr) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx) return GRAPE_ERR_INVALID;
   if (h_ptr) GRAPE_CUDA_TRY(ctx, cudaFreeHost(h_ptr));
   return GRAPE_OK;
@@ -191,6 +234,7 @@ extern "C" int grape_host_free_pinned(grape_ctx* ctx, void* h_ptr) {
 
 // ---- timing helpers (CUDA events on the context's stream) --------------------------------------
 extern "C" int grape_timer_begin(grape_ctx* ctx) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx) return GRAPE_ERR_INVALID;
   if (!ctx->t0) {
     GRAPE_CUDA_TRY(ctx, cudaEventCreate(&ctx->t0));
@@ -201,6 +245,7 @@ extern "C" int grape_timer_begin(grape_ctx* ctx) {
 }
 
 extern "C" int grape_timer_end(grape_ctx* ctx, float* ms) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !ms || !ctx->t0) return GRAPE_ERR_INVALID;
   GRAPE_CUDA_TRY(ctx, cudaEventRecord(ctx->t1, ctx->stream));
   GRAPE_CUDA_TRY(ctx, cudaEventSynchronize(ctx->t1));
@@ -209,12 +254,14 @@ extern "C" int grape_timer_end(grape_ctx* ctx, float* ms) {
 }
 
 extern "C" int grape_lookup_set_bucket_commit(grape_ctx* ctx, int mode) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || mode < 0 || mode > 2) return GRAPE_ERR_INVALID;
   ctx->bucket_mode = mode;
   return GRAPE_OK;
 }
 
 extern "C" int grape_prof_enable(grape_ctx* ctx, int on) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx) return GRAPE_ERR_INVALID;
   ctx->profile = on != 0;
   return GRAPE_OK;
@@ -222,6 +269,7 @@ extern "C" int grape_prof_enable(grape_ctx* ctx, int on) {
 
 // Sums and clears the recorded dominant-kernel intervals.
 extern "C" int grape_prof_read(grape_ctx* ctx, float* total_ms, uint32_t* count) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !total_ms || !count) return GRAPE_ERR_INVALID;
   GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
   float sum = 0;

@@ -7,6 +7,7 @@
 #include <vector>
 
 #include "../../include/grape_b200.h"
+#include "rng.cuh"
 
 struct grape_ctx {
   int device = 0;
@@ -26,7 +27,7 @@ struct grape_ctx {
   size_t pinned_bytes = 0;
   void* dstage = nullptr;
   size_t dstage_bytes = 0;
-  uint64_t rng_state = 0;
+  grape::RngState rng;   // prover randomness: OS-keyed ChaCha20, or the seeded test stream
   // device status word: kernels OR a GRAPE_STATUS_* bit into it instead of trapping
   uint32_t* d_status = nullptr;
   std::string err;
@@ -79,6 +80,15 @@ struct ProfScope {
 
 constexpr uint32_t STATUS_DIGIT_RANGE = 1u;  // a scalar exceeded the declared max_bits
 constexpr uint32_t STATUS_HIST_RANGE = 2u;   // a lookup query fell outside the table
+constexpr uint32_t STATUS_PIPE_TIMEOUT = 4u; // a bounded wait on a shared-memory copy pipeline ran out
+
+// Every entry point that takes a context makes the context's GPU the calling thread's current
+// device first (allocations and launches would otherwise land on whatever device the caller, or
+// another library in the process, selected last) and leaves it current.
+inline void make_device_current(const grape_ctx* ctx) {
+  int d = -1;
+  if (cudaGetDevice(&d) != cudaSuccess || d != ctx->device) cudaSetDevice(ctx->device);
+}
 
 inline int fail(grape_ctx* ctx, int code, const std::string& msg) {
   if (ctx) ctx->err = msg;

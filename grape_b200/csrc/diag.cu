@@ -4,6 +4,7 @@
 //   kind 1: mad.wide.u32         (32x32 -> 64-bit multiply-add)
 //   kind 2: mad.lo.cc + madc.hi  (the lo/hi pair form the field arithmetic is written in)
 //   kind 3: Montgomery multiplications in Fp (field muls per second)
+//   kind 4: the same with a 16-product loop body;  kind 5: dedicated squarings in Fp
 #include "ctx.cuh"
 #include "curve.cuh"
 
@@ -86,6 +87,17 @@ __global__ void __launch_bounds__(256) k_int_peak(uint32_t* sink, uint32_t seed)
       }
     }
     if (x[0].v[0] == 0x12345 && x[1].v[3] == 7 && x[3].v[2] == 9) sink[0] = x[0].v[1];
+  } else if (KIND == 5) {
+    // dedicated squarings, two independent chains per thread
+    Fp x[2];
+#pragma unroll
+    for (int i = 0; i < 8; i++) { x[0].v[i] = a + i; x[1].v[i] = b + i; }
+    x[0].v[7] &= 0x0fffffffu; x[1].v[7] &= 0x0fffffffu;
+    for (int it = 0; it < PEAK_ITERS / 8; it++) {
+      x[0] = fe_sqr(x[0]);
+      x[1] = fe_sqr(x[1]);
+    }
+    if (x[0].v[0] == 0x12345 && x[1].v[3] == 7) sink[0] = x[0].v[1];
   } else {
     Fp x[2], y;
 #pragma unroll
@@ -99,14 +111,58 @@ __global__ void __launch_bounds__(256) k_int_peak(uint32_t* sink, uint32_t seed)
   }
 }
 
+// Identities that tie the specialised field routines to the plain multiplication, element by element:
+//   dedicated squaring == a * a,   Euclid inverse == Fermat inverse,   a * a^-1 == 1   (a != 0).
+template <class F>
+__global__ void k_field_check(const uint32_t* __restrict__ in, uint64_t n, uint32_t* __restrict__ bad) {
+  const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const F a = F::load(in + i * F::N);
+  uint32_t fails = 0;
+  if (fe_sqr(a) != fe_mul(a, a)) fails |= 1u;
+  const F inv = fe_inv(a);
+  if (inv != fe_inv_fermat(a)) fails |= 2u;
+  if (!a.is_zero() && fe_mul(a, inv) != F::one()) fails |= 4u;
+  if (a.is_zero() && !inv.is_zero()) fails |= 8u;
+  if (fails) atomicOr(bad, fails);
+}
+
 }  // namespace grape
 
 using namespace grape;
 
+// field: 0 BN254 Fp, 1 BN254 Fr, 2 BLS12-381 Fp, 3 BLS12-381 Fr.  d_elems: n canonical Montgomery elements
+// (8 or 12 limbs each).  *h_fail_mask = OR over the elements of: 1 squaring differs from a*a, 2 the
+// Euclid inverse differs from the Fermat inverse, 4 a * a^-1 != 1, 8 the inverse of 0 is not 0.
+extern "C" int grape_diag_field_check(grape_ctx* ctx, int field, const void* d_elems, uint64_t n,
+                                      uint32_t* h_fail_mask) {
+  if (ctx) grape::make_device_current(ctx);
+  if (!ctx || !h_fail_mask || field < 0 || field > 3 || (!d_elems && n)) return GRAPE_ERR_INVALID;
+  arena_reset(ctx);
+  uint32_t* bad = nullptr;
+  int rc = arena_alloc_t(ctx, 64, &bad);
+  if (rc) return rc;
+  GRAPE_CUDA_TRY(ctx, cudaMemsetAsync(bad, 0, 4, ctx->stream));
+  if (n) {
+    const uint32_t blocks = (uint32_t)((n + 63) / 64);
+    const uint32_t* in = reinterpret_cast<const uint32_t*>(d_elems);
+    if (field == 0) k_field_check<Fp><<<blocks, 64, 0, ctx->stream>>>(in, n, bad);
+    else if (field == 1) k_field_check<Fr><<<blocks, 64, 0, ctx->stream>>>(in, n, bad);
+    else if (field == 2) k_field_check<BlsFp><<<blocks, 64, 0, ctx->stream>>>(in, n, bad);
+    else k_field_check<BlsFr><<<blocks, 64, 0, ctx->stream>>>(in, n, bad);
+    ctx->launches += 1;
+  }
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(h_fail_mask, bad, 4, cudaMemcpyDeviceToHost, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaGetLastError());
+  return GRAPE_OK;
+}
+
 // Writes operations per second: kinds 0-2 count multiply-add instructions (a lo/hi pair counts 2),
 // kind 3 counts field multiplications.
 extern "C" int grape_measure_int_peak(grape_ctx* ctx, int kind, double* ops_per_second) {
-  if (!ctx || !ops_per_second || kind < 0 || kind > 4) return GRAPE_ERR_INVALID;
+  if (ctx) grape::make_device_current(ctx);
+  if (!ctx || !ops_per_second || kind < 0 || kind > 5) return GRAPE_ERR_INVALID;
   arena_reset(ctx);
   uint32_t* sink = nullptr;
   int rc = arena_alloc_t(ctx, 64, &sink);
@@ -122,7 +178,8 @@ extern "C" int grape_measure_int_peak(grape_ctx* ctx, int kind, double* ops_per_
     else if (kind == 1) k_int_peak<1><<<blocks, threads, 0, ctx->stream>>>(sink, rep + 1);
     else if (kind == 2) k_int_peak<2><<<blocks, threads, 0, ctx->stream>>>(sink, rep + 1);
     else if (kind == 3) k_int_peak<3><<<blocks, threads, 0, ctx->stream>>>(sink, rep + 1);
-    else k_int_peak<4><<<blocks, threads, 0, ctx->stream>>>(sink, rep + 1);
+    else if (kind == 4) k_int_peak<4><<<blocks, threads, 0, ctx->stream>>>(sink, rep + 1);
+    else k_int_peak<5><<<blocks, threads, 0, ctx->stream>>>(sink, rep + 1);
     cudaEventRecord(e1, ctx->stream);
     ctx->launches += 1;
     GRAPE_CUDA_TRY(ctx, cudaEventSynchronize(e1));
@@ -136,7 +193,7 @@ extern "C" int grape_measure_int_peak(grape_ctx* ctx, int kind, double* ops_per_
   double per_thread;
   if (kind == 0 || kind == 1) per_thread = (double)PEAK_ITERS * PEAK_CHAINS;
   else if (kind == 2) per_thread = 2.0 * PEAK_ITERS * PEAK_CHAINS;
-  else if (kind == 3) per_thread = 2.0 * (PEAK_ITERS / 8);
+  else if (kind == 3 || kind == 5) per_thread = 2.0 * (PEAK_ITERS / 8);
   else per_thread = 16.0 * (PEAK_ITERS / 64);
   *ops_per_second = per_thread * blocks * threads / (best * 1e-3);
   return GRAPE_OK;
@@ -145,6 +202,7 @@ extern "C" int grape_measure_int_peak(grape_ctx* ctx, int kind, double* ops_per_
 // Mixed XYZZ additions per second on register-resident operands (kind of ceiling for the
 // commitment kernel: same code, same launch bounds, no memory traffic).
 extern "C" int grape_measure_madd_peak(grape_ctx* ctx, double* adds_per_second) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !adds_per_second) return GRAPE_ERR_INVALID;
   arena_reset(ctx);
   uint32_t* buf = nullptr;

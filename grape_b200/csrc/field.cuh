@@ -223,6 +223,121 @@ __device__ __forceinline__ uint32_t sub8(uint32_t (&r)[8], const uint32_t (&a)[8
   return m;
 }
 
+// Shorter rows for the squaring: t[0..2K-1] += {s0..} * b as one carry chain, the carry out of the last
+// limb is added to `top` (the limb that follows the row).
+__device__ __forceinline__ void mad1_top(uint32_t& t0, uint32_t& t1, uint32_t& top, uint32_t s0, uint32_t b) {
+  asm("mad.lo.cc.u32 %0, %3, %4, %0;\n\t"
+      "madc.hi.cc.u32 %1, %3, %4, %1;\n\t"
+      "addc.u32 %2, %2, 0;"
+      : "+r"(t0), "+r"(t1), "+r"(top)
+      : "r"(s0), "r"(b));
+}
+__device__ __forceinline__ void mad2_top(uint32_t& t0, uint32_t& t1, uint32_t& t2, uint32_t& t3, uint32_t& top,
+                                         uint32_t s0, uint32_t s1, uint32_t b) {
+  asm("mad.lo.cc.u32 %0, %5, %7, %0;\n\t"
+      "madc.hi.cc.u32 %1, %5, %7, %1;\n\t"
+      "madc.lo.cc.u32 %2, %6, %7, %2;\n\t"
+      "madc.hi.cc.u32 %3, %6, %7, %3;\n\t"
+      "addc.u32 %4, %4, 0;"
+      : "+r"(t0), "+r"(t1), "+r"(t2), "+r"(t3), "+r"(top)
+      : "r"(s0), "r"(s1), "r"(b));
+}
+__device__ __forceinline__ void mad3_top(uint32_t& t0, uint32_t& t1, uint32_t& t2, uint32_t& t3, uint32_t& t4,
+                                         uint32_t& t5, uint32_t& top, uint32_t s0, uint32_t s1, uint32_t s2,
+                                         uint32_t b) {
+  asm("mad.lo.cc.u32 %0, %7, %10, %0;\n\t"
+      "madc.hi.cc.u32 %1, %7, %10, %1;\n\t"
+      "madc.lo.cc.u32 %2, %8, %10, %2;\n\t"
+      "madc.hi.cc.u32 %3, %8, %10, %3;\n\t"
+      "madc.lo.cc.u32 %4, %9, %10, %4;\n\t"
+      "madc.hi.cc.u32 %5, %9, %10, %5;\n\t"
+      "addc.u32 %6, %6, 0;"
+      : "+r"(t0), "+r"(t1), "+r"(t2), "+r"(t3), "+r"(t4), "+r"(t5), "+r"(top)
+      : "r"(s0), "r"(s1), "r"(s2), "r"(b));
+}
+// t[0..5] = {s0,s1,s2} * b (three adjacent 64-bit products, no carries).
+__device__ __forceinline__ void mul3(uint32_t& t0, uint32_t& t1, uint32_t& t2, uint32_t& t3, uint32_t& t4,
+                                     uint32_t& t5, uint32_t s0, uint32_t s1, uint32_t s2, uint32_t b) {
+  asm("mul.lo.u32 %0, %6, %9;\n\t"
+      "mul.hi.u32 %1, %6, %9;\n\t"
+      "mul.lo.u32 %2, %7, %9;\n\t"
+      "mul.hi.u32 %3, %7, %9;\n\t"
+      "mul.lo.u32 %4, %8, %9;\n\t"
+      "mul.hi.u32 %5, %8, %9;"
+      : "=&r"(t0), "=&r"(t1), "=&r"(t2), "=&r"(t3), "=&r"(t4), "=&r"(t5)
+      : "r"(s0), "r"(s1), "r"(s2), "r"(b));
+}
+// t[0..15] = 2 * d[0..15] + (a_0^2, a_1^2, ..., a_7^2 laid out as eight adjacent 64-bit squares): the
+// doubled off-diagonal part of a square plus its diagonal, one carry chain.  d must be below 2^511.
+__device__ __forceinline__ void sqr_diag8(uint32_t (&t)[16], const uint32_t (&d)[16], const uint32_t (&a)[8]) {
+  uint32_t h[16];
+  h[0] = d[0] << 1;
+#pragma unroll
+  for (int i = 1; i < 16; i++) h[i] = __funnelshift_l(d[i - 1], d[i], 1);
+  asm("mad.lo.cc.u32 %0, %16, %16, %24;\n\t"
+      "madc.hi.cc.u32 %1, %16, %16, %25;\n\t"
+      "madc.lo.cc.u32 %2, %17, %17, %26;\n\t"
+      "madc.hi.cc.u32 %3, %17, %17, %27;\n\t"
+      "madc.lo.cc.u32 %4, %18, %18, %28;\n\t"
+      "madc.hi.cc.u32 %5, %18, %18, %29;\n\t"
+      "madc.lo.cc.u32 %6, %19, %19, %30;\n\t"
+      "madc.hi.cc.u32 %7, %19, %19, %31;\n\t"
+      "madc.lo.cc.u32 %8, %20, %20, %32;\n\t"
+      "madc.hi.cc.u32 %9, %20, %20, %33;\n\t"
+      "madc.lo.cc.u32 %10, %21, %21, %34;\n\t"
+      "madc.hi.cc.u32 %11, %21, %21, %35;\n\t"
+      "madc.lo.cc.u32 %12, %22, %22, %36;\n\t"
+      "madc.hi.cc.u32 %13, %22, %22, %37;\n\t"
+      "madc.lo.cc.u32 %14, %23, %23, %38;\n\t"
+      "madc.hi.u32 %15, %23, %23, %39;"
+      : "=&r"(t[0]), "=&r"(t[1]), "=&r"(t[2]), "=&r"(t[3]), "=&r"(t[4]), "=&r"(t[5]), "=&r"(t[6]), "=&r"(t[7]),
+        "=&r"(t[8]), "=&r"(t[9]), "=&r"(t[10]), "=&r"(t[11]), "=&r"(t[12]), "=&r"(t[13]), "=&r"(t[14]), "=&r"(t[15])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]),
+        "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]), "r"(h[4]), "r"(h[5]), "r"(h[6]), "r"(h[7]),
+        "r"(h[8]), "r"(h[9]), "r"(h[10]), "r"(h[11]), "r"(h[12]), "r"(h[13]), "r"(h[14]), "r"(h[15]));
+}
+// r[0..14] = a[0..14] + b[0..14] (the two off-diagonal accumulators of a square; the sum is below 2^480).
+__device__ __forceinline__ void add15(uint32_t (&r)[16], const uint32_t (&a)[16], const uint32_t (&b)[16]) {
+  asm("add.cc.u32 %0, %15, %30;\n\t"
+      "addc.cc.u32 %1, %16, %31;\n\t"
+      "addc.cc.u32 %2, %17, %32;\n\t"
+      "addc.cc.u32 %3, %18, %33;\n\t"
+      "addc.cc.u32 %4, %19, %34;\n\t"
+      "addc.cc.u32 %5, %20, %35;\n\t"
+      "addc.cc.u32 %6, %21, %36;\n\t"
+      "addc.cc.u32 %7, %22, %37;\n\t"
+      "addc.cc.u32 %8, %23, %38;\n\t"
+      "addc.cc.u32 %9, %24, %39;\n\t"
+      "addc.cc.u32 %10, %25, %40;\n\t"
+      "addc.cc.u32 %11, %26, %41;\n\t"
+      "addc.cc.u32 %12, %27, %42;\n\t"
+      "addc.cc.u32 %13, %28, %43;\n\t"
+      "addc.u32 %14, %29, %44;"
+      : "=&r"(r[1]), "=&r"(r[2]), "=&r"(r[3]), "=&r"(r[4]), "=&r"(r[5]), "=&r"(r[6]), "=&r"(r[7]), "=&r"(r[8]),
+        "=&r"(r[9]), "=&r"(r[10]), "=&r"(r[11]), "=&r"(r[12]), "=&r"(r[13]), "=&r"(r[14]), "=&r"(r[15])
+      : "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(a[4]), "r"(a[5]), "r"(a[6]), "r"(a[7]), "r"(a[8]), "r"(a[9]),
+        "r"(a[10]), "r"(a[11]), "r"(a[12]), "r"(a[13]), "r"(a[14]), "r"(a[15]),
+        "r"(b[1]), "r"(b[2]), "r"(b[3]), "r"(b[4]), "r"(b[5]), "r"(b[6]), "r"(b[7]), "r"(b[8]), "r"(b[9]),
+        "r"(b[10]), "r"(b[11]), "r"(b[12]), "r"(b[13]), "r"(b[14]), "r"(b[15]));
+  r[0] = 0;
+}
+// The division by 2^32 between two reduction steps when no new products come in:
+//   lo0 += e[1];  n[k] = e[k+2] + carry  (e[8], e[9] read as zero)
+__device__ __forceinline__ void shift_only8(uint32_t (&n)[8], uint32_t& lo0, const uint32_t (&e)[8]) {
+  asm("add.cc.u32 %8, %8, %9;\n\t"
+      "addc.cc.u32 %0, %10, 0;\n\t"
+      "addc.cc.u32 %1, %11, 0;\n\t"
+      "addc.cc.u32 %2, %12, 0;\n\t"
+      "addc.cc.u32 %3, %13, 0;\n\t"
+      "addc.cc.u32 %4, %14, 0;\n\t"
+      "addc.cc.u32 %5, %15, 0;\n\t"
+      "addc.u32 %6, 0, 0;\n\t"
+      "mov.u32 %7, 0;"
+      : "=&r"(n[0]), "=&r"(n[1]), "=&r"(n[2]), "=&r"(n[3]), "=&r"(n[4]), "=&r"(n[5]), "=&r"(n[6]), "=&r"(n[7]),
+        "+r"(lo0)
+      : "r"(e[1]), "r"(e[2]), "r"(e[3]), "r"(e[4]), "r"(e[5]), "r"(e[6]), "r"(e[7]));
+}
+
 // Twelve-limb counterparts of the helpers above (six products per chain).
 __device__ __forceinline__ void mul6(uint32_t (&t)[12], uint32_t s0, uint32_t s1, uint32_t s2,
                                      uint32_t s3, uint32_t s4, uint32_t s5, uint32_t b) {
@@ -563,8 +678,79 @@ __device__ GRAPE_MUL_ATTR Fe<P> fe_mul(const Fe<P>& a, const Fe<P>& b) {
   return mont_finish<P>(E, O);
 }
 
+// r = a * a / 2^256 mod m for the eight-limb fields (reference: the dedicated squaring of
+// include/field/mont_t.cuh:145-192).  The 28 off-diagonal limb products are formed once (rows of
+// products whose low word lands on an even limb go to one accumulator, odd to another), doubled, and
+// the 8 diagonal squares are added: 36 wide multiply-adds instead of 64.  The low half of the 512-bit
+// square is then reduced by the eight steps the multiplication uses and the high half is added on:
+//   (T + m p) / 2^256 = T_hi + (T_lo + m p) / 2^256 < 2 p.
 template <class P>
-__device__ __forceinline__ Fe<P> fe_sqr(const Fe<P>& a) { return fe_mul(a, a); }
+__device__ GRAPE_MUL_ATTR Fe<P> fe_sqr8(const Fe<P>& x) {
+  static_assert(P::LIMBS == 8, "eight-limb fields only");
+  const uint32_t (&a)[8] = x.v;
+  uint32_t Ea[16], Oa[16];
+#pragma unroll
+  for (int i = 0; i < 16; i++) { Ea[i] = 0; Oa[i] = 0; }
+  mul3(Ea[2], Ea[3], Ea[4], Ea[5], Ea[6], Ea[7], a[2], a[4], a[6], a[0]);
+  mad3_top(Ea[4], Ea[5], Ea[6], Ea[7], Ea[8], Ea[9], Ea[10], a[3], a[5], a[7], a[1]);
+  mad2_top(Ea[6], Ea[7], Ea[8], Ea[9], Ea[10], a[4], a[6], a[2]);
+  mad2_top(Ea[8], Ea[9], Ea[10], Ea[11], Ea[12], a[5], a[7], a[3]);
+  mad1_top(Ea[10], Ea[11], Ea[12], a[6], a[4]);
+  mad1_top(Ea[12], Ea[13], Ea[14], a[7], a[5]);
+  {
+    uint32_t t[8];
+    mul4(t, a[1], a[3], a[5], a[7], a[0]);
+#pragma unroll
+    for (int i = 0; i < 8; i++) Oa[1 + i] = t[i];
+  }
+  mad3_top(Oa[3], Oa[4], Oa[5], Oa[6], Oa[7], Oa[8], Oa[9], a[2], a[4], a[6], a[1]);
+  mad3_top(Oa[5], Oa[6], Oa[7], Oa[8], Oa[9], Oa[10], Oa[11], a[3], a[5], a[7], a[2]);
+  mad2_top(Oa[7], Oa[8], Oa[9], Oa[10], Oa[11], a[4], a[6], a[3]);
+  mad2_top(Oa[9], Oa[10], Oa[11], Oa[12], Oa[13], a[5], a[7], a[4]);
+  mad1_top(Oa[11], Oa[12], Oa[13], a[6], a[5]);
+  mad1_top(Oa[13], Oa[14], Oa[15], a[7], a[6]);
+  uint32_t D[16], T[16];
+  add15(D, Ea, Oa);
+  sqr_diag8(T, D, a);
+  uint32_t E[8], O[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) { E[i] = T[i]; O[i] = 0; }
+  redc_step<P>(E, O);
+#pragma unroll
+  for (int i = 1; i < 8; i++) {
+    uint32_t Nx[8];
+    shift_only8(Nx, O[0], E);
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+      E[k] = O[k];
+      O[k] = Nx[k];
+    }
+    redc_step<P>(E, O);
+  }
+  uint32_t hi[8], s[8], s2[8], t[8], m[8];
+#pragma unroll
+  for (int i = 0; i < 7; i++) hi[i] = E[i + 1];
+  hi[7] = 0;
+  add8(s, hi, O);
+#pragma unroll
+  for (int i = 0; i < 8; i++) hi[i] = T[8 + i];
+  add8(s2, s, hi);  // below 2 p < 2^255: no carry out
+  Fe<P>::mod_limbs(m);
+  uint32_t borrow = sub8(t, s2, m);
+  Fe<P> r;
+#pragma unroll
+  for (int i = 0; i < 8; i++) r.v[i] = borrow ? s2[i] : t[i];
+  return r;
+}
+
+template <class P>
+__device__ __forceinline__ Fe<P> fe_sqr(const Fe<P>& a) {
+#ifndef GRAPE_NO_DEDICATED_SQR
+  if constexpr (P::LIMBS == 8) return fe_sqr8(a);
+  else
+#endif
+    return fe_mul(a, a);
+}
 
 // Leave Montgomery form: a / 2^(32 N) mod m (N reduction steps on the bare value).
 template <class P>
@@ -592,14 +778,23 @@ __device__ __forceinline__ Fe<P> fe_from_mont(const Fe<P>& a) {
 template <class P>
 __device__ __forceinline__ Fe<P> fe_to_mont(const Fe<P>& a) { return fe_mul(a, Fe<P>::r2()); }
 
-// a^(m-2) by square-and-multiply over the constant exponent (a = 0 maps to 0).
+// a^(m-2) by square-and-multiply over the constant exponent (a = 0 maps to 0): about 1.5 * bits
+// dependent multiplications.  Kept as the cross-check of fe_inv below.
 template <class P>
-__device__ __noinline__ Fe<P> fe_inv(const Fe<P>& a) {
+__device__ __noinline__ Fe<P> fe_inv_fermat(const Fe<P>& a) {
   constexpr int N = P::LIMBS;
   uint32_t e[N];
 #pragma unroll
   for (int i = 0; i < N; i++) e[i] = P::mod(i);
-  e[0] -= 2;  // MOD[0] >= 2 for every field here, no borrow
+  // exponent m - 2, with the borrow carried (the low limb of the BLS12-381 scalar modulus is 1)
+  uint32_t borrow = e[0] < 2u ? 1u : 0u;
+  e[0] -= 2u;
+#pragma unroll
+  for (int i = 1; i < N; i++) {
+    const uint32_t b = (e[i] < borrow) ? 1u : 0u;
+    e[i] -= borrow;
+    borrow = b;
+  }
   Fe<P> acc = Fe<P>::one();
   for (int w = N - 1; w >= 0; w--) {
     uint32_t word = e[w];
@@ -609,6 +804,114 @@ __device__ __noinline__ Fe<P> fe_inv(const Fe<P>& a) {
     }
   }
   return acc;
+}
+
+// v >>= z over N limbs, 0 <= z <= 31
+template <int N>
+__device__ __forceinline__ void shr_var(uint32_t (&v)[N], uint32_t z) {
+#pragma unroll
+  for (int i = 0; i < N - 1; i++) v[i] = __funnelshift_r(v[i], v[i + 1], z);
+  v[N - 1] >>= z;
+}
+// v <<= z over N limbs, 0 <= z <= 31 (the bits shifted out must be clear)
+template <int N>
+__device__ __forceinline__ void shl_var(uint32_t (&v)[N], uint32_t z) {
+#pragma unroll
+  for (int i = N - 1; i > 0; i--) v[i] = __funnelshift_l(v[i - 1], v[i], z);
+  v[0] <<= z;
+}
+// trailing zeros of the low limb, at most 31 (an all-zero low limb counts as 31: the caller shifts again)
+__device__ __forceinline__ uint32_t ctz_cap31(uint32_t lo) {
+  return lo ? min((uint32_t)(__ffs((int)lo) - 1), 31u) : 31u;
+}
+
+// Montgomery inverse: for a = x * 2^(32 N) mod m returns x^-1 * 2^(32 N) mod m; 0 maps to 0.
+// Binary extended Euclid in Kaliski's "almost inverse" form on (u, v, r, s) = (m, a, 0, 1): while both
+// u and v are odd the smaller is subtracted from the larger, the companion pair gets r + s, and ALL
+// the factors of two of the difference are shifted out at once (the companion of the other side is
+// shifted up by as many bits), k counting the shifts.  The loop leaves r = -a^-1 * 2^k mod m with
+// k in [bits, 2 bits], and two Montgomery products by powers of two take the 2^k out.  About 0.7
+// iterations per bit, each a few add / shift chains on the plain integers with both outcomes of the
+// comparison computed side by side and selected (no divergence inside a warp except at the exit):
+// roughly a tenth of the dependent-instruction latency of the Fermat ladder.  The reference inverts
+// with a Euclid as well (include/field/mont_t.cuh:1058-1120).
+template <class P>
+__device__ __noinline__ Fe<P> fe_inv(const Fe<P>& a) {
+  constexpr int N = P::LIMBS;
+  if (a.is_zero()) return a;
+  uint32_t u[N], v[N], r[N], s[N];
+#pragma unroll
+  for (int i = 0; i < N; i++) { u[i] = P::mod(i); v[i] = a.v[i]; r[i] = 0; s[i] = 0; }
+  s[0] = 1;
+  uint32_t k = 0;
+  for (;;) {
+    if ((u[0] & 1u) == 0) {  // only after a shift that was cut at 31 bits
+      const uint32_t z = ctz_cap31(u[0]);
+      shr_var<N>(u, z);
+      shl_var<N>(s, z);
+      k += z;
+      continue;
+    }
+    if ((v[0] & 1u) == 0) {  // an even input, or after a shift that was cut at 31 bits (v is never 0 here)
+      const uint32_t z = ctz_cap31(v[0]);
+      shr_var<N>(v, z);
+      shl_var<N>(r, z);
+      k += z;
+      continue;
+    }
+    uint32_t d1[N], d2[N], t[N];
+    const uint32_t lt = subn(d1, u, v);  // all ones when u < v
+    subn(d2, v, u);
+    addn(t, r, s);
+    uint32_t ad[N], nz = 0;
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+      ad[i] = lt ? d2[i] : d1[i];  // |u - v|, even
+      nz |= ad[i];
+    }
+    if (nz == 0) {  // u == v == gcd = 1: the closing step v = 0, s += r, r *= 2
+#pragma unroll
+      for (int i = 0; i < N; i++) s[i] = t[i];
+      shl_var<N>(r, 1);
+      k += 1;
+      break;
+    }
+    const uint32_t z = ctz_cap31(ad[0]);
+    shr_var<N>(ad, z);
+    uint32_t big[N];
+#pragma unroll
+    for (int i = 0; i < N; i++) big[i] = lt ? r[i] : s[i];
+    shl_var<N>(big, z);
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+      u[i] = lt ? u[i] : ad[i];
+      v[i] = lt ? ad[i] : v[i];
+      r[i] = lt ? big[i] : t[i];
+      s[i] = lt ? t[i] : big[i];
+    }
+    k += z;
+  }
+  // r < 2 m holds -a^-1 * 2^k: bring it below m and negate
+  uint32_t m[N], t[N];
+  Fe<P>::mod_limbs(m);
+  uint32_t borrow = subn(t, r, m);
+  Fe<P> x;
+#pragma unroll
+  for (int i = 0; i < N; i++) x.v[i] = borrow ? r[i] : t[i];
+  x = fe_neg(x);
+  // x = a^-1 * 2^k.  The result is a^-1 * 2^(64 N):  x * 2^(32 N) by a product with R^2, then
+  // * 2^(32 N - k) by a product with the plain power of two 2^(64 N - k) (kept below 2^(32 N - 2):
+  // the few excess doublings of a very short run are done modularly).
+  x = fe_mul(x, Fe<P>::r2());
+  uint32_t j = 64u * N - k;
+  while (j > 32u * N - 2u) {
+    x = fe_dbl(x);
+    j--;
+  }
+  Fe<P> pw = Fe<P>::zero();
+#pragma unroll
+  for (int i = 0; i < N; i++) pw.v[i] = ((j >> 5) == (uint32_t)i) ? (1u << (j & 31u)) : 0u;
+  return fe_mul(x, pw);
 }
 
 // Signed 32-bit integer -> Montgomery residue; negatives map to m - |x|

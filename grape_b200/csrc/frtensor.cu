@@ -182,7 +182,8 @@ struct WideAcc {
   }
   // The accumulated integer V = E + (O << 32) (320 bits) as the residue V mod r.  Because the
   // weights are Montgomery residues and the integers are plain, V mod r IS the Montgomery form of
-  // the weighted sum.  V is cut into 128-bit pieces that are recombined by Horner in the field.
+  // the weighted sum.  V = V_a + 2^224 * V_b with V_a < 2^224 < r and V_b < 2^96, and
+  // 2^224 * V_b mod r is ONE Montgomery product of V_b with the constant 2^480 mod r.
   __device__ __forceinline__ Fr to_fr() const {
     uint32_t L[10];
     uint64_t carry = 0;
@@ -196,19 +197,17 @@ struct WideAcc {
     uint64_t s8 = (uint64_t)Et + O[7] + carry;
     L[8] = (uint32_t)s8;
     L[9] = Ot + (uint32_t)(s8 >> 32);
-    const uint32_t t128[8] = {0xef8cfeb9u, 0xb075da81u, 0xa5b6cd8cu, 0xa7f12accu,
-                              0x7957bf7bu, 0x32c47504u, 0x48ffa25eu, 0x03d581d7u};  // 2^128 in Montgomery form
-    Fr T, c2 = Fr::zero(), c1 = Fr::zero(), c0 = Fr::zero();
+    const uint32_t t480[8] = {0x8f8fc595u, 0x41a9cbe4u, 0x0a58dc0fu, 0x9f36d601u,
+                              0x440ad260u, 0xa6132126u, 0x093f81ddu, 0x2ab23b99u};  // 2^480 mod r
+    Fr T, va = Fr::zero(), vb = Fr::zero();
 #pragma unroll
-    for (int k = 0; k < 8; k++) T.v[k] = t128[k];
-    c2.v[0] = L[8];
-    c2.v[1] = L[9];
+    for (int k = 0; k < 8; k++) T.v[k] = t480[k];
 #pragma unroll
-    for (int k = 0; k < 4; k++) { c1.v[k] = L[4 + k]; c0.v[k] = L[k]; }
-    Fr acc = fe_to_mont(c2);
-    acc = fe_add(fe_mul(acc, T), fe_to_mont(c1));
-    acc = fe_add(fe_mul(acc, T), fe_to_mont(c0));
-    return fe_from_mont(acc);
+    for (int k = 0; k < 7; k++) va.v[k] = L[k];
+    vb.v[0] = L[7];
+    vb.v[1] = L[8];
+    vb.v[2] = L[9];
+    return fe_add(va, fe_mul(vb, T));
   }
 };
 
@@ -288,6 +287,157 @@ k_fold_axis(const void* __restrict__ t, const uint32_t* __restrict__ w, uint32_t
     }
   }
   acc.store(dst + ((uint64_t)blockIdx.y * n_out + og) * 8);
+}
+
+// ---- int32-source fold staged through shared memory -------------------------------------------
+// One block folds a tile of ST_COLS adjacent output columns over a slice of rows.  Rows arrive in
+// shared memory by bulk asynchronous copies (cp.async.bulk, one per row chunk, completion counted on
+// an mbarrier per stage), ST_STAGES stages of ST_ROWS rows deep, issued by one thread: the copies of
+// a block stay in flight while all of its threads multiply, independent of how the compiler
+// schedules loads, and a row chunk is one contiguous request.  The eq-weights of the stage's rows
+// ride along in the same stage.  Every lane owns CPT adjacent columns (one 16-, 8- or 4-byte read of
+// shared memory per row) and CPT wide accumulators.
+// Every wait on an mbarrier is bounded: a lane that gives up sets STATUS_PIPE_TIMEOUT in the status
+// word and the block leaves after a bounded wait for the copies it still has in flight.
+constexpr int ST_ROWS = 8;
+constexpr int ST_STAGES = 4;
+constexpr uint32_t ST_SPIN_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// false when the barrier did not complete the phase within the spin limit
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  for (uint32_t spin = 0; spin < ST_SPIN_LIMIT; spin++) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  return false;
+}
+// global -> shared bulk copy of `bytes` (a multiple of 16, both addresses 16-byte aligned) of this GPU's own memory
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst_smem)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+template <int CPT>
+struct StageLayout {
+  static constexpr int COLS = CPT * FOLD_THREADS;
+  static constexpr int ROW_BYTES = COLS * 4;
+  static constexpr int DATA_BYTES = ST_ROWS * ROW_BYTES;
+  static constexpr int W_BYTES = ST_ROWS * 32;
+  static constexpr int STAGE_BYTES = DATA_BYTES + W_BYTES;
+  static constexpr int SMEM_BYTES = ST_STAGES * STAGE_BYTES + ST_STAGES * 8;
+};
+
+template <int CPT>
+__global__ void __launch_bounds__(FOLD_THREADS)
+k_fold_axis_i32_staged(const int32_t* __restrict__ t, const uint32_t* __restrict__ w, uint32_t c, uint64_t gap,
+                       uint64_t n_out, uint32_t slice_len, uint32_t* __restrict__ dst, const uint32_t* __restrict__ corr,
+                       uint32_t* __restrict__ status) {
+  using L = StageLayout<CPT>;
+  extern __shared__ __align__(128) unsigned char st_smem[];
+  uint64_t* full = reinterpret_cast<uint64_t*>(st_smem + ST_STAGES * L::STAGE_BYTES);
+  const uint32_t tid = threadIdx.x;
+  const uint64_t tiles_per_o = gap / L::COLS;
+  const uint64_t o = blockIdx.x / tiles_per_o;
+  const uint64_t g0 = (blockIdx.x % tiles_per_o) * L::COLS;
+  const uint32_t j0 = blockIdx.y * slice_len;
+  const uint32_t j1 = min(c, j0 + slice_len);
+  const uint32_t n_rows = j1 > j0 ? j1 - j0 : 0;
+  const uint32_t n_iter = (n_rows + ST_ROWS - 1) / ST_ROWS;
+  const int32_t* src0 = t + (o * c + j0) * gap + g0;  // row j0 of this tile
+  const uint32_t* w0 = w + (uint64_t)j0 * 8;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < ST_STAGES; s++) mbar_init(full + s, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  auto issue = [&](uint32_t it) {  // thread 0: fill stage it % ST_STAGES with rows it*ST_ROWS ...
+    const uint32_t s = it % ST_STAGES;
+    const uint32_t r0 = it * ST_ROWS;
+    const uint32_t rows = min((uint32_t)ST_ROWS, n_rows - r0);
+    unsigned char* base = st_smem + s * L::STAGE_BYTES;
+    mbar_expect_tx(full + s, rows * (L::ROW_BYTES + 32));
+    for (uint32_t r = 0; r < rows; r++)
+      bulk_g2s(base + r * L::ROW_BYTES, src0 + (uint64_t)(r0 + r) * gap, L::ROW_BYTES, full + s);
+    bulk_g2s(base + L::DATA_BYTES, w0 + (uint64_t)r0 * 8, rows * 32, full + s);
+  };
+  uint32_t issued = 0;
+  if (tid == 0) {
+    for (; issued < n_iter && issued < ST_STAGES; issued++) issue(issued);
+  }
+
+  WideAcc acc[CPT];
+#pragma unroll
+  for (int q = 0; q < CPT; q++) acc[q].clear();
+  bool ok = true;
+  for (uint32_t it = 0; it < n_iter; it++) {
+    const uint32_t s = it % ST_STAGES;
+    // the block decides together: a lane that ran out of patience must not leave the others at the
+    // barrier below
+    if (!__syncthreads_and(mbar_wait_bounded(full + s, (it / ST_STAGES) & 1u))) {
+      ok = false;
+      break;
+    }
+    const unsigned char* base = st_smem + s * L::STAGE_BYTES;
+    const uint32_t rows = min((uint32_t)ST_ROWS, n_rows - it * ST_ROWS);
+#pragma unroll 2
+    for (uint32_t r = 0; r < rows; r++) {
+      const Fr wk = Fr::load(base + L::DATA_BYTES + r * 32);
+      const uint32_t* xr = reinterpret_cast<const uint32_t*>(base + r * L::ROW_BYTES) + tid * CPT;
+      if (CPT == 4) {
+        const uint4 x = *reinterpret_cast<const uint4*>(xr);
+        acc[0].mac(wk, x.x ^ 0x80000000u);
+        acc[1 % CPT].mac(wk, x.y ^ 0x80000000u);
+        acc[2 % CPT].mac(wk, x.z ^ 0x80000000u);
+        acc[3 % CPT].mac(wk, x.w ^ 0x80000000u);
+      } else if (CPT == 2) {
+        const uint2 x = *reinterpret_cast<const uint2*>(xr);
+        acc[0].mac(wk, x.x ^ 0x80000000u);
+        acc[1 % CPT].mac(wk, x.y ^ 0x80000000u);
+      } else {
+        acc[0].mac(wk, xr[0] ^ 0x80000000u);
+      }
+    }
+    __syncthreads();  // every lane is done with stage s before it is refilled
+    if (tid == 0 && issued < n_iter) issue(issued++);
+  }
+  if (!ok) {
+    // a copy never completed: report, give the copies still in flight a bounded time to land, leave
+    if (tid == 0) {
+      atomicOr(status, STATUS_PIPE_TIMEOUT);
+      for (int s = 0; s < ST_STAGES; s++) {
+        mbar_wait_bounded(full + s, 0);
+        mbar_wait_bounded(full + s, 1);
+      }
+    }
+    return;
+  }
+  const Fr cr = Fr::load_nc(corr + (uint64_t)blockIdx.y * 8);
+  const uint64_t og = o * gap + g0 + (uint64_t)tid * CPT;
+  uint32_t* d = dst + ((uint64_t)blockIdx.y * n_out + og) * 8;
+#pragma unroll
+  for (int q = 0; q < CPT; q++) fe_sub(acc[q].to_fr(), cr).store(d + q * 8);
 }
 
 // out[i] = sum_s partial[s][i]
@@ -386,10 +536,20 @@ int fold_axis_async(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* 
     }
   }
   // work area: eq weights (c) + slice partials
+  // staged kernel: int32 source, tensor 16-byte aligned, the tile width (512, 256 or 128 columns) divides gap
+  int cpt = 0;
+  if (FROM_I32 && gap > 1 && (reinterpret_cast<uintptr_t>(d_t) & 15) == 0) {
+    if (gap % (4 * FOLD_THREADS) == 0) cpt = 4;
+    else if (gap % (2 * FOLD_THREADS) == 0) cpt = 2;
+    else if (gap % FOLD_THREADS == 0 && gap % 4 == 0) cpt = 1;
+  }
+  const uint64_t n_threads = cpt ? n_out / cpt : n_out;
   uint32_t n_slices = 1;
   if (gap > 1) {
-    uint64_t out_blocks = (n_out + FOLD_THREADS - 1) / FOLD_THREADS;
-    uint64_t target = (uint64_t)ctx->sm_count * 8;
+    uint64_t out_blocks = (n_threads + FOLD_THREADS - 1) / FOLD_THREADS;
+    // staged blocks hold 64 KB of shared memory: three per SM, two waves of them; the plain kernel
+    // runs eight blocks per SM
+    uint64_t target = (uint64_t)ctx->sm_count * (cpt ? 6 : 8);
     if (out_blocks < target) n_slices = (uint32_t)std::min<uint64_t>((target + out_blocks - 1) / out_blocks, (c + 15) / 16);
     if (n_slices < 1) n_slices = 1;
   }
@@ -415,11 +575,27 @@ int fold_axis_async(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* 
     k_fold_inner<FROM_I32><<<(uint32_t)other, SUM_THREADS, 0, ctx->stream>>>(d_t, w, c, (uint32_t*)d_out, corr);
     ctx->launches += 1;
   } else {
-    dim3 grid((uint32_t)((n_out + FOLD_THREADS - 1) / FOLD_THREADS), n_slices);
+    dim3 grid((uint32_t)((n_threads + FOLD_THREADS - 1) / FOLD_THREADS), n_slices);
     uint32_t* fold_dst = n_slices > 1 ? partial : (uint32_t*)d_out;
     {
       ProfScope prof(ctx);
-      k_fold_axis<FROM_I32><<<grid, FOLD_THREADS, 0, ctx->stream>>>(d_t, w, c, gap, n_out, slice_len, fold_dst, corr);
+      const int32_t* ti = reinterpret_cast<const int32_t*>(d_t);
+      if (cpt == 4) {
+        GRAPE_CUDA_TRY(ctx, cudaFuncSetAttribute(k_fold_axis_i32_staged<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 StageLayout<4>::SMEM_BYTES));
+        k_fold_axis_i32_staged<4><<<grid, FOLD_THREADS, StageLayout<4>::SMEM_BYTES, ctx->stream>>>(
+            ti, w, c, gap, n_out, slice_len, fold_dst, corr, ctx->d_status);
+      } else if (cpt == 2) {
+        GRAPE_CUDA_TRY(ctx, cudaFuncSetAttribute(k_fold_axis_i32_staged<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 StageLayout<2>::SMEM_BYTES));
+        k_fold_axis_i32_staged<2><<<grid, FOLD_THREADS, StageLayout<2>::SMEM_BYTES, ctx->stream>>>(
+            ti, w, c, gap, n_out, slice_len, fold_dst, corr, ctx->d_status);
+      } else if (cpt == 1) {
+        k_fold_axis_i32_staged<1><<<grid, FOLD_THREADS, StageLayout<1>::SMEM_BYTES, ctx->stream>>>(
+            ti, w, c, gap, n_out, slice_len, fold_dst, corr, ctx->d_status);
+      } else {
+        k_fold_axis<FROM_I32><<<grid, FOLD_THREADS, 0, ctx->stream>>>(d_t, w, c, gap, n_out, slice_len, fold_dst, corr);
+      }
     }
     ctx->launches += 1;
     if (n_slices > 1) {
@@ -442,42 +618,49 @@ using namespace grape;
 #define LAUNCH_DONE(ctx, k) do { (ctx)->launches += (k); GRAPE_CUDA_TRY((ctx), cudaGetLastError()); return GRAPE_OK; } while (0)
 
 extern "C" int grape_fr_from_i32(grape_ctx* ctx, const int32_t* d_in, void* d_out, uint64_t n) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   if (n == 0) return GRAPE_OK;
   k_from_i32<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>(d_in, (uint32_t*)d_out, n);
   LAUNCH_DONE(ctx, 1);
 }
 extern "C" int grape_fr_from_u32(grape_ctx* ctx, const uint32_t* d_in, void* d_out, uint64_t n) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   if (n == 0) return GRAPE_OK;
   k_from_u32<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>(d_in, (uint32_t*)d_out, n);
   LAUNCH_DONE(ctx, 1);
 }
 extern "C" int grape_fr_to_mont(grape_ctx* ctx, void* d_t, uint64_t n) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   if (n == 0) return GRAPE_OK;
   k_to_mont<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>((uint32_t*)d_t, n);
   LAUNCH_DONE(ctx, 1);
 }
 extern "C" int grape_fr_from_mont(grape_ctx* ctx, void* d_t, uint64_t n) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   if (n == 0) return GRAPE_OK;
   k_from_mont<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>((uint32_t*)d_t, n);
   LAUNCH_DONE(ctx, 1);
 }
 extern "C" int grape_fr_add(grape_ctx* ctx, const void* d_a, const void* d_b, void* d_out, uint64_t n) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   if (n == 0) return GRAPE_OK;
   k_binary<0, Fr><<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_a, (const uint32_t*)d_b, (uint32_t*)d_out, n);
   LAUNCH_DONE(ctx, 1);
 }
 extern "C" int grape_fr_sub(grape_ctx* ctx, const void* d_a, const void* d_b, void* d_out, uint64_t n) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   if (n == 0) return GRAPE_OK;
   k_binary<1, Fr><<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_a, (const uint32_t*)d_b, (uint32_t*)d_out, n);
   LAUNCH_DONE(ctx, 1);
 }
 extern "C" int grape_fr_mul(grape_ctx* ctx, const void* d_a, const void* d_b, void* d_out, uint64_t n) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   if (n == 0) return GRAPE_OK;
   k_binary<2, Fr><<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_a, (const uint32_t*)d_b, (uint32_t*)d_out, n);
@@ -485,6 +668,7 @@ extern "C" int grape_fr_mul(grape_ctx* ctx, const void* d_a, const void* d_b, vo
 }
 // Diagnostics: the same three operations over the base field Fp (used by the curve arithmetic).
 extern "C" int grape_fp_binary(grape_ctx* ctx, int op, const void* d_a, const void* d_b, void* d_out, uint64_t n) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   if (n == 0) return GRAPE_OK;
   uint32_t g = ew_blocks(ctx, n);
@@ -495,18 +679,21 @@ extern "C" int grape_fp_binary(grape_ctx* ctx, int op, const void* d_a, const vo
   LAUNCH_DONE(ctx, 1);
 }
 extern "C" int grape_fr_scale(grape_ctx* ctx, const void* d_a, const void* d_scalar, void* d_out, uint64_t n) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   if (n == 0) return GRAPE_OK;
   k_broadcast<1><<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_a, (const uint32_t*)d_scalar, (uint32_t*)d_out, n);
   LAUNCH_DONE(ctx, 1);
 }
 extern "C" int grape_fr_add_scalar(grape_ctx* ctx, const void* d_a, const void* d_scalar, void* d_out, uint64_t n) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   if (n == 0) return GRAPE_OK;
   k_broadcast<0><<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_a, (const uint32_t*)d_scalar, (uint32_t*)d_out, n);
   LAUNCH_DONE(ctx, 1);
 }
 extern "C" int grape_fr_axpy(grape_ctx* ctx, const void* d_a, const void* d_scalar, const void* d_b, void* d_out, uint64_t n) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   if (n == 0) return GRAPE_OK;
   k_axpy<<<ew_blocks(ctx, n), EW_THREADS, 0, ctx->stream>>>((const uint32_t*)d_a, (const uint32_t*)d_scalar, (const uint32_t*)d_b, (uint32_t*)d_out, n);
@@ -531,11 +718,13 @@ int fr_inverse_async(grape_ctx* ctx, const void* d_in, const void* d_shift, void
 }
 }  // namespace grape
 extern "C" int grape_fr_inverse(grape_ctx* ctx, const void* d_in, const void* d_shift, void* d_out, uint64_t n) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   arena_reset(ctx);
   return fr_inverse_async(ctx, d_in, d_shift, d_out, n);
 }
 extern "C" int grape_pad_i32(grape_ctx* ctx, const int32_t* d_in, int32_t* d_out, uint32_t n, uint32_t pad_n, uint64_t pad_size) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   if (pad_size == 0) return GRAPE_OK;
   if (n == 0 || pad_n < n) return fail(ctx, GRAPE_ERR_INVALID, "pad: need 0 < n <= pad_n");
@@ -543,6 +732,7 @@ extern "C" int grape_pad_i32(grape_ctx* ctx, const int32_t* d_in, int32_t* d_out
   LAUNCH_DONE(ctx, 1);
 }
 extern "C" int grape_fr_pad(grape_ctx* ctx, const void* d_in, void* d_out, uint32_t n, uint32_t pad_n, uint64_t pad_size, const void* d_pad_value) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   if (pad_size == 0) return GRAPE_OK;
   if (n == 0 || pad_n < n) return fail(ctx, GRAPE_ERR_INVALID, "pad: need 0 < n <= pad_n");
@@ -550,12 +740,14 @@ extern "C" int grape_fr_pad(grape_ctx* ctx, const void* d_in, void* d_out, uint3
   LAUNCH_DONE(ctx, 1);
 }
 extern "C" int grape_fr_sum(grape_ctx* ctx, const void* d_in, uint64_t n, void* d_out) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   if (n == 0) return grape_dev_zero(ctx, d_out, 32);
   arena_reset(ctx);
   return fr_sum_async(ctx, d_in, n, d_out);
 }
 extern "C" int grape_fr_rowsum(grape_ctx* ctx, const void* d_in, void* d_out, uint64_t rows, uint32_t dim) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   if (rows == 0 || dim == 0) return GRAPE_OK;
   uint64_t threads = rows * 32;
@@ -564,12 +756,14 @@ extern "C" int grape_fr_rowsum(grape_ctx* ctx, const void* d_in, void* d_out, ui
   LAUNCH_DONE(ctx, 1);
 }
 extern "C" int grape_fr_fold(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* d_x, uint32_t c, uint64_t gap, void* d_out) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   if (c == 0 || gap == 0) return fail(ctx, GRAPE_ERR_INVALID, "fold: c and gap must be positive");
   arena_reset(ctx);
   return fold_axis_async<false>(ctx, d_t, ntot, d_x, c, gap, d_out);
 }
 extern "C" int grape_fold_i32(grape_ctx* ctx, const int32_t* d_t, uint64_t ntot, const void* d_x, uint32_t c, uint64_t gap, void* d_out) {
+  if (ctx) grape::make_device_current(ctx);
   CHECK_CTX(ctx);
   if (c == 0 || gap == 0) return fail(ctx, GRAPE_ERR_INVALID, "fold: c and gap must be positive");
   arena_reset(ctx);

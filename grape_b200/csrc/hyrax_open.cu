@@ -53,6 +53,29 @@ __global__ void k_rng_fr(uint64_t state0, uint64_t n, uint32_t* __restrict__ out
   }
 }
 
+// The same vector from the ChaCha20 stream: element i is block `position0 + i` (64 bytes = 512 bits,
+// reduced mod r as four 128-bit pieces).  Same values as rng_draw_fr on the host.
+__global__ void k_rng_fr_chacha(RngKey key, uint64_t position0, uint64_t n, uint32_t* __restrict__ out) {
+  const uint32_t t128[8] = {0xef8cfeb9u, 0xb075da81u, 0xa5b6cd8cu, 0xa7f12accu,
+                            0x7957bf7bu, 0x32c47504u, 0x48ffa25eu, 0x03d581d7u};
+  Fr T;
+#pragma unroll
+  for (int k = 0; k < 8; k++) T.v[k] = t128[k];
+  for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x) {
+    uint32_t blk[16];
+    chacha20_block(key.k, position0 + i, blk);
+    Fr acc = Fr::zero();
+#pragma unroll
+    for (int piece = 3; piece >= 0; piece--) {   // most significant 128 bits first
+      Fr c = Fr::zero();
+#pragma unroll
+      for (int k = 0; k < 4; k++) c.v[k] = blk[4 * piece + k];
+      acc = fe_add(fe_mul(acc, T), fe_to_mont(c));
+    }
+    acc.store(out + i * 8);
+  }
+}
+
 // out = [s] * P for one Jacobian point and one Fr scalar (Montgomery form): double-and-add, one thread.
 __global__ void k_scalar_mul(const uint32_t* __restrict__ point_jac, const uint32_t* __restrict__ scalar,
                              uint32_t* __restrict__ out_jac) {
@@ -83,6 +106,7 @@ extern "C" int grape_hyrax_open(grape_ctx* ctx, const grape_table* table, const 
                                 uint32_t N, uint32_t layer_num, const void* h_eval_point, uint32_t n_e,
                                 const void* h_c, const void* h_G_jacobian, void* h_result, void* h_z,
                                 void* h_com_d, void* h_com_ad) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !table || !d_tensor || !h_eval_point || !h_c || !h_G_jacobian || !h_result || !h_z || !h_com_d || !h_com_ad)
     return fail(ctx, GRAPE_ERR_INVALID, "null argument");
   if (table->curve != 0) return fail(ctx, GRAPE_ERR_INVALID, "open: the opening protocol is built over BN254 only");
@@ -114,9 +138,17 @@ extern "C" int grape_hyrax_open(grape_ctx* ctx, const grape_table* table, const 
   GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(d_cG + 8, h_G_jacobian, 96, cudaMemcpyHostToDevice, ctx->stream));
   // blinding vector d from the context's random stream (reference: src/Hyrax.cu:253-256), generated on
   // the device; the host stream is advanced past the 8 words per element it consumed
-  k_rng_fr<<<std::min<uint32_t>((new_n + 127) / 128, (uint32_t)ctx->sm_count * 8), 128, 0, ctx->stream>>>(ctx->rng_state, new_n, d_d);
-  ctx->launches += 1;
-  ctx->rng_state += (uint64_t)new_n * 8 * 0x9E3779B97F4A7C15ull;
+  {
+    const uint32_t rng_blocks = std::min<uint32_t>((new_n + 127) / 128, (uint32_t)ctx->sm_count * 8);
+    if (ctx->rng.seeded) {
+      k_rng_fr<<<rng_blocks, 128, 0, ctx->stream>>>(ctx->rng.splitmix, new_n, d_d);
+      ctx->rng.splitmix += (uint64_t)new_n * 8 * 0x9E3779B97F4A7C15ull;
+    } else {
+      k_rng_fr_chacha<<<rng_blocks, 128, 0, ctx->stream>>>(ctx->rng.key, ctx->rng.position, new_n, d_d);
+      ctx->rng.position += new_n;
+    }
+    ctx->launches += 1;
+  }
   // com_d = sum_i d_i G_i
   if ((rc = commit_fr_async(ctx, table, d_d, new_n, new_n, d_pts))) return rc;
   // x = tensor folded over the row variables, then over the layer variables
@@ -188,6 +220,7 @@ __global__ void k_lincomb_finish(const Xyzz* __restrict__ partial, uint32_t n_pa
 // include/ec_operation.cuh:37-55, test/HyraxTest.cu:96-125).  d_out: one normalised Jacobian record.
 extern "C" int grape_g1_lincomb(grape_ctx* ctx, const void* d_points_jacobian, const void* d_scalars, uint64_t n,
                                 void* d_out) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !d_out || (n && (!d_points_jacobian || !d_scalars))) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
   if (n > (uint64_t(1) << 24)) return fail(ctx, GRAPE_ERR_LIMIT, "lincomb: at most 2^24 points");
   arena_reset(ctx);

@@ -390,6 +390,7 @@ extern "C" int grape_prove_matmul(grape_ctx* ctx, void* d_A, void* d_B, uint32_t
                                   uint32_t K, const void* h_u, uint32_t n_u, const void* h_v, uint32_t n_v,
                                   void* h_claim, void* h_out_claims, void* h_transcript,
                                   uint32_t transcript_capacity, uint32_t* n_rounds) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !d_A || !d_B || !h_u || !h_v || !h_claim || !h_out_claims) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
   MatmulRun run;
   int rc = matmul_enqueue(ctx, d_A, d_B, L, N, M, K, reinterpret_cast<const HostFr*>(h_u), n_u,
@@ -415,6 +416,7 @@ extern "C" int grape_prove_matmul_i32(grape_ctx* ctx, const int32_t* d_A, const 
                                       uint32_t M, uint32_t K, const void* h_u, uint32_t n_u, const void* h_v,
                                       uint32_t n_v, void* h_claim, void* h_out_claims, void* h_transcript,
                                       uint32_t transcript_capacity, uint32_t* n_rounds) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !d_A || !d_B || !h_u || !h_v || !h_claim || !h_out_claims) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
   MatmulRun run;
   int rc = matmul_enqueue<true>(ctx, d_A, d_B, L, N, M, K, reinterpret_cast<const HostFr*>(h_u), n_u,
@@ -449,6 +451,7 @@ extern "C" int grape_prove_matmul_partial(grape_ctx* ctx, void* d_A_shard, void*
                                           uint32_t M, uint32_t K_local, const void* h_u, uint32_t n_u,
                                           const void* h_v_local, uint32_t n_v_local, void* d_part,
                                           uint32_t* local_rounds) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !d_A_shard || !d_B_shard || !h_u || !h_v_local || !d_part)
     return fail(ctx, GRAPE_ERR_INVALID, "null argument");
   MatmulRun run;
@@ -472,6 +475,7 @@ extern "C" int grape_prove_matmul_finish(grape_ctx* ctx, const void* d_gathered,
                                          uint32_t M, uint32_t K, const void* h_u, uint32_t n_u, const void* h_v,
                                          uint32_t n_v, void* h_claim, void* h_out_claims, void* h_transcript,
                                          uint32_t transcript_capacity, uint32_t* n_rounds) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !d_gathered || !h_u || !h_v || !h_claim || !h_out_claims) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
   if (!P || !L || !N || !M || !K) return fail(ctx, GRAPE_ERR_INVALID, "prove_matmul_finish: zero dimension");
   const uint32_t lP = log2ceil(P), lL = log2ceil(L), lK = log2ceil(K);
@@ -522,6 +526,7 @@ extern "C" int grape_prove_elemul(grape_ctx* ctx, void* d_A, void* d_B, uint32_t
                                   const void* h_u, uint32_t n_u, const void* h_v, uint32_t n_v, void* h_claim,
                                   void* h_out_claims, void* h_transcript, uint32_t transcript_capacity,
                                   uint32_t* n_rounds) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !d_A || !d_B || !h_u || !h_v || !h_claim || !h_out_claims) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
   if (!L || !N || !M) return fail(ctx, GRAPE_ERR_INVALID, "prove_eleMul: zero dimension");
   const uint64_t first_size = (uint64_t)L * M, size = first_size * N;
@@ -591,6 +596,7 @@ extern "C" int grape_prove_elemul(grape_ctx* ctx, void* d_A, void* d_B, uint32_t
 extern "C" int grape_combine_claims(grape_ctx* ctx, void* d_X, uint64_t size, const void* h_claims, uint32_t k,
                                     const void* h_us, const void* h_v, uint32_t n_vars, void* h_result,
                                     void* h_transcript, uint32_t transcript_capacity, uint32_t* n_rounds) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !d_X || !h_claims || !h_us || !h_v || !h_result) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
   if (k == 0 || k > MAX_CLAIMS) return fail(ctx, GRAPE_ERR_LIMIT, "combine_claims: between 1 and 4 claims are supported");
   if (size == 0 || (uint64_t(1) << n_vars) != size)

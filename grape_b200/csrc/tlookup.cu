@@ -31,6 +31,11 @@ struct grape_lookup {
   uint32_t* m = nullptr;   // multiplicities of the last prove (Fr)
   uint32_t* mapped = nullptr;  // f(x) as Fr (mapping tables)
   uint32_t* hist = nullptr;    // u32 bins
+  // what a verifier of the last proof needs besides the round polynomials: the prover's u and the
+  // five tensors folded down to one value each, A~(v), S~(v), B~(v2), T~(v2), m~(v2)
+  std::vector<grape::HostFr> last_u;
+  grape::HostFr last_finals[5];
+  bool has_last = false;
 };
 
 namespace grape {
@@ -281,8 +286,8 @@ static int lookup_create(grape_ctx* ctx, int32_t low, uint32_t len, const int32_
   lk->low = low;
   lk->n = n;
   lk->mapping = d_map != nullptr;
-  lk->alpha = rng_next_fr(ctx->rng_state);               // reference: tLookup ctor, src/tlookup.cu:247
-  if (lk->mapping) lk->r = rng_next_fr(ctx->rng_state);  // reference: src/tlookup.cu:351
+  lk->alpha = rng_draw_fr(ctx->rng);               // reference: tLookup ctor, src/tlookup.cu:247
+  if (lk->mapping) lk->r = rng_draw_fr(ctx->rng);  // reference: src/tlookup.cu:351
   lk->beta = fr_from_u64(n);
   const size_t bytes = (size_t)n * 32;
   if (cudaMalloc(&lk->T, bytes) != cudaSuccess || cudaMalloc(&lk->B, bytes) != cudaSuccess ||
@@ -296,28 +301,40 @@ static int lookup_create(grape_ctx* ctx, int32_t low, uint32_t len, const int32_
   HostFr consts[3] = {fr_from_i64(low), lk->beta, lk->r};
   uint32_t* d_c;
   int rc = upload(ctx, consts, 3, &d_c);
-  if (rc) return rc;
+  if (rc) {
+    grape_lookup_destroy(lk);
+    return rc;
+  }
   if (lk->mapping) {
     rc = grape_fr_from_i32(ctx, d_map, lk->mapped, n);
-    if (rc) return rc;
+    if (rc) {
+      grape_lookup_destroy(lk);
+      return rc;
+    }
   }
   cudaMemsetAsync(lk->m, 0, bytes, ctx->stream);
   k_table_init<<<lk_blocks(ctx, n), LT, 0, ctx->stream>>>(lk->T, d_c, lk->mapped, d_c + 16, n);
   ctx->launches += 1;
   // B = 1 / (T + beta), batched
   rc = fr_inverse_async(ctx, lk->T, d_c + 8, lk->B, n);
-  if (rc) return rc;
-  GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  if (rc == GRAPE_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess)
+    rc = fail(ctx, GRAPE_ERR_CUDA, "lookup: table set-up failed on the device");
+  if (rc) {
+    grape_lookup_destroy(lk);
+    return rc;
+  }
   *out = lk;
   return GRAPE_OK;
 }
 
 extern "C" int grape_lookup_range_create(grape_ctx* ctx, int32_t low, uint32_t len, grape_lookup** out) {
+  if (ctx) grape::make_device_current(ctx);
   return lookup_create(ctx, low, len, nullptr, out);
 }
 
 extern "C" int grape_lookup_mapping_create(grape_ctx* ctx, int32_t low, uint32_t len, const int32_t* d_map,
                                            grape_lookup** out) {
+  if (ctx) grape::make_device_current(ctx);
   if (!d_map) return fail(ctx, GRAPE_ERR_INVALID, "lookup: null mapping table");
   return lookup_create(ctx, low, len, d_map, out);
 }
@@ -340,6 +357,18 @@ extern "C" int grape_lookup_params(const grape_lookup* lk, void* h_alpha, void* 
   if (h_beta) memcpy(h_beta, &lk->beta, 32);
   if (h_r) memcpy(h_r, &lk->r, 32);
   if (n) *n = lk->n;
+  return GRAPE_OK;
+}
+
+extern "C" int grape_lookup_last_proof(const grape_lookup* lk, void* h_finals, void* h_u, uint32_t u_capacity,
+                                       uint32_t* n_u) {
+  if (!lk || !lk->has_last) return GRAPE_ERR_INVALID;
+  if (h_finals) memcpy(h_finals, lk->last_finals, sizeof lk->last_finals);
+  if (n_u) *n_u = (uint32_t)lk->last_u.size();
+  if (h_u) {
+    if (u_capacity < lk->last_u.size()) return GRAPE_ERR_LIMIT;
+    memcpy(h_u, lk->last_u.data(), lk->last_u.size() * 32);
+  }
   return GRAPE_OK;
 }
 
@@ -367,7 +396,7 @@ static int lookup_prove(grape_ctx* ctx, grape_lookup* lk, uint32_t* d_S, uint64_
     return fail(ctx, GRAPE_ERR_INVALID, "lookup: cannot pad the queries to a power of two with the given row lengths");
   // u is drawn before anything else, as in the reference (src/tlookup.cu:293)
   std::vector<HostFr> u(lD);
-  for (auto& x : u) x = rng_next_fr(ctx->rng_state);
+  for (auto& x : u) x = rng_draw_fr(ctx->rng);
   uint32_t *d_u, *d_v, *d_c;
   int rc;
   if ((rc = upload(ctx, u.data(), lD, &d_u))) return rc;
@@ -380,16 +409,15 @@ static int lookup_prove(grape_ctx* ctx, grape_lookup* lk, uint32_t* d_S, uint64_
   if (D != Dp && (pad_bin < 0 || pad_bin >= (int64_t)N))
     return fail(ctx, GRAPE_ERR_INVALID, "lookup: padding needs 0 inside the table range");
   // Commit A by the bucket method?  Cost per row in units of one mixed addition of the direct kernel:
-  // direct = elements * windows of the table; bucketed = 1.5 * elements + 120 * table entries as
-  // MEASURED for this implementation (its second stage runs at a fraction of the direct kernel's
-  // rate: 20 * entries additions in the count, uneven bucket lengths and eight warps per SM in practice),
-  // so it is chosen only for rows several times longer than the table.
+  // direct = elements * windows of the table; bucketed = 1.2 * elements (stage 1: one addition per
+  // element, some spread inside a warp) + table entries * (1.3 for the normalisation + 20 windows *
+  // (1.08 for the bucket sums + 0.19 for the running sums)) = 1.2 * elements + 27 * table entries.
   uint32_t* d_idx = nullptr;
-  if (table && msm_size && ctx->bucket_mode != 0 && N % 8 == 0) {
+  if (table && msm_size && ctx->bucket_mode != 0 && N % 32 == 0) {
     const uint64_t a_wd0 = (uint64_t)msm_size * GRAPE_COM_SCALE;
     const uint64_t valid = (D != Dp && a_wd0 % inner_pad == 0) ? a_wd0 / inner_pad * inner : a_wd0;
     const double direct = (double)valid * ((254 + table->window_bits - 1) / table->window_bits);
-    const double bucketed = 1.5 * (double)valid + 120.0 * N;
+    const double bucketed = 1.2 * (double)valid + 27.0 * N;
     if (ctx->bucket_mode == 2 || bucketed < 0.9 * direct) {
       if ((rc = arena_alloc_t(ctx, (size_t)Dp, &d_idx))) return rc;
     }
@@ -505,7 +533,14 @@ static int lookup_prove(grape_ctx* ctx, grape_lookup* lk, uint32_t* d_S, uint64_
   if (lD) GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(hs.data(), sums, (size_t)lD * 11 * 32, cudaMemcpyDeviceToHost, ctx->stream));
   GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(&hs[(size_t)lD * 11], d_bm, 32, cudaMemcpyDeviceToHost, ctx->stream));
   GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(&hs[(size_t)lD * 11 + 1], d_S, 32, cudaMemcpyDeviceToHost, ctx->stream));
+  lk->has_last = false;
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(&lk->last_finals[0], d_A, 32, cudaMemcpyDeviceToHost, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(&lk->last_finals[1], d_S, 32, cudaMemcpyDeviceToHost, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(&lk->last_finals[2], Bw, 32, cudaMemcpyDeviceToHost, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(&lk->last_finals[3], Tw, 32, cudaMemcpyDeviceToHost, ctx->stream));
+  GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(&lk->last_finals[4], Mw, 32, cudaMemcpyDeviceToHost, ctx->stream));
   GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+  lk->last_u = u;
   uint32_t st = 0;
   GRAPE_CUDA_TRY(ctx, cudaMemcpy(&st, ctx->d_status, 4, cudaMemcpyDeviceToHost));
   if (st & STATUS_HIST_RANGE) {
@@ -550,6 +585,7 @@ static int lookup_prove(grape_ctx* ctx, grape_lookup* lk, uint32_t* d_S, uint64_
   }
   if (n_rounds) *n_rounds = emitted;
   *h_claim = hs[(size_t)lD * 11 + 1];
+  lk->has_last = true;
   return GRAPE_OK;
 }
 
@@ -559,6 +595,7 @@ extern "C" int grape_lookup_prove_range(grape_ctx* ctx, grape_lookup* lk, void* 
                                         const grape_table* table, uint32_t msm_size, void* d_com_A, void* d_com_m,
                                         void* h_claim, void* h_transcript, uint32_t transcript_capacity,
                                         uint32_t* n_rounds) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !lk || !d_S || !d_A || !h_v || !h_claim) return fail(ctx, GRAPE_ERR_INVALID, "null argument");
   if (lk->mapping) return fail(ctx, GRAPE_ERR_INVALID, "lookup: use grape_lookup_prove_mapping for a mapping table");
   arena_reset(ctx);
@@ -574,6 +611,7 @@ extern "C" int grape_lookup_prove_mapping(grape_ctx* ctx, grape_lookup* lk, cons
                                           uint32_t inner, uint32_t inner_pad, const grape_table* table,
                                           uint32_t msm_size, void* d_com_A, void* d_com_m, void* h_claim,
                                           void* h_transcript, uint32_t transcript_capacity, uint32_t* n_rounds) {
+  if (ctx) grape::make_device_current(ctx);
   if (!ctx || !lk || !d_S_in || !d_S_out || !d_S_work || !d_A || !h_v || !h_claim)
     return fail(ctx, GRAPE_ERR_INVALID, "null argument");
   if (!lk->mapping) return fail(ctx, GRAPE_ERR_INVALID, "lookup: not a mapping table");

@@ -201,6 +201,13 @@ class Context:
         self._check(self.lib.grape_measure_madd_peak(self.handle, C.byref(v)))
         return v.value
 
+    def field_check(self, field: int, d_elems, n: int) -> int:
+        """Failure mask of the squaring / inversion self-check over n elements of field 0 BN254 Fp,
+        1 BN254 Fr, 2 BLS12-381 Fp, 3 BLS12-381 Fr (0 = every identity holds)."""
+        m = C.c_uint32()
+        self._check(self.lib.grape_diag_field_check(self.handle, field, _p(d_elems), n, C.byref(m)))
+        return m.value
+
     def set_bucket_commit(self, mode: int):
         """How lookups commit A: 0 never by the bucket method, 1 when cheaper (default), 2 whenever possible."""
         self._check(self.lib.grape_lookup_set_bucket_commit(self.handle, mode))
@@ -512,6 +519,17 @@ class Lookup:
                                                       table.handle if table else None, msm_size, _p(d_com_A),
                                                       _p(d_com_m), out.ctypes.data, tr.ctypes.data, cap, C.byref(nr)))
         return decode_field(out)[0], [decode_field(tr[i]) for i in range(nr.value)]
+
+    def last_proof(self):
+        """(finals, u) of the last proof: finals = dict(A, S, B, T, m), the five tensors of the argument
+        folded to one value each; u = the prover's own draws.  What ``verifier.verify_lookup`` takes."""
+        fin = np.zeros((5, 8), dtype=np.uint32)
+        n = C.c_uint32()
+        self.ctx._check(self.ctx.lib.grape_lookup_last_proof(self.handle, fin.ctypes.data, None, 0, C.byref(n)))
+        u = np.zeros((max(n.value, 1), 8), dtype=np.uint32)
+        self.ctx._check(self.ctx.lib.grape_lookup_last_proof(self.handle, None, u.ctypes.data, n.value, C.byref(n)))
+        vals = decode_field(fin)
+        return dict(zip(("A", "S", "B", "T", "m"), vals)), decode_field(u[:n.value])
 
     def close(self):
         if getattr(self, "handle", None):

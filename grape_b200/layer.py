@@ -101,6 +101,7 @@ class FFNTrace:
     lookups: int = 0
     matmuls: int = 0
     seconds: dict = field(default_factory=dict)  # wall time per kind of step (filled when timing is on)
+    steps: list = field(default_factory=list)    # (kind, seconds) of every step in walk order (timing on)
 
 
 class FFNProver:
@@ -129,7 +130,9 @@ class FFNProver:
         t0 = time.perf_counter()
         yield
         self.ctx.sync()
-        trace.seconds[name] = trace.seconds.get(name, 0.0) + time.perf_counter() - t0
+        dt = time.perf_counter() - t0
+        trace.seconds[name] = trace.seconds.get(name, 0.0) + dt
+        trace.steps.append((name, dt))
 
     # -- helpers ---------------------------------------------------------------------------------
     # Device buffers are recycled between steps (the reference keeps three preallocated tensors for

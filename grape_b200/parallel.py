@@ -46,6 +46,55 @@ def gather_rows(local: np.ndarray, rows: int, dist=None, device: str = "cpu") ->
     return out
 
 
+class _DeviceBytes:
+    """A device region as a CUDA-array-interface object (bytes), so that torch can wrap it without a copy."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (int(nbytes),), "typestr": "|u1", "data": (int(ptr), False),
+                                         "version": 2, "strides": None}
+
+
+def torch_view(ptr: int, nbytes: int):
+    """torch uint8 tensor over `nbytes` of device memory at `ptr` (no copy; the caller keeps it alive)."""
+    import torch
+    return torch.as_tensor(_DeviceBytes(ptr, nbytes), device="cuda")
+
+
+def library_stream(ctx):
+    """The context's CUDA stream as a torch stream: collectives issued under ``torch.cuda.stream(...)``
+    of it are ordered after the library's kernels and before its next ones on the device, with no
+    host synchronisation in between."""
+    import torch
+    return torch.cuda.ExternalStream(ctx.stream)
+
+
+def gather_rows_device(ctx, d_local, block_rows: int, d_all, dist, record_bytes: int = 96):
+    """NCCL all-gather of this rank's `block_rows` row commitments (device buffer `d_local`) into the
+    device buffer `d_all` ([world][block_rows] records, rank order), issued on the library's stream.
+    Every rank passes the same `block_rows` (``row_block(rows, 0, world)`` length; ranks with one row
+    fewer pad their last record).  Nothing passes through the host."""
+    import torch
+    from .host import _p
+    world = dist.get_world_size()
+    n = block_rows * record_bytes
+    src = torch_view(_p(d_local), n)
+    dst = torch_view(_p(d_all), n * world)
+    with torch.cuda.stream(library_stream(ctx)):
+        dist.all_gather_into_tensor(dst, src)
+
+
+def commit_rows_sharded_device(ctx, table, d_scalars_block, block_rows: int, wd: int, d_local, d_all, dist,
+                               max_bits: int = 32):
+    """One rank's share of a row commitment dealt to the GPUs (Hyrax::commit over a row block,
+    src/Hyrax.cu:312-333, rows are independent): commit `block_rows` rows of `wd` int32 scalars resident
+    at `d_scalars_block` into `d_local`, then all-gather every rank's records into `d_all` over NCCL.
+    All work is queued on the library's stream; the caller synchronises when it needs the result."""
+    from .host import commit_i32
+    commit_i32(ctx, table, d_scalars_block, block_rows * wd, wd, d_local, max_bits=max_bits)
+    if dist is not None and dist.get_world_size() > 1:
+        gather_rows_device(ctx, d_local, block_rows, d_all, dist, table.jacobian_bytes)
+
+
 def commit_rows_sharded(scalars: np.ndarray, wd: int, commit_fn, dist=None, device: str = "cpu") -> np.ndarray:
     """Row commitments of a host int32 tensor with the rows dealt to the ranks in contiguous blocks.
     `commit_fn(block_scalars) -> uint32[block_rows, 24]` commits one block on this rank's GPU
@@ -102,12 +151,13 @@ def prove_matmul_sharded(ctx, d_A_shard, d_B_shard, L: int, N: int, M: int, K: i
     k_local = K // world
     n_el = host.matmul_partial_elems(L, k_local)
     device = torch.device("cuda", torch.cuda.current_device())
-    part = torch.empty(n_el * 8, dtype=torch.int32, device=device)
-    host.prove_matmul_partial(ctx, d_A_shard, d_B_shard, L, N, M, k_local, u, list(v)[lp:], part.data_ptr())
-    ctx.sync()                                   # the library's stream -> visible to the collective
-    gathered = gather_partials(part, dist)
-    torch.cuda.current_stream().synchronize()    # the collective -> visible to the library's stream
-    return host.prove_matmul_finish(ctx, gathered.data_ptr(), world, L, N, M, K, u, v, claim)
+    # torch runs under the library's own stream here: the collective is ordered after the partial
+    # proof and before the finish on the device, without a host synchronisation on either side
+    with torch.cuda.stream(library_stream(ctx)):
+        part = torch.empty(n_el * 8, dtype=torch.int32, device=device)
+        host.prove_matmul_partial(ctx, d_A_shard, d_B_shard, L, N, M, k_local, u, list(v)[lp:], part.data_ptr())
+        gathered = gather_partials(part, dist)
+        return host.prove_matmul_finish(ctx, gathered.data_ptr(), world, L, N, M, K, u, v, claim)
 
 
 def max_over_ranks(value: float, dist=None, device: str = "cpu") -> float:

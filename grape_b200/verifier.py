@@ -78,10 +78,17 @@ def _eq2(u, v):
     return (2 * u * v - u - v + 1) % R
 
 
-def check_rounds(claim: int, transcript, challenges) -> int | None:
+def check_rounds(claim: int, transcript, challenges, max_degree=3) -> int | None:
     """Runs p(0) + p(1) == claim, claim <- p(challenge) over the rounds; returns the final claim or
-    None when a round fails."""
-    for p, ch in zip(transcript, challenges):
+    None when a round fails, when the number of rounds differs from the number of challenges, or
+    when a round polynomial has a non-zero coefficient above its degree bound (`max_degree`: one
+    bound for all rounds or one per round; the provers pad every polynomial to four coefficients)."""
+    if len(transcript) != len(challenges):
+        return None
+    bounds = max_degree if isinstance(max_degree, (list, tuple)) else [max_degree] * len(transcript)
+    for p, ch, deg in zip(transcript, challenges, bounds):
+        if len(p) == 0 or len(p) > 4 or any(c % R for c in p[deg + 1:]):
+            return None
         if (p[0] + sum(p)) % R != claim % R:
             return None
         claim = _eval(p, ch)
@@ -93,10 +100,10 @@ def verify_matmul(claim: int, transcript, u, v, L: int, N: int, M: int, K: int, 
     v_K from the top; the final claim must equal a_claim * b_claim * prod eq(u_L, v_L)."""
     lL, lK = log2ceil(L), log2ceil(K)
     u_end, v_end = log2ceil(L * N * M), log2ceil(L * K)
-    if len(transcript) != lL + lK:
+    if len(transcript) != lL + lK or len(u) < u_end or len(v) < v_end:
         return False
     chal = [v[v_end - i - 1] for i in range(lL)] + [v[lK - i - 1] for i in range(lK)]
-    final = check_rounds(claim, transcript, chal)
+    final = check_rounds(claim, transcript, chal, max_degree=[3] * lL + [2] * lK)
     if final is None:
         return False
     E = 1
@@ -105,14 +112,15 @@ def verify_matmul(claim: int, transcript, u, v, L: int, N: int, M: int, K: int, 
     return a_claim * b_claim * E % R == final
 
 
-def verify_elemul(claim: int, transcript, u, v, a_claim: int, b_claim: int) -> bool:
+def verify_elemul(claim: int, transcript, u, v, a_claim: int, b_claim: int, size: int | None = None) -> bool:
     """Transcript of ``prove_eleMul``: one round per variable from the top; final claim must equal
-    a_claim * b_claim * eq(u, v)."""
-    n = len(transcript)
-    if len(u) < n or len(v) < n:
+    a_claim * b_claim * eq(u, v).  `size` (elements of the tensors, padded per axis as the prover pads
+    them) fixes the number of rounds; without it the number of challenges does."""
+    n = len(v) if size is None else log2ceil(size)
+    if len(transcript) != n or len(u) != n or len(v) != n:
         return False
     chal = [v[n - i - 1] for i in range(n)]
-    final = check_rounds(claim, transcript, chal)
+    final = check_rounds(claim, transcript, chal, max_degree=3)
     if final is None:
         return False
     E = 1
@@ -124,9 +132,9 @@ def verify_elemul(claim: int, transcript, u, v, a_claim: int, b_claim: int) -> b
 def verify_combine(claims, transcript, us, v, result: int) -> bool:
     """Transcript of ``combine_claims``: final claim must equal result * sum_j eq(u_j, v)."""
     n = len(v)
-    if len(transcript) != n:
+    if len(transcript) != n or len(us) != len(claims) or any(len(uj) != n for uj in us):
         return False
-    final = check_rounds(sum(claims) % R, transcript, [v[n - i - 1] for i in range(n)])
+    final = check_rounds(sum(claims) % R, transcript, [v[n - i - 1] for i in range(n)], max_degree=2)
     if final is None:
         return False
     total = 0
@@ -136,3 +144,74 @@ def verify_combine(claims, transcript, us, v, result: int) -> bool:
             E = E * _eq2(a, b) % R
         total = (total + E) % R
     return result * total % R == final
+
+
+# ---- lookup argument (LogUp sumcheck of src/tlookup.cu:192-244) ---------------------------------------
+def mle_eval(values, point) -> int:
+    """Multilinear extension of `values` (length 2^len(point), variable k = bit k of the index) at `point`."""
+    vals = [x % R for x in values]
+    for xk in point:
+        vals = [(vals[2 * i] + xk * (vals[2 * i + 1] - vals[2 * i])) % R for i in range(len(vals) // 2)]
+    return vals[0]
+
+
+def lookup_table_evals(low: int, n: int, beta: int, v_low, mapped=None, r: int = 0):
+    """(T~(v_low), B~(v_low)) of the PUBLIC table of a lookup object: T_j = low + j (+ r * mapped_j for a
+    mapping table, src/tlookup.cu:16-50), B_j = 1 / (T_j + beta).  O(n) field operations, one batched
+    inversion."""
+    T = [(low + j + (r * int(mapped[j]) if mapped is not None else 0)) % R for j in range(n)]
+    den = [(t + beta) % R for t in T]
+    pref, run = [], 1
+    for d in den:
+        run = run * d % R
+        pref.append(run)
+    inv = pow(run, -1, R)
+    B = [0] * n
+    for j in range(n - 1, -1, -1):
+        B[j] = inv * (pref[j - 1] if j else 1) % R
+        inv = inv * den[j] % R
+    return mle_eval(T, v_low), mle_eval(B, v_low)
+
+
+def verify_lookup(alpha: int, beta: int, n_table: int, d_padded: int, transcript, u, v, finals: dict,
+                  table_evals=None) -> bool:
+    """Transcript of ``tLookupRange::prove`` / ``tLookupRangeMapping::prove``.
+
+    The argument proves  sum_x [alpha eq(u,x) A(x) (S(x) + beta) + A(x)] + C = alpha + alpha^2  over the
+    padded queries, with C = alpha^2 - sum_j B_j m_j restated over the table in the second phase
+    (src/tlookup.cu:117-190).  Rounds 0 .. log2(D/N)-1 fold the top variables of A and S, the remaining
+    log2 N rounds fold A, S, B, T, m together.  Checks: the number and degree of the round polynomials;
+    p(0) + p(1) == claim in every round; and the closing identity at the random point,
+
+        claim_final == a A~ (S~ + beta) + ratio a2 B~ (T~ + beta) + A~ - ratio m~ B~,
+
+    a = alpha prod_all eq(u_i, v_i), a2 = alpha^2 prod_phase2 eq(u_i, v_i), ratio = N / D.
+    `finals` holds the claimed A~(v), S~(v), B~, T~, m~ (``Lookup.last_proof``): S~ is what the prover
+    returns and the caller ties to an opening of S; A~ and m~ are to be tied to openings of the
+    commitments of A and m; `table_evals` = (T~, B~) recomputed from the public table
+    (``lookup_table_evals``) replaces trust in the prover's B~ and T~ when given."""
+    lD, lN = log2ceil(d_padded), log2ceil(n_table)
+    if d_padded != 1 << lD or n_table != 1 << lN or lN > lD:
+        return False
+    if len(transcript) != lD or len(u) != lD or len(v) != lD:
+        return False
+    if table_evals is not None and (finals["T"] % R, finals["B"] % R) != (table_evals[0] % R, table_evals[1] % R):
+        return False
+    n_phase1 = lD - lN
+    claim = (alpha + alpha * alpha) % R
+    a, a2 = alpha % R, alpha * alpha % R
+    for i, p in enumerate(transcript):
+        if len(p) == 0 or len(p) > 4:
+            return False
+        if (p[0] + sum(p)) % R != claim:
+            return False
+        vb, ub = v[lD - 1 - i], u[lD - 1 - i]
+        claim = _eval(p, vb)
+        e = _eq2(ub, vb)
+        a = a * e % R
+        if i >= n_phase1:
+            a2 = a2 * e % R
+    ratio = n_table * pow(d_padded, -1, R) % R
+    A, S, B, T, m = (finals[k] % R for k in ("A", "S", "B", "T", "m"))
+    want = (a * A % R * ((S + beta) % R) + ratio * a2 % R * B % R * ((T + beta) % R) + A - ratio * m % R * B) % R
+    return want == claim

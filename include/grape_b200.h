@@ -45,9 +45,10 @@ typedef struct grape_table grape_table;
 typedef struct grape_lookup grape_lookup;
 
 /* ---- context ------------------------------------------------------------------------------ */
-/* One context = one GPU + one stream + a grow-only scratch arena + a seedable RNG.  The
- * reference has no such object (single device, default stream, src/Hyrax.cu:312-333 allocates
- * and frees scratch in every call). */
+/* One context = one GPU + one stream + a grow-only scratch arena + the prover's random stream.
+ * The reference has no such object (single device, default stream, src/Hyrax.cu:312-333 allocates
+ * and frees scratch in every call).  Every call that takes a context makes the context's GPU the
+ * calling thread's current CUDA device and leaves it so; one host thread at a time per context. */
 int grape_ctx_create(int device, grape_ctx** out);
 int grape_ctx_destroy(grape_ctx* ctx);
 const char* grape_ctx_error(const grape_ctx* ctx);
@@ -55,10 +56,16 @@ int grape_ctx_sync(grape_ctx* ctx);
 void* grape_ctx_stream(grape_ctx* ctx); /* cudaStream_t */
 int grape_version(void);
 
-/* Seeds the stream that replaces libff's Fr::random_element() inside the provers
- * (reference draws: src/tlookup.cu:247,293,351,403; src/Hyrax.cu:253-256). */
+/* The stream that replaces libff's Fr::random_element() inside the provers (reference draws:
+ * src/tlookup.cu:247,293,351,403; src/Hyrax.cu:253-256: the lookups' alpha, r and u, the blinding
+ * vector of every opening).  A new context draws from ChaCha20 under a 256-bit key taken from the
+ * operating system (grape_ctx_create fails without one), 512 bits per element reduced mod r.
+ * grape_rng_seed switches the context to a REPLAYABLE SplitMix64 stream with 64 bits of state, the
+ * one the oracle and the reference stand-in use, so that tests can compare proofs bit for bit.
+ * Security: with a seeded stream the blinders are predictable and z = c*x + d reveals x; never
+ * seed a context whose proofs must hide their witness. */
 int grape_rng_seed(grape_ctx* ctx, uint64_t seed);
-/* Draws n Fr elements (Montgomery form) from that stream into host memory. */
+/* Draws n Fr elements (Montgomery form) from the context's stream into host memory. */
 int grape_rng_fr(grape_ctx* ctx, void* h_out, uint64_t n);
 
 /* ---- raw device memory (so that FFI callers need not bind the CUDA runtime) ---------------- */
@@ -227,6 +234,14 @@ int grape_lookup_mapping_create(grape_ctx* ctx, int32_t low, uint32_t len, const
 int grape_lookup_destroy(grape_lookup* lk);
 /* alpha, beta, r (32 bytes each, any may be NULL) and the table size. */
 int grape_lookup_params(const grape_lookup* lk, void* h_alpha, void* h_beta, void* h_r, uint32_t* n);
+/* What a verifier of the LAST successful prove on this object needs besides the round polynomials
+ * (no counterpart in the reference, whose tLookup_phase2 returns S~(v) alone, src/tlookup.cu:195,
+ * and whose only checks are the prover-side p(0)+p(1) tests, src/tlookup.cu:203,231):
+ *   h_finals: five Fr elements A~(v), S~(v), B~(v_low), T~(v_low), m~(v_low), the tensors of the
+ *             argument folded down to one value each (v_low = the log2(table size) low challenges);
+ *   h_u:      the ceil(log2 D) elements the prover drew for u (src/tlookup.cu:293), *n_u of them.
+ * Either pointer may be NULL.  GRAPE_ERR_INVALID when no proof has been produced yet. */
+int grape_lookup_last_proof(const grape_lookup* lk, void* h_finals, void* h_u, uint32_t u_capacity, uint32_t* n_u);
 /* Device tensors of the object: 0 = T, 1 = B = 1/(T+beta), 2 = m (multiplicities of the last
  * prove), 3 = mapped values. */
 const void* grape_lookup_table(const grape_lookup* lk, int which);
@@ -292,8 +307,10 @@ int grape_g1_lincomb(grape_ctx* ctx, const void* d_points_jacobian, const void* 
  * afford cudaMalloc's implicit device synchronisation -- this variant of grape_commit_i32 keeps
  * its per-(row, chunk) partial sums in a fixed 8 MiB array inside the library image instead of
  * the context's arena.  It takes no context: d_table / n_gens / window_bits / n_windows describe
- * a table as grape_table_create lays it out (grape_table_data returns the pointer), the work runs
- * on the current CUDA device and on `stream` (a cudaStream_t, NULL = default stream).
+ * a BN254 table as grape_table_create lays it out (grape_table_data returns the pointer; a
+ * BLS12-381 table or the 256-row layout wrapped by grape_table_from_reference is NOT accepted and,
+ * since a raw pointer cannot tell, would be misread), the work runs on the current CUDA device and
+ * on `stream` (a cudaStream_t, NULL = default stream).
  *   - calls no cudaMalloc / cudaFree / allocating routine;
  *   - at most 65536 partial sums per call, one or more per (row, window group) where window
  *     groups = ceil(ceil(max_bits / window_bits) / n_windows): rows * groups > 65536 returns
@@ -304,7 +321,10 @@ int grape_g1_lincomb(grape_ctx* ctx, const void* d_points_jacobian, const void* 
  *     rewrites what it reads and clears its status word, so calls queued on one stream are safe,
  *     calls that can overlap on the GPU race;
  *   - h_status may be NULL; otherwise the call synchronises `stream` and stores 1 when a scalar
- *     exceeded max_bits, else 0.
+ *     exceeded max_bits, else 0 (with NULL such a scalar goes unreported);
+ *   - several host threads may call it: the per-device set-up is serialised and
+ *     grape_static_error() returns the calling thread's last message; their kernels still share the
+ *     one array, so the overlap rule above applies across threads too.
  * Every GPU that loads the library holds the array until the process exits. */
 int grape_commit_i32_static(const void* d_table, uint32_t n_gens, uint32_t window_bits, uint32_t n_windows,
                             const int32_t* d_scalars, uint64_t size, uint32_t wd, uint32_t max_bits,
@@ -329,8 +349,14 @@ int grape_ctx_status(grape_ctx* ctx, uint32_t* flags);
 uint64_t grape_ctx_launches(const grape_ctx* ctx);
 /* Measured integer-pipe ceilings (operations per second): kind 0 mad.lo.u32, 1 mad.wide.u32,
  * 2 mad.lo.cc/madc.hi pairs (counted as two), 3 Fp Montgomery multiplications, 4 the same with a
- * loop body of 16 inlined multiplications (instruction-fetch probe). */
+ * loop body of 16 inlined multiplications (instruction-fetch probe), 5 dedicated Fp squarings. */
 int grape_measure_int_peak(grape_ctx* ctx, int kind, double* ops_per_second);
+/* Self-check of the specialised field routines against the plain multiplication (the reference has a
+ * dedicated squaring and a Euclid inversion too: include/field/mont_t.cuh:145-192, 1058-1120).
+ * field: 0 BN254 Fp, 1 BN254 Fr, 2 BLS12-381 Fp, 3 BLS12-381 Fr; d_elems: n canonical Montgomery
+ * elements.  *h_fail_mask = OR over the elements of: 1 squaring != a*a, 2 Euclid inverse != Fermat
+ * inverse, 4 a * a^-1 != 1, 8 inverse of 0 != 0. */
+int grape_diag_field_check(grape_ctx* ctx, int field, const void* d_elems, uint64_t n, uint32_t* h_fail_mask);
 /* Mixed point additions per second on register-resident operands: the commitment kernel's
  * arithmetic with no memory traffic, at the same register budget. */
 int grape_measure_madd_peak(grape_ctx* ctx, double* adds_per_second);

@@ -154,7 +154,7 @@ static int parity(const char* in_path, const char* out_path) {
   return 0;
 }
 
-static int commit_bench(uint32_t rows, int steps) {
+static int commit_bench(uint32_t rows, int steps, int warmup) {
   const uint32_t wd = 4096, n_gens = 4096;
   ppT::init_public_params();
   ref_shim_seed(0xC4);
@@ -173,8 +173,11 @@ static int commit_bench(uint32_t rows, int steps) {
   }
   int* d = to_dev(h.data(), h.size());
   Hyrax hyrax(1, n_gens / 16, points, cpu_points[0]);
-  jacob_t* c = hyrax.commit(d, rows * wd, wd / 16);  // warm-up
-  cudaFree(c);
+  jacob_t* c = nullptr;
+  for (int s = 0; s < (warmup < 1 ? 1 : warmup); s++) {  // untimed warm-up steps
+    c = hyrax.commit(d, rows * wd, wd / 16);
+    cudaFree(c);
+  }
   cudaEvent_t e0, e1;
   cudaEventCreate(&e0);
   cudaEventCreate(&e1);
@@ -202,9 +205,9 @@ static int commit_bench(uint32_t rows, int steps) {
   float ms_e2e = 0;
   cudaEventElapsedTime(&ms_e2e, e0, e1);
   cudaError_t e = cudaGetLastError();
-  printf("{\"rows\": %u, \"row_len\": %u, \"steps\": %d, \"ms_per_step\": %.4f, \"points_per_s\": %.1f, "
+  printf("{\"rows\": %u, \"row_len\": %u, \"warmup\": %d, \"steps\": %d, \"ms_per_step\": %.4f, \"points_per_s\": %.1f, "
          "\"e2e_ms_per_step\": %.4f, \"e2e_points_per_s\": %.1f, \"table_build_s\": %.3f, \"cuda_status\": \"%s\"}\n",
-         rows, wd, steps, ms / steps, (double)rows * wd * steps / (ms * 1e-3), ms_e2e / steps,
+         rows, wd, warmup < 1 ? 1 : warmup, steps, ms / steps, (double)rows * wd * steps / (ms * 1e-3), ms_e2e / steps,
          (double)rows * wd * steps / (ms_e2e * 1e-3), table_s, cudaGetErrorString(e));
   return e == cudaSuccess ? 0 : 6;
 }
@@ -258,8 +261,8 @@ static int matmul_bench(uint32_t shrink, int steps) {
 
 // C3: the reference's tLookupRange::prove on 2^log2_d uniform queries into a 2^16 table, with its
 // commitments of A and m over 4096 generators (test/tlookupTest.cu flow).
-static int lookup_bench(uint32_t log2_d, int steps) {
-  const uint32_t D = 1u << log2_d, len = 1u << 16, n_gens = 4096;
+static int lookup_bench(uint32_t log2_d, int steps, uint32_t n_gens) {
+  const uint32_t D = 1u << log2_d, len = 1u << 16;
   ppT::init_public_params();
   ref_shim_seed(0xC3);
   affine_t* points;
@@ -290,17 +293,17 @@ static int lookup_bench(uint32_t log2_d, int steps) {
     (void)value;
   }
   cudaError_t e = cudaGetLastError();
-  printf("{\"D\": %u, \"table\": %u, \"steps\": %d, \"ms_per_proof\": %.4f, \"commit_ms_reported_by_reference\": %.4f, "
-         "\"cuda_status\": \"%s\"}\n", D, len, steps, total / steps * 1e3, com_total / steps * 1e3, cudaGetErrorString(e));
+  printf("{\"D\": %u, \"table\": %u, \"generators\": %u, \"steps\": %d, \"ms_per_proof\": %.4f, \"commit_ms_reported_by_reference\": %.4f, "
+         "\"cuda_status\": \"%s\"}\n", D, len, n_gens, steps, total / steps * 1e3, com_total / steps * 1e3, cudaGetErrorString(e));
   return e == cudaSuccess ? 0 : 6;
 }
 
 int main(int argc, char** argv) {
   if (argc >= 4 && std::string(argv[1]) == "parity") return parity(argv[2], argv[3]);
-  if (argc >= 4 && std::string(argv[1]) == "commit-bench") return commit_bench(atoi(argv[2]), atoi(argv[3]));
+  if (argc >= 4 && std::string(argv[1]) == "commit-bench") return commit_bench(atoi(argv[2]), atoi(argv[3]), argc >= 5 ? atoi(argv[4]) : 1);
   if (argc >= 4 && std::string(argv[1]) == "matmul-bench") return matmul_bench(atoi(argv[2]), atoi(argv[3]));
-  if (argc >= 4 && std::string(argv[1]) == "lookup-bench") return lookup_bench(atoi(argv[2]), atoi(argv[3]));
-  fprintf(stderr, "usage: ref_harness parity <in> <out> | commit-bench <rows> <steps> | matmul-bench <shrink> <steps> | "
-                  "lookup-bench <log2 queries> <steps>\n");
+  if (argc >= 4 && std::string(argv[1]) == "lookup-bench") return lookup_bench(atoi(argv[2]), atoi(argv[3]), argc >= 5 ? (uint32_t)atoi(argv[4]) : 4096u);
+  fprintf(stderr, "usage: ref_harness parity <in> <out> | commit-bench <rows> <steps> [warm-up steps] | matmul-bench <shrink> <steps> | "
+                  "lookup-bench <log2 queries> <steps> [generators]\n");
   return 2;
 }
