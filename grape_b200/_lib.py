@@ -130,6 +130,11 @@ def _declare(lib):
                                      C.POINTER(u32)])
     f("grape_hyrax_open", [vp, vp, vp, u64, u32, u32, vp, u32, vp, vp, vp, vp, vp, vp])
     f("grape_g1_lincomb", [vp, vp, vp, u64, vp])
+    for name in ("grape_hg1_add", "grape_hg1_scalar_mul"):
+        f(name, [vp, vp, vp], None)
+    for name in ("grape_hg1_neg", "grape_hg1_normalise"):
+        f(name, [vp, vp], None)
+    f("grape_hg1_equal", [vp, vp])
     for name in _OPTIONAL:
         if hasattr(lib, name):
             f(name, _OPTIONAL[name])

@@ -546,11 +546,28 @@ int fold_axis_async(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* 
   const uint64_t n_threads = cpt ? n_out / cpt : n_out;
   uint32_t n_slices = 1;
   if (gap > 1) {
-    uint64_t out_blocks = (n_threads + FOLD_THREADS - 1) / FOLD_THREADS;
-    // staged blocks hold 64 KB of shared memory: three per SM, two waves of them; the plain kernel
-    // runs eight blocks per SM
-    uint64_t target = (uint64_t)ctx->sm_count * (cpt ? 6 : 8);
-    if (out_blocks < target) n_slices = (uint32_t)std::min<uint64_t>((target + out_blocks - 1) / out_blocks, (c + 15) / 16);
+    // Split the folded axis so that the grid fills the blocks the GPU can hold at once without
+    // spilling a few blocks into one more wave (896 blocks on room for 444 run as three waves).
+    int per_sm = 0;
+    cudaError_t oe;
+    if (cpt == 4) {
+      GRAPE_CUDA_TRY(ctx, cudaFuncSetAttribute(k_fold_axis_i32_staged<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               StageLayout<4>::SMEM_BYTES));
+      oe = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_fold_axis_i32_staged<4>, FOLD_THREADS,
+                                                         StageLayout<4>::SMEM_BYTES);
+    } else if (cpt == 2) {
+      oe = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_fold_axis_i32_staged<2>, FOLD_THREADS,
+                                                         StageLayout<2>::SMEM_BYTES);
+    } else if (cpt == 1) {
+      oe = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_fold_axis_i32_staged<1>, FOLD_THREADS,
+                                                         StageLayout<1>::SMEM_BYTES);
+    } else {
+      oe = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k_fold_axis<FROM_I32>, FOLD_THREADS, 0);
+    }
+    if (oe != cudaSuccess || per_sm < 1) per_sm = 4;
+    const uint64_t room = (uint64_t)ctx->sm_count * per_sm;
+    const uint64_t out_blocks = (n_threads + FOLD_THREADS - 1) / FOLD_THREADS;
+    if (out_blocks < room) n_slices = (uint32_t)std::min<uint64_t>(room / out_blocks, (c + 15) / 16);
     if (n_slices < 1) n_slices = 1;
   }
   size_t w_bytes = ((size_t)c * 32 + 255) & ~size_t(255);
@@ -581,13 +598,9 @@ int fold_axis_async(grape_ctx* ctx, const void* d_t, uint64_t ntot, const void* 
       ProfScope prof(ctx);
       const int32_t* ti = reinterpret_cast<const int32_t*>(d_t);
       if (cpt == 4) {
-        GRAPE_CUDA_TRY(ctx, cudaFuncSetAttribute(k_fold_axis_i32_staged<4>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 StageLayout<4>::SMEM_BYTES));
         k_fold_axis_i32_staged<4><<<grid, FOLD_THREADS, StageLayout<4>::SMEM_BYTES, ctx->stream>>>(
             ti, w, c, gap, n_out, slice_len, fold_dst, corr, ctx->d_status);
       } else if (cpt == 2) {
-        GRAPE_CUDA_TRY(ctx, cudaFuncSetAttribute(k_fold_axis_i32_staged<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 StageLayout<2>::SMEM_BYTES));
         k_fold_axis_i32_staged<2><<<grid, FOLD_THREADS, StageLayout<2>::SMEM_BYTES, ctx->stream>>>(
             ti, w, c, gap, n_out, slice_len, fold_dst, corr, ctx->d_status);
       } else if (cpt == 1) {

@@ -401,16 +401,27 @@ static int check_table(grape_ctx* ctx, const grape_table* t, uint32_t wd) {
   return GRAPE_OK;
 }
 
-// Picks how many warps share one row: one when there are at least two warps per scheduler already,
-// otherwise enough to reach that while leaving every lane at least two generators.  More warps
-// than that lose: every extra warp pays the five-step shuffle reduction (measured on 1024 rows of
-// 1024 generators: one chunk 0.29 ms, five chunks 0.42 ms).
+// Picks how many warps (chunks of generators) share one (row, window group).
+//   * Few units (less than half of the warps the GPU holds at once): enough chunks to reach that, while
+//     every lane keeps at least two generators.  More lose: every chunk pays its share of the block
+//     reduction (measured on 1024 rows of 1024 generators: one chunk 0.29 ms, five chunks 0.42 ms).
+//   * Otherwise a grid of equal units ends with a partial wave of warps whose cost is about a third of
+//     one unit's duration whatever the grid size; with only a few waves that is 10 to 15 % of the
+//     launch (10 240 units of a 512-row lookup commitment: 4.3 waves).  Units are cut until the grid
+//     has about twelve waves, as long as a chunk keeps 2048 generators (64 additions per lane, the
+//     reduction stays near 3 % of a unit).
 static uint32_t pick_chunks(const grape_ctx* ctx, uint64_t rows, uint32_t wd, uint32_t groups = 1) {
-  uint64_t target_warps = (uint64_t)ctx->sm_count * 8;
-  rows *= groups;  // every (row, window group) is a unit of its own
-  if (rows >= target_warps) return 1;
-  uint64_t want = (target_warps + rows - 1) / rows;
-  uint64_t max_chunks = (wd + 63) / 64;
+  const uint64_t cap = (uint64_t)ctx->sm_count * 16;  // resident warps: four blocks of four per SM
+  const uint64_t units = rows * groups;               // every (row, window group) is a unit of its own
+  if (units == 0) return 1;
+  uint64_t want, max_chunks;
+  if (units < cap / 2) {
+    want = (cap / 2 + units - 1) / units;
+    max_chunks = (wd + 63) / 64;
+  } else {
+    want = (12 * cap + units - 1) / units;
+    max_chunks = wd / 2048;
+  }
   if (want > max_chunks) want = max_chunks;
   if (want < 1) want = 1;
   return (uint32_t)want;

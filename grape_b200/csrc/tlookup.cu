@@ -36,6 +36,10 @@ struct grape_lookup {
   std::vector<grape::HostFr> last_u;
   grape::HostFr last_finals[5];
   bool has_last = false;
+  // device time of the commitments of A and m inside the last prove (the reference reports it through
+  // its commit_time argument, src/tlookup.cu:319-323)
+  cudaEvent_t ev_commit0 = nullptr, ev_commit1 = nullptr;
+  float last_commit_ms = 0.f;
 };
 
 namespace grape {
@@ -347,6 +351,10 @@ extern "C" int grape_lookup_destroy(grape_lookup* lk) {
   cudaFree(lk->m);
   cudaFree(lk->hist);
   cudaFree(lk->mapped);
+  if (lk->ev_commit0) {
+    cudaEventDestroy(lk->ev_commit0);
+    cudaEventDestroy(lk->ev_commit1);
+  }
   delete lk;
   return GRAPE_OK;
 }
@@ -369,6 +377,12 @@ extern "C" int grape_lookup_last_proof(const grape_lookup* lk, void* h_finals, v
     if (u_capacity < lk->last_u.size()) return GRAPE_ERR_LIMIT;
     memcpy(h_u, lk->last_u.data(), lk->last_u.size() * 32);
   }
+  return GRAPE_OK;
+}
+
+extern "C" int grape_lookup_last_commit_seconds(const grape_lookup* lk, double* seconds) {
+  if (!lk || !seconds) return GRAPE_ERR_INVALID;
+  *seconds = lk->last_commit_ms * 1e-3;
   return GRAPE_OK;
 }
 
@@ -441,7 +455,13 @@ static int lookup_prove(grape_ctx* ctx, grape_lookup* lk, uint32_t* d_S, uint64_
   }
   if ((rc = grape_fr_from_u32(ctx, lk->hist, lk->m, N))) return rc;
   // commitments to A and m (reference: src/tlookup.cu:319-323); optional here
+  lk->last_commit_ms = 0.f;
   if (table) {
+    if (!lk->ev_commit0) {
+      GRAPE_CUDA_TRY(ctx, cudaEventCreate(&lk->ev_commit0));
+      GRAPE_CUDA_TRY(ctx, cudaEventCreate(&lk->ev_commit1));
+    }
+    GRAPE_CUDA_TRY(ctx, cudaEventRecord(lk->ev_commit0, ctx->stream));
     if (msm_size == 0 || Dp % ((uint64_t)msm_size * GRAPE_COM_SCALE) != 0)
       return fail(ctx, GRAPE_ERR_INVALID, "lookup: D must be a multiple of msm_size * 16");
     const uint32_t m_wd = (1u << (lN / 2)) * GRAPE_COM_SCALE;
@@ -483,6 +503,7 @@ static int lookup_prove(grape_ctx* ctx, grape_lookup* lk, uint32_t* d_S, uint64_
       return rc;
     }
     if ((rc = commit_fr_async(ctx, table, lk->m, N, m_wd, d_com_m))) return rc;
+    GRAPE_CUDA_TRY(ctx, cudaEventRecord(lk->ev_commit1, ctx->stream));
   }
   // working copies of B, T, m (the rounds fold in place), sum_j B_j m_j
   uint32_t *Bw, *Tw, *Mw, *partial, *sums, *whi, *wlo, *d_bm;
@@ -541,6 +562,7 @@ static int lookup_prove(grape_ctx* ctx, grape_lookup* lk, uint32_t* d_S, uint64_
   GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(&lk->last_finals[4], Mw, 32, cudaMemcpyDeviceToHost, ctx->stream));
   GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
   lk->last_u = u;
+  if (table) cudaEventElapsedTime(&lk->last_commit_ms, lk->ev_commit0, lk->ev_commit1);
   uint32_t st = 0;
   GRAPE_CUDA_TRY(ctx, cudaMemcpy(&st, ctx->d_status, 4, cudaMemcpyDeviceToHost));
   if (st & STATUS_HIST_RANGE) {

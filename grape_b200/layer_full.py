@@ -30,6 +30,24 @@ class LayerShape(FFNShape):
     softmax_len: int = 1 << 16       # range of the softmax rounding residual (reference: tLookupRange(0, 1<<16))
 
 
+def rms_factor(x: np.ndarray, scale: int, eps: float = 1e-5) -> np.ndarray:
+    """The quantised RMSNorm factor of every token, in integers: for x = scale * x_real,
+
+        rms = round(scale / sqrt(mean(x_real^2) + eps)) = round(scale^2 * sqrt(d) / sqrt(sum(x^2) + eps * d * scale^2)),
+
+    computed as an integer square root with 16 guard bits (the model computes it in floating point,
+    zzllama/llama/model.py:204,221-226: rsqrt of the mean square plus eps, times the scale, rounded).
+    x: int64 [..., d]; returns int64 [...]."""
+    d = x.shape[-1]
+    sq = (x.astype(np.int64) ** 2).sum(axis=-1)
+    e = int(round(eps * d * scale * scale))
+    guard = 16
+    num = (scale ** 4 * d) << (2 * guard)
+    import math
+    flat = [(math.isqrt(num // (int(v) + e)) + (1 << (guard - 1))) >> guard if int(v) + e > 0 else 0 for v in sq.reshape(-1)]
+    return np.array(flat, dtype=np.int64).reshape(sq.shape)
+
+
 def synthesize_layer(shape: LayerShape, seed: int, x_range: int = 1 << 13, w_std: float = 0.02 * 65536,
                      matmul=None, exp_max: int = 15):
     """Integer tensors of one layer batch, all relations of the quantised forward pass holding exactly."""
@@ -43,9 +61,11 @@ def synthesize_layer(shape: LayerShape, seed: int, x_range: int = 1 << 13, w_std
     inp = rng.integers(-x_range, x_range, size=(L, T, d)).astype(np.int64)
 
     def rmsnorm(x, tag):
-        # the per-token factor is committed and opened but not derived in the proof; any positive integers do
-        rms = rng.integers(s1 // 4, s1 // 2, size=(L, T, 1)).astype(np.int64)
-        wn = rng.integers(s1 // 2, s1, size=(L, d, 1)).astype(np.int64)
+        # per-token factor derived from the data as the model does (zzllama/llama/model.py:204,221-239):
+        # rms = round(scale / sqrt(mean((x/scale)^2) + eps)) by an integer square root, then the two rescales
+        # rmsw = rms (x) w / scale and out = x * rmsw / scale; the norm weights are near one (random init)
+        rms = rms_factor(x, s1).reshape(L, T, 1)
+        wn = rng.integers(s1 - s1 // 8, s1 + s1 // 8 + 1, size=(L, d, 1)).astype(np.int64)
         rmsw_q, rmsw_rem = round_div(matmul(rms, wn), s1)              # [L][T][d] = rms (x) w
         out_q, out_rem = round_div(x * rmsw_q, s1)
         t.update({f"rms{tag}": rms, f"wnorm{tag}": wn, f"rmsw{tag}_q": rmsw_q, f"rmsw{tag}_rem": rmsw_rem,

@@ -242,6 +242,9 @@ int grape_lookup_params(const grape_lookup* lk, void* h_alpha, void* h_beta, voi
  *   h_u:      the ceil(log2 D) elements the prover drew for u (src/tlookup.cu:293), *n_u of them.
  * Either pointer may be NULL.  GRAPE_ERR_INVALID when no proof has been produced yet. */
 int grape_lookup_last_proof(const grape_lookup* lk, void* h_finals, void* h_u, uint32_t u_capacity, uint32_t* n_u);
+/* Device time, in seconds, that the commitments of A and m took inside the last prove with a table
+ * (what the reference adds to its commit_time argument, src/tlookup.cu:319-323); 0 without one. */
+int grape_lookup_last_commit_seconds(const grape_lookup* lk, double* seconds);
 /* Device tensors of the object: 0 = T, 1 = B = 1/(T+beta), 2 = m (multiplicities of the last
  * prove), 3 = mapped values. */
 const void* grape_lookup_table(const grape_lookup* lk, int which);
@@ -299,6 +302,17 @@ void grape_hfr_from_i64(int64_t v, void* out);
  * (host_partial_me<G1>, Fr * G1: include/ec_operation.cuh:37-55, test/HyraxTest.cu:96-125). */
 int grape_g1_lincomb(grape_ctx* ctx, const void* d_points_jacobian, const void* d_scalars, uint64_t n,
                      void* d_out);
+
+/* ---- host-side group arithmetic for drivers (not on the proving path) ------------------------- */
+/* What the reference's drivers do with libff's alt_bn128_G1 on the host: the verifier identities of
+ * test/HyraxTest.cu:88-125, host_partial_me<bn128> (include/ec_operation.cuh:37-55).  All pointers are
+ * HOST pointers to 96-byte Jacobian records (X|Y|Z Montgomery, Z = 0 infinity), any Z accepted;
+ * scalars are 32-byte Montgomery Fr.  Thread-safe (no state). */
+void grape_hg1_add(const void* h_a, const void* h_b, void* h_out);
+void grape_hg1_scalar_mul(const void* h_fr, const void* h_point, void* h_out);
+void grape_hg1_neg(const void* h_a, void* h_out);
+void grape_hg1_normalise(const void* h_a, void* h_out); /* Z = 1, or (1, 1, 0) for infinity */
+int grape_hg1_equal(const void* h_a, const void* h_b);  /* 1 when the two records are the same group element */
 
 /* ---- allocation-free commitment ------------------------------------------------------------ */
 /* No counterpart in the reference (its commit allocates and frees scratch on every call,

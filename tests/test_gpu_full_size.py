@@ -89,7 +89,8 @@ def test_c3_range_lookup_2p22_queries(gctx):
     gens = wl.make_generators(gctx, wd, 0xC3)
     table = g.GeneratorTable(gctx, gens, 13, 1)
     dqi, dS, dA = gctx.upload(q), gctx.alloc(D * 32), gctx.alloc(D * 32)
-    com_A, com_m = gctx.alloc(D // wd * 96), gctx.alloc(Nt // 256 * 96)
+    m_wd = 256 * 16    # the multiplicities are committed in rows of 2^(log2(N)/2) * 16 elements (src/tlookup.cu:321)
+    com_A, com_m = gctx.alloc(D // wd * 96), gctx.alloc(Nt // m_wd * 96)
     gctx.seed(0xC3)
     lk = host.Lookup(gctx, low, Nt)
     vv = host.decode_field(gctx.random_fr(22))
@@ -116,8 +117,8 @@ def test_c3_range_lookup_2p22_queries(gctx):
         row = [inv_of.setdefault(int(x), pow((int(x) + beta) % R, -1, R)) for x in q[r * wd:(r + 1) * wd]]
         assert np.array_equal(cport.commit_fr(host.encode_field(row), wd, ctable)[0], got_A[r])
     m_enc = host.encode_field(m)
-    got_m = gctx.download(com_m, Nt // 256 * 96).reshape(-1, 24)
-    want_m = cport.commit_fr(m_enc, 256, ctable[:, :256].copy())
+    got_m = gctx.download(com_m, Nt // m_wd * 96).reshape(-1, 24)
+    want_m = cport.commit_fr(m_enc, m_wd, ctable)
     assert np.array_equal(got_m, want_m)
     # the same lookup with the bucket method for A commits to the same rows
     gctx.set_bucket_commit(2)

@@ -113,7 +113,7 @@ def test_lookup_proof_verifies_with_openings_of_A_and_m(gctx, mapping):
     v = host.decode_field(gctx.random_fr(12))
     dS, dA = gctx.alloc(D * 32), gctx.alloc(D * 32)
     gctx.fr_from_i32(gctx.upload(q), D, dS)
-    com_A, com_m = gctx.alloc(D // wd * 96), gctx.alloc(N // 256 * 96)
+    com_A, com_m = gctx.alloc(D // wd * 96), gctx.alloc(96)     # m: one row of 2^(8/2) * 16 = 256 multiplicities
     if mapping:
         d_out, work = gctx.alloc(D * 32), gctx.alloc(D * 32)
         gctx.fr_from_i32(gctx.upload(mapped[q - low]), D, d_out)
@@ -142,7 +142,7 @@ def test_lookup_proof_verifies_with_openings_of_A_and_m(gctx, mapping):
     m_vals = lk.table("m")
     proof_m = host.hyrax_open(gctx, table, gctx.fr_upload(m_vals), N, 16, 1, v[:8], c, gens_j[0])
     assert proof_m["result"] == finals["m"]
-    com_m_rows = gctx.download(com_m, N // 256 * 96).reshape(-1, 24)
+    com_m_rows = gctx.download(com_m, 96).reshape(-1, 24)
     assert verifier.verify_open(gctx, table, com_m_rows, proof_m, v[:8], c, N, 16, 1, gens_j[0])
     lk.close()
     table.close()

@@ -71,3 +71,32 @@ def test_points_bin_export_and_commit_all(gctx, tmp_path):
             assert gctx.download(out, got.nbytes).tobytes() == got.tobytes()
     gctx.lib.grape_table_destroy(h)
     table.close()
+
+
+def test_rmsnorm_factor_is_the_integer_rsqrt_of_the_model():
+    """The synthesised layers derive their RMSNorm factor as the model does (zzllama/llama/model.py:204,
+    221-226): rms = round(scale / sqrt(mean((x/scale)^2) + eps)).  The integer square root must agree
+    with a float64 evaluation to within one unit of the quantisation step, on inputs of the scale the
+    benchmark uses, and the two rescales that follow must be exact."""
+    import numpy as np
+    from grape_b200 import layer_full
+    from grape_b200.layer import round_div
+    rng = np.random.default_rng(4)
+    scale = 1 << 16
+    x = rng.integers(-(1 << 13), 1 << 13, size=(2, 9, 4096)).astype(np.int64)
+    x[0, 0] = 0                       # an all-zero token: the factor is scale / sqrt(eps)
+    x[0, 1] = (1 << 20)               # a large-magnitude token
+    r = layer_full.rms_factor(x, scale)
+    xr = x.astype(np.float64) / scale
+    f = scale / np.sqrt((xr ** 2).mean(-1) + 1e-5)
+    assert np.all(np.abs(r - f) <= 1.0)
+    assert r[0, 0] == round(scale / np.sqrt(1e-5))
+    shape = layer_full.LayerShape(layer_num=1, tokens=4, dim=64, ffn=96, scale1=256, scale2=512, swiglu_low=-256,
+                                  swiglu_len=512, npoints=64, scale3=1 << 9, exp_low=-511, exp_len=512, softmax_len=512)
+    t = layer_full.synthesize_layer(shape, seed=3, x_range=256, w_std=8.0)
+    inp = t["input"].astype(np.int64)
+    assert np.array_equal(t["rms1"].reshape(1, 4), layer_full.rms_factor(inp, 256))
+    prod = t["rms1"].astype(np.int64) * t["wnorm1"].astype(np.int64).reshape(1, 1, 64)
+    assert np.array_equal(prod, t["rmsw1_q"].astype(np.int64) * 256 + t["rmsw1_rem"])
+    assert np.array_equal(inp * t["rmsw1_q"], t["norm1_q"].astype(np.int64) * 256 + t["norm1_rem"])
+    assert np.abs(t["rmsw1_rem"]).max() <= 128 and np.abs(t["norm1_rem"]).max() <= 128
