@@ -59,7 +59,7 @@ def parse_args():
                     help="layers per batch of the proof timing carried in `layer_proof` (seq 2048); 0 = skip it")
     ap.add_argument("--proof-window-bits", type=int, default=13)
     ap.add_argument("--proof-scope", default="layer", choices=["layer", "ffn"])
-    ap.add_argument("--workload", default="commit", choices=["commit", "matmul", "lookup", "commit-bls12-381", "matmul-sharded", "layer-proof", "fold"],
+    ap.add_argument("--workload", default="commit", choices=["commit", "matmul", "lookup", "lookup-bucket", "commit-bls12-381", "matmul-sharded", "layer-proof", "fold"],
                     help="commit = C4 (the headline); matmul = C2 prove_matmul; lookup = C3 range lookup")
     ap.add_argument("--shrink", type=int, default=1, help="divide the matmul / lookup sizes (profiling cases)")
     ap.add_argument("--rows", type=int, default=0, help="commit only this many rows (reduced case for profiling)")
@@ -695,6 +695,38 @@ def run_secondary(args):
                               "frac_of_hbm": res["fr"]["gbs"] / hbm_peak, "kernel_ms": res["fr"]["kernel_ms"],
                               "note": "32 B and one full field multiplication per element: bound by the multiply pipe"},
                 "kernel_ms": res["int32"]["kernel_ms"], "gpu_launches": int(launches)}
+    elif args.workload == "lookup-bucket":
+        # One range lookup whose rows (2^18 elements) are four times longer than its table (2^16 entries), proved
+        # with the commitment of A by the direct kernel and by the bucket method: same commitments, two timings.
+        D, Nt, msm = (1 << 24) // args.shrink, 1 << 16, 16384
+        gens = wl.make_generators(ctx, msm * 16, 3)
+        table = g.GeneratorTable(ctx, gens, 13, 1)
+        ctx.seed(1)
+        lk = host.Lookup(ctx, -(1 << 15), Nt)
+        q = rng.integers(-(1 << 15), 1 << 15, size=D).astype(np.int32)
+        dq, dS, dA, com = ctx.upload(q), ctx.alloc(D * 32), ctx.alloc(D * 32), ctx.alloc(D // (msm * 16) * 96)
+        vv = host.decode_field(ctx.random_fr((D - 1).bit_length()))
+        res, coms, launches = {}, {}, 0
+        for label, mode in (("direct", 0), ("bucket", 2)):
+            ctx.set_bucket_commit(mode)
+            ts = []
+            for it in range(args.warmup + args.steps):
+                ctx.fr_from_i32(dq, D, dS)
+                l0 = ctx.launches
+                ctx.timer_begin()
+                lk.prove(dS, D, dA, vv, table=table, msm_size=msm, d_com_A=com)
+                ms = ctx.timer_end()
+                if it >= args.warmup:
+                    ts.append(ms)
+                    launches += ctx.launches - l0
+            res[label] = float(np.mean(ts))
+            coms[label] = ctx.download(com, D // (msm * 16) * 96).tobytes()
+        ctx.set_bucket_commit(1)
+        line = {"metric": "lookup_prove_ms (A committed by the bucket method)", "value": res["bucket"], "unit": "ms",
+                "higher_is_better": False, "direct_kernel_ms": res["direct"],
+                "commitments_identical": coms["direct"] == coms["bucket"], "gpu_launches": int(launches),
+                "config": {"workload": f"range lookup, {D} queries, 2^16 table, commitment rows of {msm * 16} elements "
+                                       f"({D // (msm * 16)} rows), 13-bit windows"}}
     elif args.workload == "commit-bls12-381":
         # The C4 shape over BLS12-381 G1 (the reference compiles BN254 only; reported separately).
         wd = args.gens

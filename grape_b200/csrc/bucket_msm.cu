@@ -20,9 +20,9 @@
 //            magnitude after the other and stores each magnitude's sum when it is complete.  Every
 //            lane executes one mixed addition per step; a change of magnitude costs a store, not a
 //            divergent general addition.
-//            2b (k_window_running_sums): one warp per (row, window): lane l takes the magnitudes
-//            (128 l, 128 l + 128] from the top with the running-sum rule (run += bucket, tot += run),
-//            adds 128 l * run, and the warp adds up its 32 totals;
+//            2b (k_window_running_sums): two warps per (row, window): lane k of the 64 takes the
+//            magnitudes (64 k, 64 k + 64] from the top with the running-sum rule (run += bucket,
+//            tot += run), adds 64 k * run, and each warp adds up its 32 totals;
 //   stage 3  the finalize kernel of the fixed-base path recombines the windows (Horner) and adds
 //            the shared point of the padded columns.
 //
@@ -132,13 +132,13 @@ __global__ void __launch_bounds__(128, 4) k_bucket_sums(const Affine* __restrict
   Xyzz acc = Xyzz::inf();
   for (;;) {
     while (pos == next) {  // entry t is complete (possibly empty)
-      acc.store(prow + t);
+      xyzz_canon(acc).store(prow + t);   // the walk keeps lazy residues
       acc = Xyzz::inf();
       t++;
       if (t == t1) return;
       next = orow[t + 1];
     }
-    xyzz_madd(acc, Affine::load_nc(gens + srow[pos]));
+    xyzz_madd_lazy(acc, Affine::load_nc(gens + srow[pos]));
     pos++;
   }
 }
@@ -249,41 +249,47 @@ k_window_buckets(const Affine* __restrict__ P, uint32_t n_bins, const uint32_t* 
   for (; pos < end; pos++) {
     const uint2 en = __ldg(e + pos);
     if (en.y != m_cur) {
-      if (m_cur) run.store(srow + (m_cur - 1));
+      if (m_cur) xyzz_canon(run).store(srow + (m_cur - 1));
       run = Xyzz::inf();
       m_cur = en.y;
     }
     Affine p = Affine::load_nc(prow + (en.x & 0x7fffffffu));
     if (en.x >> 31) p.y = fe_neg(p.y);  // the point at infinity is (0, 0) and stays so
-    xyzz_madd(run, p);
+    xyzz_madd_lazy(run, p);
   }
-  run.store(srow + (m_cur - 1));
+  xyzz_canon(run).store(srow + (m_cur - 1));
 }
 
-// Stage 2b.  One warp per (row, window): sum over magnitudes m of m * S_m.  Lane l takes the magnitudes
-// (base, base + 128], base = 128 l, from the top with the running-sum rule, which leaves
-// tot = sum (m - base) * S_m and run = sum S_m; base * run is added by double-and-add over the five
-// bits of l followed by seven doublings; a shuffle tree adds the 32 totals.
+// Stage 2b.  RS_SPLIT warps per (row, window): sum over magnitudes m of m * S_m.  Lane k of the
+// RS_SPLIT * 32 lanes of a (row, window) takes the magnitudes (base, base + RS_PER_LANE], base =
+// RS_PER_LANE * k, from the top with the running-sum rule, which leaves tot = sum (m - base) * S_m and
+// run = sum S_m; base * run is added by double-and-add over the bits of k followed by log2(RS_PER_LANE)
+// doublings; a shuffle tree adds the 32 totals of a warp and the warps of a (row, window) leave one
+// partial sum each for the finalize kernel.  Two warps of 64 magnitudes per lane instead of one of 128:
+// twice as many units, half as long, so the partial last wave of the grid costs half as much.
 constexpr int RS_THREADS = 128;
-constexpr uint32_t RS_PER_LANE = STAGE2_HALF / 32;
-__global__ void __launch_bounds__(RS_THREADS)
+constexpr uint32_t RS_SPLIT = 2;
+constexpr uint32_t RS_PER_LANE = STAGE2_HALF / (32 * RS_SPLIT);
+__global__ void __launch_bounds__(RS_THREADS, 3)
 k_window_running_sums(const Xyzz* __restrict__ S, uint64_t n_units, Xyzz* __restrict__ partial) {
-  const uint64_t unit = (uint64_t)blockIdx.x * (RS_THREADS / 32) + (threadIdx.x >> 5);
+  const uint64_t unit = (uint64_t)blockIdx.x * (RS_THREADS / 32) + (threadIdx.x >> 5);  // (row, window, part)
   if (unit >= n_units) return;  // whole warps leave together
   const uint32_t lane = threadIdx.x & 31;
-  const Xyzz* s = S + unit * STAGE2_HALF + (uint64_t)lane * RS_PER_LANE;
+  const uint32_t part = (uint32_t)(unit % RS_SPLIT);
+  const uint32_t k = part * 32 + lane;  // index of this lane's magnitude range inside the window
+  const Xyzz* s = S + (unit / RS_SPLIT) * STAGE2_HALF + (uint64_t)k * RS_PER_LANE;
   Xyzz run = Xyzz::inf(), tot = Xyzz::inf();
 #pragma unroll 1
   for (int m = (int)RS_PER_LANE - 1; m >= 0; m--) {
     xyzz_add(run, Xyzz::load(s + m));
     xyzz_add(tot, run);
   }
-  if (lane != 0 && !run.is_inf()) {
+  if (k != 0 && !run.is_inf()) {
     Xyzz acc = Xyzz::inf();
 #pragma unroll 1
-    for (int bit = 4; bit >= 0; bit--) {
+    for (int bit = 31 - __clz(k); bit >= 0; bit--) {
       acc = xyzz_dbl(acc);
-      if ((lane >> bit) & 1u) xyzz_add(acc, run);
+      if ((k >> bit) & 1u) xyzz_add(acc, run);
     }
 #pragma unroll 1
     for (uint32_t v = RS_PER_LANE; v > 1; v >>= 1) acc = xyzz_dbl(acc);
@@ -302,7 +308,7 @@ k_window_running_sums(const Xyzz* __restrict__ S, uint64_t n_units, Xyzz* __rest
 // Returns GRAPE_ERR_INVALID when the shape is not supported (the caller then commits directly).
 int commit_gathered_async(grape_ctx* ctx, const grape_table* t, const uint32_t* d_idx, const uint32_t* d_B,
                           uint32_t n_bins, uint64_t size, uint32_t wd, const void* d_extra, void* d_out) {
-  static_assert(STAGE2_HALF % 32 == 0 && (RS_PER_LANE & (RS_PER_LANE - 1)) == 0, "stage 2b lane ranges");
+  static_assert(STAGE2_HALF % (32 * RS_SPLIT) == 0 && (RS_PER_LANE & (RS_PER_LANE - 1)) == 0, "stage 2b lane ranges");
   if (!t || t->curve != Bn254::ID || wd == 0 || wd > t->n_gens || size % wd != 0 || n_bins < BS_ENTRIES ||
       n_bins % BS_ENTRIES != 0 || n_bins > (1u << 24))
     return GRAPE_ERR_INVALID;
@@ -327,7 +333,7 @@ int commit_gathered_async(grape_ctx* ctx, const grape_table* t, const uint32_t* 
   if ((rc = arena_alloc_t(ctx, (uint64_t)STAGE2_WINDOWS * n_bins, &sorted2))) return rc;
   if ((rc = arena_alloc_t(ctx, (uint64_t)STAGE2_WINDOWS * n_bins, &ent))) return rc;
   if ((rc = arena_alloc_t(ctx, batch * STAGE2_WINDOWS * STAGE2_HALF, &S))) return rc;
-  if ((rc = arena_alloc_t(ctx, rows * STAGE2_WINDOWS, &partial))) return rc;
+  if ((rc = arena_alloc_t(ctx, rows * STAGE2_WINDOWS * RS_SPLIT, &partial))) return rc;
   GRAPE_CUDA_TRY(ctx, cudaFuncSetAttribute(k_row_sort, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)(SORT_PART_BINS * sizeof(uint32_t))));
   // stage 1
@@ -371,15 +377,15 @@ int commit_gathered_async(grape_ctx* ctx, const grape_table* t, const uint32_t* 
         k_window_buckets<<<(uint32_t)((n_threads + WB_THREADS - 1) / WB_THREADS), WB_THREADS, 0, ctx->stream>>>(
             P + r0 * n_bins, n_bins, offs2, ent, slices, slice_len, n_threads, S);
       }
-      const uint64_t n_units = nr * STAGE2_WINDOWS;
+      const uint64_t n_units = nr * STAGE2_WINDOWS * RS_SPLIT;
       k_window_running_sums<<<(uint32_t)((n_units + RS_THREADS / 32 - 1) / (RS_THREADS / 32)), RS_THREADS, 0,
-                              ctx->stream>>>(S, n_units, partial + r0 * STAGE2_WINDOWS);
+                              ctx->stream>>>(S, n_units, partial + r0 * STAGE2_WINDOWS * RS_SPLIT);
       ctx->launches += 2;
     }
   }
   GRAPE_CUDA_TRY(ctx, cudaGetLastError());
   // stage 3: Horner over the windows, extra point, normalisation
-  return finalize_bn254_async(ctx, partial, 1, STAGE2_WINDOWS, STAGE2_BITS, rows, d_out, d_extra);
+  return finalize_bn254_async(ctx, partial, RS_SPLIT, STAGE2_WINDOWS, STAGE2_BITS, rows, d_out, d_extra);
 }
 
 }  // namespace grape

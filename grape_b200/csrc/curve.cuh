@@ -128,6 +128,41 @@ __device__ __forceinline__ void xyzz_madd(XyzzT<F>& acc, const AffineT<F>& q) {
   acc.zzz = fe_mul(acc.zzz, PPP);
 }
 
+// acc += q (q affine, canonical) with the accumulator's coordinates kept as LAZY residues in [0, 2 p):
+// the same formulas, every product without its closing subtraction.  The inner loop of the commitment
+// kernel runs on this; xyzz_canon brings an accumulator back before anything else reads it.
+template <class F>
+__device__ __forceinline__ void xyzz_madd_lazy(XyzzT<F>& acc, const AffineT<F>& q) {
+  if (q.is_inf()) return;
+  if (fe_lis_zero(acc.zz)) {
+    acc = XyzzT<F>{q.x, q.y, F::one(), F::one()};
+    return;
+  }
+  F U2 = fe_lmul(q.x, acc.zz);
+  F S2 = fe_lmul(q.y, acc.zzz);
+  F Pd = fe_lsub(U2, acc.x);
+  F Rd = fe_lsub(S2, acc.y);
+  if (fe_lis_zero(Pd)) {
+    if (fe_lis_zero(Rd)) acc = xyzz_dbl_affine(q);
+    else acc = XyzzT<F>::inf();
+    return;
+  }
+  F PP = fe_lsqr(Pd);
+  F PPP = fe_lmul(Pd, PP);
+  F Q = fe_lmul(acc.x, PP);
+  F X3 = fe_lsub(fe_lsub(fe_lsqr(Rd), PPP), fe_ladd(Q, Q));
+  F Y3 = fe_lsub(fe_lmul(Rd, fe_lsub(Q, X3)), fe_lmul(acc.y, PPP));
+  acc.x = X3;
+  acc.y = Y3;
+  acc.zz = fe_lmul(acc.zz, PP);
+  acc.zzz = fe_lmul(acc.zzz, PPP);
+}
+
+template <class F>
+__device__ __forceinline__ XyzzT<F> xyzz_canon(const XyzzT<F>& p) {
+  return XyzzT<F>{fe_canon(p.x), fe_canon(p.y), fe_canon(p.zzz), fe_canon(p.zz)};
+}
+
 // acc += q (both XYZZ)
 template <class F>
 __device__ __forceinline__ void xyzz_add(XyzzT<F>& acc, const XyzzT<F>& q) {

@@ -684,7 +684,7 @@ __device__ GRAPE_MUL_ATTR Fe<P> fe_mul(const Fe<P>& a, const Fe<P>& b) {
 // the 8 diagonal squares are added: 36 wide multiply-adds instead of 64.  The low half of the 512-bit
 // square is then reduced by the eight steps the multiplication uses and the high half is added on:
 //   (T + m p) / 2^256 = T_hi + (T_lo + m p) / 2^256 < 2 p.
-template <class P>
+template <class P, bool LAZY = false>
 __device__ GRAPE_MUL_ATTR Fe<P> fe_sqr8(const Fe<P>& x) {
   static_assert(P::LIMBS == 8, "eight-limb fields only");
   const uint32_t (&a)[8] = x.v;
@@ -735,9 +735,14 @@ __device__ GRAPE_MUL_ATTR Fe<P> fe_sqr8(const Fe<P>& x) {
 #pragma unroll
   for (int i = 0; i < 8; i++) hi[i] = T[8 + i];
   add8(s2, s, hi);  // below 2 p < 2^255: no carry out
+  Fe<P> r;
+  if (LAZY) {  // operands and result in [0, 2 m): (4 m^2 + 2^256 m) / 2^256 < 2 m
+#pragma unroll
+    for (int i = 0; i < 8; i++) r.v[i] = s2[i];
+    return r;
+  }
   Fe<P>::mod_limbs(m);
   uint32_t borrow = sub8(t, s2, m);
-  Fe<P> r;
 #pragma unroll
   for (int i = 0; i < 8; i++) r.v[i] = borrow ? s2[i] : t[i];
   return r;
@@ -750,6 +755,115 @@ __device__ __forceinline__ Fe<P> fe_sqr(const Fe<P>& a) {
   else
 #endif
     return fe_mul(a, a);
+}
+
+// ---------------------------------------------------------------------------------------------
+// Lazy residues.  Where 4 m < 2^(32 N) (both curves' base fields: BN254 p < 2^254, BLS12-381 p < 2^381
+// on twelve limbs) a value may be kept anywhere in [0, 2 m): the Montgomery product of two such values is
+// below (4 m^2) / 2^(32 N) + m < 2 m WITHOUT the closing conditional subtraction, and sums / differences
+// are brought back into [0, 2 m) by one conditional correction with 2 m.  The commitment inner loop runs
+// on these (fe_lmul, fe_lsqr, fe_ladd, fe_lsub): each product sheds a subtract chain and a select chain.
+// A value is zero mod m iff it is 0 or m (fe_lis_zero); fe_canon returns the canonical residue.
+// ---------------------------------------------------------------------------------------------
+template <class P>
+__device__ __forceinline__ void mod2_limbs(uint32_t (&m2)[P::LIMBS]) {
+  constexpr int N = P::LIMBS;
+#pragma unroll
+  for (int i = 0; i < N; i++) m2[i] = (P::mod(i) << 1) | (i ? (P::mod(i - 1) >> 31) : 0u);
+}
+
+template <class P>
+__device__ __forceinline__ Fe<P> mont_finish_lazy(const uint32_t (&E)[P::LIMBS], const uint32_t (&O)[P::LIMBS]) {
+  constexpr int N = P::LIMBS;
+  uint32_t hi[N];
+#pragma unroll
+  for (int i = 0; i < N - 1; i++) hi[i] = E[i + 1];
+  hi[N - 1] = 0;
+  Fe<P> r;
+  addn(r.v, hi, O);
+  return r;
+}
+
+// a * b / 2^(32 N), operands in [0, 2 m), result in [0, 2 m)
+template <class P>
+__device__ GRAPE_MUL_ATTR Fe<P> fe_lmul(const Fe<P>& a, const Fe<P>& b) {
+  constexpr int N = P::LIMBS;
+  static_assert((P::mod(N - 1) >> 30) == 0, "lazy residues need 4 m < 2^(32 N)");
+  uint32_t E[N], O[N];
+  mul_half<0>(E, a.v, b.v[0]);
+  mul_half<1>(O, a.v, b.v[0]);
+  redc_step<P>(E, O);
+#pragma unroll
+  for (int i = 1; i < N; i++) {
+    uint32_t Nx[N];
+    shift_mad_half<1>(Nx, O[0], E, a.v, b.v[i]);
+    mad_half_top<0>(O, Nx[N - 1], a.v, b.v[i]);
+#pragma unroll
+    for (int k = 0; k < N; k++) {
+      E[k] = O[k];
+      O[k] = Nx[k];
+    }
+    redc_step<P>(E, O);
+  }
+  return mont_finish_lazy<P>(E, O);
+}
+
+template <class P>
+__device__ __forceinline__ Fe<P> fe_lsqr(const Fe<P>& a) {
+#ifndef GRAPE_NO_DEDICATED_SQR
+  if constexpr (P::LIMBS == 8) return fe_sqr8<P, true>(a);
+  else
+#endif
+    return fe_lmul(a, a);
+}
+
+template <class P>
+__device__ __forceinline__ Fe<P> fe_ladd(const Fe<P>& a, const Fe<P>& b) {
+  constexpr int N = P::LIMBS;
+  uint32_t s[N], t[N], m2[N];
+  mod2_limbs<P>(m2);
+  addn(s, a.v, b.v);  // below 4 m: no carry out
+  const uint32_t borrow = subn(t, s, m2);
+  Fe<P> r;
+#pragma unroll
+  for (int i = 0; i < N; i++) r.v[i] = borrow ? s[i] : t[i];
+  return r;
+}
+
+template <class P>
+__device__ __forceinline__ Fe<P> fe_lsub(const Fe<P>& a, const Fe<P>& b) {
+  constexpr int N = P::LIMBS;
+  uint32_t s[N], m2[N];
+  mod2_limbs<P>(m2);
+  const uint32_t borrow = subn(s, a.v, b.v);
+#pragma unroll
+  for (int i = 0; i < N; i++) m2[i] &= borrow;
+  Fe<P> r;
+  addn(r.v, s, m2);
+  return r;
+}
+
+template <class P>
+__device__ __forceinline__ bool fe_lis_zero(const Fe<P>& a) {
+  uint32_t z = 0, e = 0;
+#pragma unroll
+  for (int i = 0; i < P::LIMBS; i++) {
+    z |= a.v[i];
+    e |= a.v[i] ^ P::mod(i);
+  }
+  return z == 0 || e == 0;
+}
+
+template <class P>
+__device__ __forceinline__ Fe<P> fe_canon(const Fe<P>& a) {
+  constexpr int N = P::LIMBS;
+  uint32_t t[N], m[N];
+  Fe<P>::mod_limbs(m);
+  const uint32_t borrow = subn(t, a.v, m);
+  Fe<P> r;
+#pragma unroll
+  for (int i = 0; i < N; i++) r.v[i] = borrow ? a.v[i] : t[i];
+  return r;
 }
 
 // Leave Montgomery form: a / 2^(32 N) mod m (N reduction steps on the bare value).

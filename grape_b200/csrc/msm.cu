@@ -131,16 +131,20 @@ __global__ void __launch_bounds__(128) table_build_kernel(const JacobianT<typena
 }
 
 // ------------------------------------------------------------------------------------------
-// Scalar preparation for Fr scalars: leave Montgomery form and add the signed-digit bias, so the
-// accumulate kernel can read window e_w = bits [c w, c w + c) of (v + bias) and use digit e_w - 2^(c-1).
+// Scalar preparation for Fr scalars: leave Montgomery form, add the signed-digit bias and cut the
+// value into its signed c-bit digits ONCE, stored window-major as 16-bit integers
+// (digits[w][element]).  Window e_w = bits [c w, c w + c) of (v + bias) gives digit e_w - 2^(c-1)
+// (the top window is read unsigned).  The accumulate kernel then reads one digit per addition with
+// consecutive lanes on consecutive addresses, where reading the 32-byte scalar again for every window
+// group cost two scattered 4-byte loads per addition.
 // ------------------------------------------------------------------------------------------
 struct Bias256 {
   uint32_t v[8];
 };
 
 template <class C>
-__global__ void fr_bias_kernel(const uint32_t* __restrict__ in, uint32_t* __restrict__ out,
-                               uint64_t n, Bias256 bias) {
+__global__ void fr_digits_kernel(const uint32_t* __restrict__ in, int16_t* __restrict__ digits, uint64_t n,
+                                 Bias256 bias, uint32_t c, uint32_t total_windows) {
   using Fr = typename C::S;
   uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= n) return;
@@ -148,9 +152,14 @@ __global__ void fr_bias_kernel(const uint32_t* __restrict__ in, uint32_t* __rest
   s = fe_from_mont(s);
   uint32_t r[8];
   add8(r, s.v, bias.v);  // value < 2^255 and bias < 2^255: no carry out
-  uint4* o = reinterpret_cast<uint4*>(out + gid * 8);
-  o[0] = make_uint4(r[0], r[1], r[2], r[3]);
-  o[1] = make_uint4(r[4], r[5], r[6], r[7]);
+  const uint32_t mask = (1u << c) - 1u, half = 1u << (c - 1);
+  for (uint32_t w = 0; w < total_windows; w++) {
+    const uint32_t bit = c * w, word = bit >> 5;
+    const uint32_t lo = word < 8 ? r[word] : 0u, hi = word < 7 ? r[word + 1] : 0u;
+    const uint32_t e = __funnelshift_r(lo, hi, bit & 31) & mask;
+    const int32_t d = (w + 1 == total_windows) ? (int32_t)e : (int32_t)e - (int32_t)half;
+    digits[(uint64_t)w * n + gid] = (int16_t)d;
+  }
 }
 
 // 2^(c-1) at the bottom of every window below the top one
@@ -181,15 +190,6 @@ struct DigitI32 {
   }
 };
 
-// Signed digit of window w of an Fr scalar stored biased (see fr_bias_kernel): 0 = skip.
-__device__ __forceinline__ int32_t fr_digit(const uint32_t* sp, uint32_t w, uint32_t c, uint32_t mask, uint32_t half,
-                                            uint32_t total_windows) {
-  const uint32_t bit = c * w, word = bit >> 5;
-  const uint32_t lo = __ldg(sp + word), hi = word < 7 ? __ldg(sp + word + 1) : 0u;
-  const uint32_t e = __funnelshift_r(lo, hi, bit & 31) & mask;
-  return (w + 1 == total_windows) ? (int32_t)e : (int32_t)e - (int32_t)half;
-}
-
 // Signed digit of window w of |s| + bias (int32 scalars; the sign of s is applied by the caller).
 __device__ __forceinline__ int32_t i32_digit(uint32_t vb, uint32_t w, uint32_t c, uint32_t mask, uint32_t half,
                                              uint32_t total_windows) {
@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(MSM_THREADS, C::MSM_BLOCKS)
 commit_accumulate_kernel(const void* __restrict__ scalars, TableViewT<typename C::F> tab, uint32_t wd,
                          uint32_t total_windows, uint32_t n_chunks, uint32_t chunk_len,
                          uint64_t n_units, XyzzT<typename C::F>* __restrict__ partials,
-                         uint32_t* __restrict__ status, uint32_t inner, uint32_t inner_pad) {
+                         uint32_t* __restrict__ status, uint32_t inner, uint32_t inner_pad, uint64_t n_scalars) {
   using Affine = AffineT<typename C::F>;
   using Xyzz = XyzzT<typename C::F>;
   const uint64_t unit0 = (uint64_t)blockIdx.x * (MSM_THREADS / 32);
@@ -252,14 +252,15 @@ commit_accumulate_kernel(const void* __restrict__ scalars, TableViewT<typename C
     const uint32_t i = column(j);
     const uint64_t idx = row * wd + i;
     if (FR) {
-      const uint32_t* sp = reinterpret_cast<const uint32_t*>(scalars) + idx * 8;
+      // scalars = the digit planes written by fr_digits_kernel: digits[w][element], n_scalars elements each
+      const int16_t* dp = reinterpret_cast<const int16_t*>(scalars) + idx;
       for (uint32_t w = w_lo; w < w_hi; w++) {
-        const int32_t d = fr_digit(sp, w, c, mask, half, total_windows);
+        const int32_t d = __ldg(dp + (uint64_t)w * n_scalars);
         if (d == 0) continue;
         uint32_t mag = d < 0 ? (uint32_t)(-d) : (uint32_t)d;
         Affine p = Affine::load_nc(tab.entry(w - w_lo, mag, i));
         if (d < 0) p.y = fe_neg(p.y);
-        xyzz_madd(acc, p);
+        xyzz_madd_lazy(acc, p);
       }
     } else {
       DigitI32 dg;
@@ -274,7 +275,7 @@ commit_accumulate_kernel(const void* __restrict__ scalars, TableViewT<typename C
         }
         Affine p = Affine::load_nc(tab.entry(w - w_lo, mag, i));
         if ((d < 0) != dg.neg) p.y = fe_neg(p.y);
-        xyzz_madd(acc, p);
+        xyzz_madd_lazy(acc, p);
       }
     }
   }
@@ -283,7 +284,7 @@ commit_accumulate_kernel(const void* __restrict__ scalars, TableViewT<typename C
     __shared__ __align__(16) unsigned char pool_raw[MSM_THREADS * sizeof(Xyzz)];
     Xyzz* pool = reinterpret_cast<Xyzz*>(pool_raw);
     const uint32_t tid = threadIdx.x;
-    acc.store(pool + tid);
+    xyzz_canon(acc).store(pool + tid);   // the loop keeps lazy residues; everything downstream is canonical
     __syncthreads();
 #pragma unroll 1
     for (uint32_t width = 16; width >= 1; width >>= 1) {
@@ -443,7 +444,7 @@ static int launch_commit(grape_ctx* ctx, const grape_table* t, const void* d_sca
     ProfScope prof(ctx);
     commit_accumulate_kernel<C, FR><<<(uint32_t)blocks, MSM_THREADS, 0, ctx->stream>>>(
         d_scalars, make_view<typename C::F>(t), wd, total_windows, n_chunks, chunk_len, units, partials,
-        ctx->d_status, inner, inner_pad);
+        ctx->d_status, inner, inner_pad, rows * (uint64_t)wd);
   }
   const JacobianT<typename C::F>* extra = reinterpret_cast<const JacobianT<typename C::F>*>(d_extra);
   if (n_chunks >= 8 && groups <= FIN_MAX_GROUPS && rows <= 4096)
@@ -532,15 +533,16 @@ static int commit_fr_impl(grape_ctx* ctx, const grape_table* t, const void* d_sc
   const uint32_t groups = (total_windows + t->n_windows - 1) / t->n_windows;
   uint32_t n_chunks = pick_chunks(ctx, rows, wd, groups);
   XyzzT<typename C::F>* partials = nullptr;
-  uint32_t* biased = nullptr;
+  int16_t* digits = nullptr;
   int rc = arena_alloc_t(ctx, rows * groups * n_chunks, &partials);
   if (rc) return rc;
-  rc = arena_alloc_t(ctx, size * 8, &biased);
+  rc = arena_alloc_t(ctx, size * total_windows, &digits);
   if (rc) return rc;
-  fr_bias_kernel<C><<<(uint32_t)((size + 255) / 256), 256, 0, ctx->stream>>>(
-      reinterpret_cast<const uint32_t*>(d_scalars), biased, size, make_bias(t->window_bits, total_windows));
+  fr_digits_kernel<C><<<(uint32_t)((size + 255) / 256), 256, 0, ctx->stream>>>(
+      reinterpret_cast<const uint32_t*>(d_scalars), digits, size, make_bias(t->window_bits, total_windows),
+      t->window_bits, total_windows);
   ctx->launches += 1;
-  return launch_commit<C, true>(ctx, t, biased, rows, wd, total_windows, partials, n_chunks, d_out, inner, inner_pad,
+  return launch_commit<C, true>(ctx, t, digits, rows, wd, total_windows, partials, n_chunks, d_out, inner, inner_pad,
                                d_extra);
 }
 
@@ -922,7 +924,8 @@ extern "C" int grape_commit_i32_static(const void* d_table, uint32_t n_gens, uin
   cudaError_t e = cudaMemsetAsync(st->status, 0, sizeof(uint32_t), s);  // must start at zero
   if (e == cudaSuccess) {
     commit_accumulate_kernel<Bn254, false><<<(uint32_t)blocks, MSM_THREADS, 0, s>>>(
-        d_scalars, view, wd, total_windows, (uint32_t)n_chunks, chunk_len, units, partials, st->status, 0u, 0u);
+        d_scalars, view, wd, total_windows, (uint32_t)n_chunks, chunk_len, units, partials, st->status, 0u, 0u,
+        (uint64_t)0);
     commit_finalize_kernel<Bn254><<<(uint32_t)((rows + 127) / 128), 128, 0, s>>>(partials, (uint32_t)n_chunks, groups,
                                                                           window_bits * n_windows, rows,
                                                                           reinterpret_cast<Jacobian*>(d_out), nullptr);

@@ -95,6 +95,45 @@ def commit_rows_sharded_device(ctx, table, d_scalars_block, block_rows: int, wd:
         gather_rows_device(ctx, d_local, block_rows, d_all, dist, table.jacobian_bytes)
 
 
+def hyrax_open_sharded(ctx, table, d_block, block_rows: int, rows: int, N: int, eval_point, c: int, G_jacobian, dist=None,
+                       z_out=None):
+    """``Hyrax::open`` (src/Hyrax.cu:237-305) of ONE layer's tensor whose `rows` commitment rows (of
+    wd = N * 16 field elements) are dealt to the ranks in contiguous blocks of `block_rows`; `d_block` is
+    this rank's block on its GPU.  The reference folds the row variables of the whole tensor on one GPU
+    (src/Hyrax.cu:263-279); here every rank folds its own rows over the low row variables, ONE all-gather
+    carries the wd-element partial vectors (NCCL, on the library's stream), every rank folds the gathered
+    [ranks][wd] tensor over the remaining (high) row variables, and the opening proper (blinding vector,
+    z, com_d, com_ad) runs on that single row.  Same proof as the unsharded call with the same random
+    stream.  `rows`, `block_rows` and the number of ranks must be powers of two."""
+    import torch
+    from . import host
+    from .host import COM_SCALE, _p
+    world = 1 if dist is None else dist.get_world_size()
+    wd = N * COM_SCALE
+    if block_rows * world != rows or rows & (rows - 1) or world & (world - 1):
+        raise ValueError("rows = ranks * block_rows, all powers of two")
+    lw = max(wd - 1, 0).bit_length()
+    l_local = max(block_rows - 1, 0).bit_length()
+    e = list(eval_point)
+    if len(e) != lw + max(rows - 1, 0).bit_length():
+        raise ValueError("the evaluation point must have log2(rows * wd) coordinates")
+    d_e = ctx.fr_upload(e)
+    d_part = ctx.alloc(wd * 32)
+    if block_rows > 1:
+        ctx.fr_fold(d_block, block_rows * wd, d_e.at(lw * 32), block_rows, wd, d_part)
+    else:
+        ctx._check(ctx.lib.grape_d2d(ctx.handle, d_part.ptr, _p(d_block), wd * 32))
+    if world > 1:
+        d_all = ctx.alloc(world * wd * 32)
+        with torch.cuda.stream(library_stream(ctx)):
+            dist.all_gather_into_tensor(torch_view(d_all.ptr, world * wd * 32), torch_view(d_part.ptr, wd * 32))
+        d_x = ctx.alloc(wd * 32)
+        ctx.fr_fold(d_all, world * wd, d_e.at((lw + l_local) * 32), world, wd, d_x)
+    else:
+        d_x = d_part
+    return host.hyrax_open(ctx, table, d_x, wd, N, 1, e[:lw], c, G_jacobian, z_out=z_out)
+
+
 def commit_rows_sharded(scalars: np.ndarray, wd: int, commit_fn, dist=None, device: str = "cpu") -> np.ndarray:
     """Row commitments of a host int32 tensor with the rows dealt to the ranks in contiguous blocks.
     `commit_fn(block_scalars) -> uint32[block_rows, 24]` commits one block on this rank's GPU

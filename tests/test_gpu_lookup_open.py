@@ -302,3 +302,35 @@ def test_lookup_mid_size_equals_c_oracle(gctx):
     assert host.decode_field(s_claim.reshape(1, 8))[0] == claim
     assert [host.decode_field(ctr[i]) for i in range(ctr.shape[0])] == tr
     lk.close()
+
+
+def test_open_of_row_blocks_equals_open_of_the_whole_tensor(gctx):
+    """The identity behind ``parallel.hyrax_open_sharded``: folding every block of rows over the low row
+    variables, then the stacked partial vectors over the high ones, then opening the single row, gives
+    the proof of the unsharded opening (here the four blocks are folded one after the other on one GPU)."""
+    import random
+    import grape_b200 as g
+    from grape_b200 import host, workloads as wl
+    rnd = random.Random(31)
+    N, rows, P = 4, 16, 4
+    wd = N * 16
+    gens_j = wl.make_generators(gctx, wd, seed=8)
+    table = g.GeneratorTable(gctx, gens_j, 8, 1)
+    t = [rnd.randrange(R) for _ in range(rows * wd)]
+    e = [rnd.randrange(R) for _ in range(pr.log2ceil(rows * wd))]
+    c = rnd.randrange(R)
+    gctx.seed(77)
+    whole = host.hyrax_open(gctx, table, gctx.fr_upload(t), rows * wd, N, 1, e, c, gens_j[0])
+    lw, block = pr.log2ceil(wd), rows // P
+    d_e = gctx.fr_upload(e)
+    d_all = gctx.alloc(P * wd * 32)
+    for r in range(P):
+        d_blk = gctx.fr_upload(t[r * block * wd:(r + 1) * block * wd])
+        gctx.fr_fold(d_blk, block * wd, d_e.at(lw * 32), block, wd, d_all.at(r * wd * 32))
+    d_x = gctx.alloc(wd * 32)
+    gctx.fr_fold(d_all, P * wd, d_e.at((lw + pr.log2ceil(block)) * 32), P, wd, d_x)
+    gctx.seed(77)
+    shard = host.hyrax_open(gctx, table, d_x, wd, N, 1, e[:lw], c, gens_j[0])
+    assert shard["result"] == whole["result"] == pr.partial_eval(list(t), rows * wd, e, rows * wd, 0, 1)[0]
+    assert shard.z_raw.tobytes() == whole.z_raw.tobytes() and shard.com_raw.tobytes() == whole.com_raw.tobytes()
+    table.close()

@@ -35,7 +35,28 @@ def _worker(rank, world, port, q):
             parallel.commit_rows_sharded_device(ctx, table, d_block, block, wd, d_local, d_all, dist, max_bits=16)
         got = ctx.download(d_all, rows * 96).reshape(rows, 24)
         want = cport.commit_i32(s, wd, cport.table_build(gens))
-        q.put((rank, bool(np.array_equal(got, want)), ctx.status()))
+        ok = bool(np.array_equal(got, want))
+        # the opening of the same tensor with its rows dealt to the two ranks: same proof as on one GPU
+        import random
+        from grape_b200 import host
+        from oracle import bn254
+        rnd = random.Random(9)
+        N = wd // 16
+        e = [rnd.randrange(bn254.R) for _ in range((rows * wd - 1).bit_length())] if False else None
+        rows2 = 64                                            # a power of two for the opening
+        e = [rnd.randrange(bn254.R) for _ in range((rows2 * wd - 1).bit_length())]
+        cc = rnd.randrange(bn254.R)
+        d_fr = ctx.alloc(rows2 * wd * 32)
+        ctx.fr_from_i32(ctx.upload(s[:rows2 * wd]), rows2 * wd, d_fr)
+        keep = ctx.clone(d_fr, rows2 * wd * 32)
+        ctx.seed(1234)
+        whole = host.hyrax_open(ctx, table, d_fr, rows2 * wd, N, 1, e, cc, gens[0])
+        ctx.seed(1234)
+        half = rows2 // world
+        shard = parallel.hyrax_open_sharded(ctx, table, keep.at(rank * half * wd * 32), half, rows2, N, e, cc, gens[0], dist)
+        ok = ok and shard["result"] == whole["result"] and shard.z_raw.tobytes() == whole.z_raw.tobytes() \
+            and shard.com_raw.tobytes() == whole.com_raw.tobytes()
+        q.put((rank, ok, ctx.status()))
         table.close()
     finally:
         dist.destroy_process_group()

@@ -1,4 +1,5 @@
-"""The allocation-free commitment entry point must agree, byte for byte, with the regular one.
+"""The allocation-free commitment entry point must agree, byte for byte, with the regular one (and both
+with the C restatement of the reference's commit).
 
 Some embedders cannot allocate device memory at the moment they commit (a framework that owns all
 GPU memory through its own pool, or a latency-critical loop where cudaMalloc's implicit
@@ -34,6 +35,8 @@ def test_static_commit_matches_arena_commit_twice(window_bits, rows, wd):
     assert lib.grape_static_scratch_bytes() == 65536 * 128
     gens = wl.make_generators(ctx, max(wd, 64), seed=21)
     table = g.GeneratorTable(ctx, gens, window_bits, 1)
+    from oracle import cport
+    ctable = cport.table_build(gens)
     rng = np.random.default_rng(window_bits)
     want_out, got_out = ctx.alloc(rows * 96), ctx.alloc(rows * 96)
     for call in range(2):  # two calls in a row share the static array
@@ -48,10 +51,16 @@ def test_static_commit_matches_arena_commit_twice(window_bits, rows, wd):
         assert status == 0
         got = ctx.download(got_out, rows * 96)
         assert got.tobytes() == want.tobytes()
+        assert got.tobytes() == cport.commit_i32(s, wd, ctable[:, :wd].copy()).tobytes()   # and the reference's rows
     # sizes beyond the fixed scratch are refused, not truncated
     big_rows = 65537
     rc, _ = _static_commit(g, ctx, table, want_out, big_rows * wd, wd, 16, got_out)
     assert rc == 5  # GRAPE_ERR_LIMIT
     assert b"limit" in lib.grape_static_error()
+    # a table geometry that grape_table_create would refuse is refused here too
+    rc = lib.grape_commit_i32_static(C.c_void_p(lib.grape_table_data(table.handle)), table.n_gens, 16, 17,
+                                     C.c_void_p(want_out.ptr), rows * wd, wd, 16, C.c_void_p(got_out.ptr),
+                                     C.c_void_p(ctx.stream), None)
+    assert rc == 1 and b"geometry" in lib.grape_static_error()
     table.close()
     ctx.close()
