@@ -356,7 +356,7 @@ def run_own(args):
     # measured up to three times slower).
     ref_cuda = ref_pieces = None
     if world == 1 and headline:
-        ref_cuda = reference_cuda(LAYER_PAIRS // WD, 2, 1)
+        ref_cuda = reference_cuda(LAYER_PAIRS // WD, 3, 3)   # three warm-up steps: an idle GPU takes a while to clock up
         if args.proof_layers:
             ref_pieces = {
                 "range_lookup_2p25": reference_cuda_secondary(

@@ -6,11 +6,13 @@ Python or CPU stand-in for any entry point.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import re
 from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
-LIB_PATH = PKG / "libgrape_b200.so"
+#: the shared library; GRAPE_B200_LIBRARY names another build of it (e.g. one compiled with other flags)
+LIB_PATH = Path(os.environ.get("GRAPE_B200_LIBRARY") or PKG / "libgrape_b200.so")
 HEADER = PKG.parent / "include" / "grape_b200.h"
 
 GRAPE_OK = 0

@@ -281,21 +281,36 @@ commit_accumulate_kernel(const void* __restrict__ scalars, TableViewT<typename C
   }
 
   {
-    __shared__ __align__(16) unsigned char pool_raw[MSM_THREADS * sizeof(Xyzz)];
-    Xyzz* pool = reinterpret_cast<Xyzz*>(pool_raw);
+    // The pool holds the 128 lane sums as 16-byte pieces, piece k of slot t at pool4[k * 128 + t]:
+    // consecutive lanes touch consecutive 16-byte words (a record-per-thread layout would put all lanes
+    // of a quarter warp on the same four banks).
+    constexpr int PIECES = sizeof(Xyzz) / 16;
+    __shared__ uint4 pool4[PIECES * MSM_THREADS];
+    auto put = [&](uint32_t slot, const Xyzz& p) {
+      const uint4* src = reinterpret_cast<const uint4*>(&p);
+#pragma unroll
+      for (int k = 0; k < PIECES; k++) pool4[k * MSM_THREADS + slot] = src[k];
+    };
+    auto get = [&](uint32_t slot) {
+      Xyzz p;
+      uint4* dst = reinterpret_cast<uint4*>(&p);
+#pragma unroll
+      for (int k = 0; k < PIECES; k++) dst[k] = pool4[k * MSM_THREADS + slot];
+      return p;
+    };
     const uint32_t tid = threadIdx.x;
-    xyzz_canon(acc).store(pool + tid);   // the loop keeps lazy residues; everything downstream is canonical
+    put(tid, xyzz_canon(acc));   // the loop keeps lazy residues; everything downstream is canonical
     __syncthreads();
 #pragma unroll 1
     for (uint32_t width = 16; width >= 1; width >>= 1) {
       if (tid < (MSM_THREADS / 32) * width) {
         const uint32_t u = tid / width, k = tid - u * width;
-        Xyzz a = Xyzz::load(pool + u * 32 + k);
-        xyzz_add(a, Xyzz::load(pool + u * 32 + k + width));
+        Xyzz a = get(u * 32 + k);
+        xyzz_add(a, get(u * 32 + k + width));
         if (width == 1) {
           if (unit0 + u < n_units) a.store(partials + unit0 + u);
         } else {
-          a.store(pool + u * 32 + k);
+          put(u * 32 + k, a);
         }
       }
       __syncthreads();

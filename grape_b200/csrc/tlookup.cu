@@ -424,14 +424,15 @@ static int lookup_prove(grape_ctx* ctx, grape_lookup* lk, uint32_t* d_S, uint64_
     return fail(ctx, GRAPE_ERR_INVALID, "lookup: padding needs 0 inside the table range");
   // Commit A by the bucket method?  Cost per row in units of one mixed addition of the direct kernel:
   // direct = elements * windows of the table; bucketed = 1.2 * elements (stage 1: one addition per
-  // element, some spread inside a warp) + table entries * (1.3 for the normalisation + 20 windows *
-  // (1.08 for the bucket sums + 0.19 for the running sums)) = 1.2 * elements + 27 * table entries.
+  // element, some spread inside a warp) + 40 * table entries as MEASURED (64 rows of 2^18 elements over a
+  // 2^16-entry table: 0.53 ms per row against 0.89 ms; on paper 1.3 for the normalisation + 20 windows *
+  // (1.08 for the bucket sums + 0.19 for the running sums) = 27, the rest is lanes idle at slice ends).
   uint32_t* d_idx = nullptr;
   if (table && msm_size && ctx->bucket_mode != 0 && N % 32 == 0) {
     const uint64_t a_wd0 = (uint64_t)msm_size * GRAPE_COM_SCALE;
     const uint64_t valid = (D != Dp && a_wd0 % inner_pad == 0) ? a_wd0 / inner_pad * inner : a_wd0;
     const double direct = (double)valid * ((254 + table->window_bits - 1) / table->window_bits);
-    const double bucketed = 1.2 * (double)valid + 27.0 * N;
+    const double bucketed = 1.2 * (double)valid + 40.0 * N;
     if (ctx->bucket_mode == 2 || bucketed < 0.9 * direct) {
       if ((rc = arena_alloc_t(ctx, (size_t)Dp, &d_idx))) return rc;
     }
