@@ -400,9 +400,23 @@ def run_own(args):
         if world == 1:
             g.commit_i32_host(ctx, table, h_scalars, wd, max_bits=bits, out=h_out)
             return
-        # this rank's block from page-locked host memory, all commitments back to every rank's host
-        ctx._check(lib.grape_h2d(ctx.handle, d_stage.ptr, h_scalars[r0 * wd:r1 * wd].ctypes.data, block * wd * 4))
-        parallel.commit_rows_sharded_device(ctx, table, d_stage, block, wd, d_local, d_out, dist, max_bits=bits)
+        # this rank's block from page-locked host memory in three row slices (1/8, 3/8, 4/8: each copy runs
+        # on the copy stream behind the commitment of the slice before it), then the gather, then all
+        # commitments back to every rank's host
+        import ctypes as C
+        bounds = [0, block // 8, block // 2, block]
+        tickets = []
+        for a, b in zip(bounds[:-1], bounds[1:]):
+            tk = C.c_uint32()
+            ctx._check(lib.grape_h2d_prefetch(ctx.handle, d_stage.at(a * wd * 4),
+                                              h_scalars[(r0 + a) * wd:(r0 + b) * wd].ctypes.data, (b - a) * wd * 4,
+                                              C.byref(tk)))
+            tickets.append(tk.value)
+        for (a, b), tk in zip(zip(bounds[:-1], bounds[1:]), tickets):
+            ctx._check(lib.grape_prefetch_wait(ctx.handle, tk))
+            if b > a:
+                g.commit_i32(ctx, table, d_stage.at(a * wd * 4), (b - a) * wd, wd, d_local.at(a * 96), max_bits=bits)
+        parallel.gather_rows_device(ctx, d_local, block, d_out, dist)
         ctx._check(lib.grape_d2h(ctx.handle, h_out.ctypes.data, d_out.ptr, rows * 96))
 
     def barrier():
