@@ -421,21 +421,22 @@ static int check_table(grape_ctx* ctx, const grape_table* t, uint32_t wd) {
 //   * Few units (less than half of the warps the GPU holds at once): enough chunks to reach that, while
 //     every lane keeps at least two generators.  More lose: every chunk pays its share of the block
 //     reduction (measured on 1024 rows of 1024 generators: one chunk 0.29 ms, five chunks 0.42 ms).
-//   * Otherwise a grid of equal units ends with a partial wave of warps whose cost is about a third of
-//     one unit's duration whatever the grid size; with only a few waves that is 10 to 15 % of the
-//     launch (10 240 units of a 512-row lookup commitment: 4.3 waves).  Units are cut until the grid
-//     has about twelve waves, as long as a chunk keeps 2048 generators (64 additions per lane, the
-//     reduction stays near 3 % of a unit).
+//   * Fewer than two waves of units: cut them until there are two, as long as a chunk keeps 2048
+//     generators (64 additions per lane, the reduction stays near 3 % of a unit).
+//   * Otherwise one chunk.  Cutting units further to shorten the partial last wave of a grid was
+//     measured and does not pay: with 24 704 rows of 4096 generators two chunks per row took 16.9 ms
+//     where one chunk took half of the 49 408-row launch plus 1.4 % (the end of a grid is already
+//     staggered, and every chunk adds its reduction).
 static uint32_t pick_chunks(const grape_ctx* ctx, uint64_t rows, uint32_t wd, uint32_t groups = 1) {
   const uint64_t cap = (uint64_t)ctx->sm_count * 16;  // resident warps: four blocks of four per SM
   const uint64_t units = rows * groups;               // every (row, window group) is a unit of its own
   if (units == 0) return 1;
-  uint64_t want, max_chunks;
+  uint64_t want = 1, max_chunks = 1;
   if (units < cap / 2) {
     want = (cap / 2 + units - 1) / units;
     max_chunks = (wd + 63) / 64;
-  } else {
-    want = (12 * cap + units - 1) / units;
+  } else if (units < 2 * cap) {
+    want = (2 * cap + units - 1) / units;
     max_chunks = wd / 2048;
   }
   if (want > max_chunks) want = max_chunks;
