@@ -63,6 +63,8 @@ def parse_args():
                     help="commit = C4 (the headline); matmul = C2 prove_matmul; lookup = C3 range lookup")
     ap.add_argument("--shrink", type=int, default=1, help="divide the matmul / lookup sizes (profiling cases)")
     ap.add_argument("--rows", type=int, default=0, help="commit only this many rows (reduced case for profiling)")
+    ap.add_argument("--affine", default="", help="B,chunks: commit with the affine-accumulator kernel, B slots per lane "
+                                                 "(0,0 = chosen by its planner); profiling cases")
     ap.add_argument("--gens", type=int, default=WD, help="generators = scalars per row (reduced case for profiling)")
     return ap.parse_args()
 
@@ -366,6 +368,8 @@ def run_own(args):
                 "matmul_c2": reference_cuda_secondary(
                     "matmul-bench", 1, 2, "reference CUDA prove_matmul, A 2048x4096 . B 4096x4096, Fr tensors resident")}
     ctx = g.Context(local_rank)
+    if args.affine:
+        ctx.set_affine_commit(2, *(int(v) for v in args.affine.split(",")))
 
     wd = args.gens
     n = LAYER_PAIRS if not args.rows else args.rows * wd
@@ -469,6 +473,29 @@ def run_own(args):
     e2e_value = n * args.steps / (e2e_ms * 1e-3)
     host_path_matches = bool(np.array_equal(dev_records, h_out))
 
+    # ---- the same commitment by the affine-accumulator kernel (off by default), N = 1 -----------------
+    affine = None
+    if world == 1 and headline and not args.affine:
+        d_alt = ctx.alloc(rows * 96)
+        ctx.set_affine_commit(2)
+        for _ in range(3):   # the first calls grow the scratch arena
+            g.commit_i32(ctx, table, d_scalars, n, wd, d_alt, max_bits=bits)
+        ctx.prof_enable(True)
+        ctx.timer_begin()
+        for _ in range(args.steps):
+            g.commit_i32(ctx, table, d_scalars, n, wd, d_alt, max_bits=bits)
+        alt_ms = ctx.timer_end() / args.steps
+        alt_kernel_ms, alt_launches = ctx.prof_read()
+        ctx.prof_enable(False)
+        ctx.set_affine_commit(0)
+        affine = {"what": "commit_accumulate_affine_kernel: affine accumulators in device memory, one inversion shared "
+                          "by the additions of a batch of rows (5 multiplications + 1 squaring per addition); selectable "
+                          "with grape_commit_set_affine, not the default",
+                  "ms_per_step": alt_ms, "kernel_ms": alt_kernel_ms / max(alt_launches, 1), "value": n / (alt_ms * 1e-3),
+                  "unit": UNIT,
+                  "identical_output": bool(np.array_equal(ctx.download(d_alt, rows * 96).reshape(rows, 24), dev_records))}
+        d_alt.free()
+
     # ---- N > 1: every rank commits the whole layer alone (the check of the sharded result, and the
     # weak-scaling figure: N layers on N GPUs, no collective) --------------------------------------
     multi = None
@@ -569,6 +596,8 @@ def run_own(args):
             "table_bytes": int(2 ** (args.window_bits - 1) * n_windows * wd * 64)}
     if multi is not None:
         line["multi_gpu"] = multi
+    if affine is not None:
+        line["affine_commit"] = affine
     if ref_cuda is not None:
         line["reference_cuda"] = ref_cuda
     if proof is not None:

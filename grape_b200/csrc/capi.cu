@@ -260,6 +260,16 @@ extern "C" int grape_lookup_set_bucket_commit(grape_ctx* ctx, int mode) {
   return GRAPE_OK;
 }
 
+extern "C" int grape_commit_set_affine(grape_ctx* ctx, int mode, int slots_per_lane, int chunks) {
+  if (ctx) grape::make_device_current(ctx);
+  if (!ctx || mode < 0 || mode > 2 || slots_per_lane < 0 || slots_per_lane > 64 || chunks < 0)
+    return GRAPE_ERR_INVALID;
+  ctx->affine_mode = mode;
+  ctx->affine_b = slots_per_lane;
+  ctx->affine_chunks = chunks;
+  return GRAPE_OK;
+}
+
 extern "C" int grape_prof_enable(grape_ctx* ctx, int on) {
   if (ctx) grape::make_device_current(ctx);
   if (!ctx) return GRAPE_ERR_INVALID;

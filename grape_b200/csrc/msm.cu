@@ -198,6 +198,10 @@ __device__ __forceinline__ int32_t i32_digit(uint32_t vb, uint32_t w, uint32_t c
   return (int32_t)((vb >> sh) & mask) - (int32_t)half;
 }
 
+}  // namespace grape
+#include "msm_affine.cuh"
+namespace grape {
+
 // The 32 lane sums of each of the block's four warps become one partial sum per warp through shared
 // memory: the 128 sums are paired off by as few threads as there are pairs (64, 32, 16, 8, 4), which
 // costs the block six warp-wide general additions where a shuffle tree inside every warp costs twenty
@@ -448,7 +452,7 @@ template <class C, bool FR>
 static int launch_commit(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t rows,
                          uint32_t wd, uint32_t total_windows, XyzzT<typename C::F>* partials,
                          uint32_t n_chunks, void* d_out, uint32_t inner = 0, uint32_t inner_pad = 0,
-                         const void* d_extra = nullptr) {
+                         const void* d_extra = nullptr, const AffinePlan* plan = nullptr, uint4* aff_scratch = nullptr) {
   const uint32_t wd_walk = inner ? wd / inner_pad * inner : wd;
   uint32_t chunk_len = (wd_walk + n_chunks - 1) / n_chunks;
   const uint32_t groups = (total_windows + t->n_windows - 1) / t->n_windows;
@@ -456,7 +460,28 @@ static int launch_commit(grape_ctx* ctx, const grape_table* t, const void* d_sca
   if (units == 0) return GRAPE_OK;
   uint64_t blocks = (units + MSM_THREADS / 32 - 1) / (MSM_THREADS / 32);
   if (blocks > 0x7fffffffull) return fail(ctx, GRAPE_ERR_LIMIT, "too many commitment rows for one launch");
-  {
+  if (plan && plan->use) {
+    AffineArgs<typename C::F> a;
+    a.scalars = d_scalars;
+    a.tab = make_view<typename C::F>(t);
+    a.wd = wd;
+    a.total_windows = total_windows;
+    a.groups = groups;
+    a.n_chunks = plan->n_chunks;
+    a.chunk_len = plan->chunk_len;
+    a.n_slots = rows * groups;
+    a.n_units = plan->units;
+    a.B = plan->B;
+    a.partials = partials;
+    a.status = ctx->d_status;
+    a.inner = inner;
+    a.inner_pad = inner_pad;
+    a.n_scalars = rows * (uint64_t)wd;
+    a.scratch = aff_scratch;
+    const uint32_t grid = (uint32_t)((plan->grid_warps + AFF_THREADS / 32 - 1) / (AFF_THREADS / 32));
+    ProfScope prof(ctx);
+    commit_accumulate_affine_kernel<C, FR><<<grid, AFF_THREADS, 0, ctx->stream>>>(a);
+  } else {
     ProfScope prof(ctx);
     commit_accumulate_kernel<C, FR><<<(uint32_t)blocks, MSM_THREADS, 0, ctx->stream>>>(
         d_scalars, make_view<typename C::F>(t), wd, total_windows, n_chunks, chunk_len, units, partials,
@@ -473,6 +498,28 @@ static int launch_commit(grape_ctx* ctx, const grape_table* t, const void* d_sca
         reinterpret_cast<JacobianT<typename C::F>*>(d_out), extra);
   ctx->launches += 2;
   GRAPE_CUDA_TRY(ctx, cudaGetLastError());
+  return GRAPE_OK;
+}
+
+// Chooses between the two accumulation kernels for `rows` rows and carves the scratch either needs.
+template <class C>
+static int plan_commit(grape_ctx* ctx, const grape_table* t, uint64_t rows, uint32_t wd_walk, uint32_t groups,
+                       AffinePlan* plan, uint32_t* n_chunks, XyzzT<typename C::F>** partials, uint4** aff_scratch) {
+  *plan = AffinePlan();
+  *aff_scratch = nullptr;
+  // below a few million additions the extended-coordinate kernel fills the GPU better
+  if (ctx->affine_mode == 2 || (ctx->affine_mode == 1 && (uint64_t)rows * groups * wd_walk * t->n_windows >= (1ull << 22)))
+    *plan = plan_affine(ctx, rows * groups, wd_walk, t->n_windows, ctx->affine_mode == 2,
+                        ctx->affine_mode == 2 ? ctx->affine_b : 0, ctx->affine_mode == 2 ? ctx->affine_chunks : 0);
+  *n_chunks = plan->use ? plan->n_chunks : pick_chunks(ctx, rows, wd_walk, groups);
+  int rc = arena_alloc_t(ctx, rows * groups * *n_chunks, partials);
+  if (rc) return rc;
+  if (plan->use) {
+    constexpr size_t rec = 3 * (C::F::BYTES / 16) * 32 * sizeof(uint4);
+    void* p = nullptr;
+    if ((rc = arena_alloc(ctx, (size_t)plan->grid_warps * plan->B * rec, &p))) return rc;
+    *aff_scratch = reinterpret_cast<uint4*>(p);
+  }
   return GRAPE_OK;
 }
 
@@ -530,12 +577,15 @@ static int commit_i32_impl(grape_ctx* ctx, const grape_table* t, const int32_t* 
                            uint32_t wd, uint32_t max_bits, void* d_out) {
   uint32_t total_windows = (max_bits + t->window_bits - 1) / t->window_bits;
   const uint32_t groups = (total_windows + t->n_windows - 1) / t->n_windows;
-  uint32_t n_chunks = pick_chunks(ctx, rows, wd, groups);
   arena_reset(ctx);
+  AffinePlan plan;
+  uint32_t n_chunks = 1;
   XyzzT<typename C::F>* partials = nullptr;
-  int rc = arena_alloc_t(ctx, rows * groups * n_chunks, &partials);
+  uint4* aff = nullptr;
+  int rc = plan_commit<C>(ctx, t, rows, wd, groups, &plan, &n_chunks, &partials, &aff);
   if (rc) return rc;
-  return launch_commit<C, false>(ctx, t, d_scalars, rows, wd, total_windows, partials, n_chunks, d_out);
+  return launch_commit<C, false>(ctx, t, d_scalars, rows, wd, total_windows, partials, n_chunks, d_out, 0, 0, nullptr,
+                                 &plan, aff);
 }
 
 // The number of windows is chosen so that window_bits * windows exceeds the scalar width: the top
@@ -547,10 +597,13 @@ static int commit_fr_impl(grape_ctx* ctx, const grape_table* t, const void* d_sc
   uint32_t total_windows = (C::SCALAR_BITS + t->window_bits) / t->window_bits;
   if (C::ID == Bn254::ID) total_windows = (254 + t->window_bits - 1) / t->window_bits;
   const uint32_t groups = (total_windows + t->n_windows - 1) / t->n_windows;
-  uint32_t n_chunks = pick_chunks(ctx, rows, wd, groups);
+  const uint32_t wd_walk = inner ? wd / inner_pad * inner : wd;
+  AffinePlan plan;
+  uint32_t n_chunks = 1;
   XyzzT<typename C::F>* partials = nullptr;
+  uint4* aff = nullptr;
   int16_t* digits = nullptr;
-  int rc = arena_alloc_t(ctx, rows * groups * n_chunks, &partials);
+  int rc = plan_commit<C>(ctx, t, rows, wd_walk, groups, &plan, &n_chunks, &partials, &aff);
   if (rc) return rc;
   rc = arena_alloc_t(ctx, size * total_windows, &digits);
   if (rc) return rc;
@@ -559,7 +612,7 @@ static int commit_fr_impl(grape_ctx* ctx, const grape_table* t, const void* d_sc
       t->window_bits, total_windows);
   ctx->launches += 1;
   return launch_commit<C, true>(ctx, t, digits, rows, wd, total_windows, partials, n_chunks, d_out, inner, inner_pad,
-                               d_extra);
+                               d_extra, &plan, aff);
 }
 
 static size_t jacobian_bytes(const grape_table* t) {

@@ -212,6 +212,11 @@ class Context:
         """How lookups commit A: 0 never by the bucket method, 1 when cheaper (default), 2 whenever possible."""
         self._check(self.lib.grape_lookup_set_bucket_commit(self.handle, mode))
 
+    def set_affine_commit(self, mode: int, slots_per_lane: int = 0, chunks: int = 0):
+        """Which kernel accumulates row commitments: 0 extended coordinates only (default), 1 affine accumulators
+        with shared inversions when the cost model favours them, 2 always affine (slots_per_lane / chunks: 0 = chosen)."""
+        self._check(self.lib.grape_commit_set_affine(self.handle, mode, slots_per_lane, chunks))
+
     # -- randomness seam
     def seed(self, seed: int):
         self._check(self.lib.grape_rng_seed(self.handle, seed))

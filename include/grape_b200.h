@@ -257,6 +257,17 @@ const void* grape_lookup_table(const grape_lookup* lk, int which);
  * times longer than the table has entries); 2: whenever the shape allows. */
 int grape_lookup_set_bucket_commit(grape_ctx* ctx, int mode);
 
+/* Which kernel accumulates the row commitments (no reference counterpart; the commitments are the same
+ * group elements either way).  With many rows the additions of different rows are independent, so they
+ * can run in affine coordinates with one shared inversion per batch (6 field multiplications per
+ * addition instead of 10), at the price of keeping the accumulators in device memory.  Measured on a
+ * B200 it gains 8 % on 49 408 rows x 4096 generators and loses below about a hundred million additions,
+ * so it is off unless asked for.
+ * mode 0 (default): never the affine kernel; 1: when the cost model favours it; 2: always, with
+ * slots_per_lane accumulators per lane (up to 64, 0 = chosen) and `chunks` chunks of generators per
+ * block of rows (0 = chosen) -- for measurements. */
+int grape_commit_set_affine(grape_ctx* ctx, int mode, int slots_per_lane, int chunks);
+
 /* tLookupRange::prove (src/tlookup.cu:288-343).  d_S: D queries; when D is not a power of two the
  * rows of length `inner` are padded to `inner_pad` (the reference hard-codes 11008 -> 16384) and
  * d_S, d_A must hold 2^ceil(log2 D) elements.  d_A receives 1/(S+beta); both are consumed.
