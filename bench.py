@@ -617,6 +617,8 @@ def run_secondary(args):
     import grape_b200 as g
     from grape_b200 import host, workloads as wl
     ctx = g.Context(int(os.environ.get("LOCAL_RANK", "0")))
+    if args.affine:
+        ctx.set_affine_commit(2, *(int(v) for v in args.affine.split(",")))
     peaks_file = ROOT / "MEASURED_PEAKS.json"
     hbm_peak = json.loads(peaks_file.read_text())["hbm_gbs"] if peaks_file.exists() else 6650.0
     rng = np.random.default_rng(0xC2)
@@ -976,6 +978,8 @@ def run_layer_proof(args):
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ctx = g.Context(local_rank)
+    if args.affine:
+        ctx.set_affine_commit(2, *(int(v) for v in args.affine.split(",")))
     layers = args.proof_layers or 4
     if dist is not None:
         dist.barrier()

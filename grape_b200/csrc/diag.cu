@@ -112,7 +112,8 @@ __global__ void __launch_bounds__(256) k_int_peak(uint32_t* sink, uint32_t seed)
 }
 
 // Identities that tie the specialised field routines to the plain multiplication, element by element:
-//   dedicated squaring == a * a,   Euclid inverse == Fermat inverse,   a * a^-1 == 1   (a != 0).
+//   dedicated squaring == a * a,   division-step inverse == Fermat inverse == Euclid inverse,
+//   a * a^-1 == 1   (a != 0).
 template <class F>
 __global__ void k_field_check(const uint32_t* __restrict__ in, uint64_t n, uint32_t* __restrict__ bad) {
   const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -122,6 +123,7 @@ __global__ void k_field_check(const uint32_t* __restrict__ in, uint64_t n, uint3
   if (fe_sqr(a) != fe_mul(a, a)) fails |= 1u;
   const F inv = fe_inv(a);
   if (inv != fe_inv_fermat(a)) fails |= 2u;
+  if (inv != fe_inv_kaliski(a)) fails |= 16u;
   if (!a.is_zero() && fe_mul(a, inv) != F::one()) fails |= 4u;
   if (a.is_zero() && !inv.is_zero()) fails |= 8u;
   if (fails) atomicOr(bad, fails);
@@ -133,7 +135,8 @@ using namespace grape;
 
 // field: 0 BN254 Fp, 1 BN254 Fr, 2 BLS12-381 Fp, 3 BLS12-381 Fr.  d_elems: n canonical Montgomery elements
 // (8 or 12 limbs each).  *h_fail_mask = OR over the elements of: 1 squaring differs from a*a, 2 the
-// Euclid inverse differs from the Fermat inverse, 4 a * a^-1 != 1, 8 the inverse of 0 is not 0.
+// inverse (batched division steps) differs from the Fermat inverse, 4 a * a^-1 != 1, 8 the inverse of 0
+// is not 0, 16 the inverse differs from the binary-Euclid inverse.
 extern "C" int grape_diag_field_check(grape_ctx* ctx, int field, const void* d_elems, uint64_t n,
                                       uint32_t* h_fail_mask) {
   if (ctx) grape::make_device_current(ctx);

@@ -379,8 +379,8 @@ int grape_measure_int_peak(grape_ctx* ctx, int kind, double* ops_per_second);
 /* Self-check of the specialised field routines against the plain multiplication (the reference has a
  * dedicated squaring and a Euclid inversion too: include/field/mont_t.cuh:145-192, 1058-1120).
  * field: 0 BN254 Fp, 1 BN254 Fr, 2 BLS12-381 Fp, 3 BLS12-381 Fr; d_elems: n canonical Montgomery
- * elements.  *h_fail_mask = OR over the elements of: 1 squaring != a*a, 2 Euclid inverse != Fermat
- * inverse, 4 a * a^-1 != 1, 8 inverse of 0 != 0. */
+ * elements.  *h_fail_mask = OR over the elements of: 1 squaring != a*a, 2 inverse (batched division
+ * steps) != Fermat inverse, 4 a * a^-1 != 1, 8 inverse of 0 != 0, 16 inverse != binary-Euclid inverse. */
 int grape_diag_field_check(grape_ctx* ctx, int field, const void* d_elems, uint64_t n, uint32_t* h_fail_mask);
 /* Mixed point additions per second on register-resident operands: the commitment kernel's
  * arithmetic with no memory traffic, at the same register budget. */
