@@ -16,9 +16,12 @@
 //   commit_accumulate:  one WARP per (row, window group, chunk of generators), four warps per
 //                       block; a window group is the set of windows the table stores pre-shifted
 //                       (all of them for 16-bit windows over int16 data).  A lane walks its
-//                       generators with stride 32 and keeps one XYZZ accumulator -- it never
-//                       doubles; the 32 accumulators are folded with a shuffle tree (5 general
-//                       additions) and lane 0 writes the partial sum to scratch memory.
+//                       generators with stride 32 and keeps one XYZZ accumulator (lazy residues) -- it
+//                       never doubles; the block's 128 lane sums are paired off through shared
+//                       memory (six warp-wide general additions) and one thread per warp writes
+//                       the partial sum to scratch memory.
+//   commit_accumulate_affine (msm_affine.cuh, selectable): the same sums with affine accumulators
+//                       kept in device memory and one inversion shared by a batch of rows.
 //   commit_finalize:    one thread per row recombines the groups (Horner: window_bits * n_windows
 //                       doublings between groups, paid once per row instead of once per lane),
 //                       adds the chunk partials, normalises (one inversion) and writes the

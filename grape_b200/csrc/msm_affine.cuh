@@ -330,8 +330,8 @@ static AffinePlan plan_affine(const grape_ctx* ctx, uint64_t slots, uint32_t wal
   const double pipes = (double)ctx->sm_count * 4 * 32;
   const double cost_xyzz = (double)slots * walk * tw * AFF_COST_MADD / pipes;
   double best_cost = force ? 1e300 : cost_xyzz * 0.92;  // unforced: switch only for a clear gain
-  for (uint32_t B = force_b ? (uint32_t)force_b : AFF_MAX_B; B >= 8; B -= 8) {
-    if (B > slots && B > 8) continue;
+  for (uint32_t B = force_b ? (uint32_t)force_b : AFF_MAX_B; B >= (force_b ? 1u : 8u); B -= 8) {
+    if (!force_b && B > slots && B > 8) continue;
     const uint64_t blocks = (slots + B - 1) / B;
     for (uint32_t waves = 1; waves <= 4; waves++) {
       uint64_t c = force_chunks ? (uint64_t)force_chunks : waves * R / blocks;

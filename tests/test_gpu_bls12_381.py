@@ -94,6 +94,14 @@ def test_commit_i32_matches_oracle(gctx, window_bits, n_windows, max_bits):
     got = _dec_jac(gctx.download(out, rows * 144))
     want = bls.commit_rows([int(x) for x in t], wd, gens)
     assert got == want
+    # the affine-accumulator kernel on the 12-limb field: same records
+    try:
+        gctx.set_affine_commit(2, 4, 1)
+        out2 = gctx.alloc(rows * 144)
+        g.commit_i32(gctx, table, gctx.upload(t), rows * wd, wd, out2, max_bits=max_bits)
+        assert _dec_jac(gctx.download(out2, rows * 144)) == want
+    finally:
+        gctx.set_affine_commit(0)
     assert got[0] is None
     # the records are canonical: Z is the Montgomery one (or zero for infinity)
     raw = gctx.download(out, rows * 144).tobytes()
