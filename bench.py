@@ -404,11 +404,12 @@ def run_own(args):
         if world == 1:
             g.commit_i32_host(ctx, table, h_scalars, wd, max_bits=bits, out=h_out)
             return
-        # this rank's block from page-locked host memory in three row slices (1/8, 3/8, 4/8: each copy runs
-        # on the copy stream behind the commitment of the slice before it), then the gather, then all
-        # commitments back to every rank's host
+        # this rank's block from page-locked host memory in five row slices (1, 3, 7, 10, 11 of 32, as the
+        # library's own host-buffer entry point cuts them: each copy runs on the copy stream behind the
+        # commitment of the slice before it, only the first, small one is exposed), then the gather, then
+        # all commitments back to every rank's host
         import ctypes as C
-        bounds = [0, block // 8, block // 2, block]
+        bounds = [0] + [block * k // 32 for k in (1, 4, 11, 21)] + [block]
         tickets = []
         for a, b in zip(bounds[:-1], bounds[1:]):
             tk = C.c_uint32()
