@@ -64,7 +64,8 @@ def parse_args():
     ap.add_argument("--shrink", type=int, default=1, help="divide the matmul / lookup sizes (profiling cases)")
     ap.add_argument("--rows", type=int, default=0, help="commit only this many rows (reduced case for profiling)")
     ap.add_argument("--affine", default="", help="B,chunks: commit with the affine-accumulator kernel, B slots per lane "
-                                                 "(0,0 = chosen by its planner); profiling cases")
+                                                 "(0,0 = chosen by its planner), or 'auto': where its planner "
+                                                 "expects a gain; profiling cases")
     ap.add_argument("--gens", type=int, default=WD, help="generators = scalars per row (reduced case for profiling)")
     return ap.parse_args()
 
@@ -339,6 +340,14 @@ def layer_proof(ctx, layers: int, window_bits: int, scope: str, seed: int = 0xC5
     return out
 
 
+def set_affine(ctx, spec: str):
+    """--affine B,chunks forces the affine-accumulator kernel; --affine auto leaves the choice to its planner."""
+    if spec == "auto":
+        ctx.set_affine_commit(1)
+    else:
+        ctx.set_affine_commit(2, *(int(v) for v in spec.split(",")))
+
+
 def run_own(args):
     import grape_b200 as g
     from grape_b200 import parallel, workloads as wl
@@ -369,7 +378,7 @@ def run_own(args):
                     "matmul-bench", 1, 2, "reference CUDA prove_matmul, A 2048x4096 . B 4096x4096, Fr tensors resident")}
     ctx = g.Context(local_rank)
     if args.affine:
-        ctx.set_affine_commit(2, *(int(v) for v in args.affine.split(",")))
+        set_affine(ctx, args.affine)
 
     wd = args.gens
     n = LAYER_PAIRS if not args.rows else args.rows * wd
@@ -488,7 +497,7 @@ def run_own(args):
         alt_ms = ctx.timer_end() / args.steps
         alt_kernel_ms, alt_launches = ctx.prof_read()
         ctx.prof_enable(False)
-        ctx.set_affine_commit(0)
+        ctx.set_affine_commit(-1)
         affine = {"what": "commit_accumulate_affine_kernel: affine accumulators in device memory, one inversion shared "
                           "by the additions of a batch of rows (5 multiplications + 1 squaring per addition); selectable "
                           "with grape_commit_set_affine, not the default",
@@ -619,7 +628,7 @@ def run_secondary(args):
     from grape_b200 import host, workloads as wl
     ctx = g.Context(int(os.environ.get("LOCAL_RANK", "0")))
     if args.affine:
-        ctx.set_affine_commit(2, *(int(v) for v in args.affine.split(",")))
+        set_affine(ctx, args.affine)
     peaks_file = ROOT / "MEASURED_PEAKS.json"
     hbm_peak = json.loads(peaks_file.read_text())["hbm_gbs"] if peaks_file.exists() else 6650.0
     rng = np.random.default_rng(0xC2)
@@ -980,7 +989,7 @@ def run_layer_proof(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ctx = g.Context(local_rank)
     if args.affine:
-        ctx.set_affine_commit(2, *(int(v) for v in args.affine.split(",")))
+        set_affine(ctx, args.affine)
     layers = args.proof_layers or 4
     if dist is not None:
         dist.barrier()

@@ -262,9 +262,10 @@ extern "C" int grape_lookup_set_bucket_commit(grape_ctx* ctx, int mode) {
 
 extern "C" int grape_commit_set_affine(grape_ctx* ctx, int mode, int slots_per_lane, int chunks) {
   if (ctx) grape::make_device_current(ctx);
-  if (!ctx || mode < 0 || mode > 2 || slots_per_lane < 0 || slots_per_lane > 64 || chunks < 0)
+  if (!ctx || mode < -1 || mode > 2 || slots_per_lane < 0 || slots_per_lane > 64 || chunks < 0)
     return GRAPE_ERR_INVALID;
-  ctx->affine_mode = mode;
+  ctx->affine_mode = mode < 0 ? 0 : mode;     // -1: back to what a new context starts with
+  ctx->affine_mode_fr = mode < 0 ? 1 : mode;
   ctx->affine_b = slots_per_lane;
   ctx->affine_chunks = chunks;
   return GRAPE_OK;

@@ -34,9 +34,12 @@ struct grape_ctx {
   int sm_count = 148;
   // commitments of a lookup's A by the bucket method: 0 never, 1 when the cost model favours it, 2 whenever supported
   int bucket_mode = 1;
-  // accumulation of commitments with affine accumulators: 0 never (default), 1 when the cost model
-  // favours it, 2 always with affine_b slots per lane and affine_chunks chunks per row block (0 = chosen)
+  // accumulation of commitments with affine accumulators: 0 never, 1 when the cost model favours it,
+  // 2 always with affine_b slots per lane and affine_chunks chunks per row block (0 = chosen).  Kept
+  // apart for int32 scalars (default 0) and Fr scalars (default 1: the lookups' A tensors, where the
+  // planner's choice was measured to take 8 % off a layer proof).
   int affine_mode = 0;
+  int affine_mode_fr = 1;
   int affine_b = 0, affine_chunks = 0;
   // launch counters (own kernels launched since creation), read by the benchmark
   uint64_t launches = 0;

@@ -507,13 +507,15 @@ static int launch_commit(grape_ctx* ctx, const grape_table* t, const void* d_sca
 // Chooses between the two accumulation kernels for `rows` rows and carves the scratch either needs.
 template <class C>
 static int plan_commit(grape_ctx* ctx, const grape_table* t, uint64_t rows, uint32_t wd_walk, uint32_t groups,
-                       AffinePlan* plan, uint32_t* n_chunks, XyzzT<typename C::F>** partials, uint4** aff_scratch) {
+                       bool fr_scalars, AffinePlan* plan, uint32_t* n_chunks, XyzzT<typename C::F>** partials,
+                       uint4** aff_scratch) {
   *plan = AffinePlan();
   *aff_scratch = nullptr;
+  const int mode = fr_scalars ? ctx->affine_mode_fr : ctx->affine_mode;
   // below a few million additions the extended-coordinate kernel fills the GPU better
-  if (ctx->affine_mode == 2 || (ctx->affine_mode == 1 && (uint64_t)rows * groups * wd_walk * t->n_windows >= (1ull << 22)))
-    *plan = plan_affine(ctx, rows * groups, wd_walk, t->n_windows, ctx->affine_mode == 2,
-                        ctx->affine_mode == 2 ? ctx->affine_b : 0, ctx->affine_mode == 2 ? ctx->affine_chunks : 0);
+  if (mode == 2 || (mode == 1 && (uint64_t)rows * groups * wd_walk * t->n_windows >= (1ull << 22)))
+    *plan = plan_affine(ctx, rows * groups, wd_walk, t->n_windows, mode == 2, mode == 2 ? ctx->affine_b : 0,
+                        mode == 2 ? ctx->affine_chunks : 0);
   *n_chunks = plan->use ? plan->n_chunks : pick_chunks(ctx, rows, wd_walk, groups);
   int rc = arena_alloc_t(ctx, rows * groups * *n_chunks, partials);
   if (rc) return rc;
@@ -585,7 +587,7 @@ static int commit_i32_impl(grape_ctx* ctx, const grape_table* t, const int32_t* 
   uint32_t n_chunks = 1;
   XyzzT<typename C::F>* partials = nullptr;
   uint4* aff = nullptr;
-  int rc = plan_commit<C>(ctx, t, rows, wd, groups, &plan, &n_chunks, &partials, &aff);
+  int rc = plan_commit<C>(ctx, t, rows, wd, groups, false, &plan, &n_chunks, &partials, &aff);
   if (rc) return rc;
   return launch_commit<C, false>(ctx, t, d_scalars, rows, wd, total_windows, partials, n_chunks, d_out, 0, 0, nullptr,
                                  &plan, aff);
@@ -606,7 +608,7 @@ static int commit_fr_impl(grape_ctx* ctx, const grape_table* t, const void* d_sc
   XyzzT<typename C::F>* partials = nullptr;
   uint4* aff = nullptr;
   int16_t* digits = nullptr;
-  int rc = plan_commit<C>(ctx, t, rows, wd_walk, groups, &plan, &n_chunks, &partials, &aff);
+  int rc = plan_commit<C>(ctx, t, rows, wd_walk, groups, true, &plan, &n_chunks, &partials, &aff);
   if (rc) return rc;
   rc = arena_alloc_t(ctx, size * total_windows, &digits);
   if (rc) return rc;

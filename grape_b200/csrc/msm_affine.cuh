@@ -319,6 +319,9 @@ struct AffinePlan {
 // an affine addition 5.8 and a mixed XYZZ addition 9.6; an inversion as seen by a warp whose
 // neighbours keep the multiplier busy meanwhile.
 constexpr double AFF_COST_ADD = 5.8, AFF_COST_MADD = 9.6, AFF_COST_INV = 30.0;
+// This kernel keeps the multiplier pipe 64 % busy where the XYZZ kernel reaches 87 % (twelve warps per SM
+// against sixteen, operands from device memory): measured 28.8 ms where the counts alone say 22.
+constexpr double AFF_PIPE_PENALTY = 1.3;
 
 static AffinePlan plan_affine(const grape_ctx* ctx, uint64_t slots, uint32_t walk, uint32_t tw, bool force,
                               int force_b, int force_chunks) {
@@ -346,7 +349,7 @@ static AffinePlan plan_affine(const grape_ctx* ctx, uint64_t slots, uint32_t wal
       const double steps = (double)(chunk_len / 32) * tw;
       const double unit_cost = steps * (B * AFF_COST_ADD + AFF_COST_INV) + (double)((B + 31) / 32) * 32 * AFF_COST_MADD;
       // a round keeps min(units, R) warps busy: R warps share the pipes
-      const double cost = (double)rounds * unit_cost * (double)R * 32 / pipes;
+      const double cost = AFF_PIPE_PENALTY * (double)rounds * unit_cost * (double)R * 32 / pipes;
       if (cost < best_cost) {
         best_cost = cost;
         best.use = true;

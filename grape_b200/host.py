@@ -213,8 +213,9 @@ class Context:
         self._check(self.lib.grape_lookup_set_bucket_commit(self.handle, mode))
 
     def set_affine_commit(self, mode: int, slots_per_lane: int = 0, chunks: int = 0):
-        """Which kernel accumulates row commitments: 0 extended coordinates only (default), 1 affine accumulators
-        with shared inversions when the cost model favours them, 2 always affine (slots_per_lane / chunks: 0 = chosen)."""
+        """Which kernel accumulates row commitments: 0 extended coordinates only, 1 affine accumulators with
+        shared inversions where the cost model expects a gain, 2 always affine (slots_per_lane / chunks: 0 = chosen).
+        A new context uses 1 for Fr scalars and 0 for int32 scalars; this sets both, -1 restores that."""
         self._check(self.lib.grape_commit_set_affine(self.handle, mode, slots_per_lane, chunks))
 
     # -- randomness seam

@@ -261,11 +261,13 @@ int grape_lookup_set_bucket_commit(grape_ctx* ctx, int mode);
  * group elements either way).  With many rows the additions of different rows are independent, so they
  * can run in affine coordinates with one shared inversion per batch (6 field multiplications per
  * addition instead of 10), at the price of keeping the accumulators in device memory.  Measured on a
- * B200 it gains 8 % on 49 408 rows x 4096 generators and loses below about a hundred million additions,
- * so it is off unless asked for.
- * mode 0 (default): never the affine kernel; 1: when the cost model favours it; 2: always, with
+ * B200 it gains 10 % on 49 408 rows x 4096 generators of int16 scalars, 8 % on a whole layer proof (the
+ * lookups' full-width A tensors) and loses below some tens of millions of additions.
+ * mode 0: never the affine kernel; 1: when its cost model expects a clear gain; 2: always, with
  * slots_per_lane accumulators per lane (up to 64, 0 = chosen) and `chunks` chunks of generators per
- * block of rows (0 = chosen) -- for measurements. */
+ * block of rows (0 = chosen) -- for measurements.  A new context starts with mode 1 for Fr-scalar
+ * commitments (grape_commit_fr, the lookup provers) and mode 0 for int32-scalar ones; this call sets
+ * both, and mode -1 restores that starting state. */
 int grape_commit_set_affine(grape_ctx* ctx, int mode, int slots_per_lane, int chunks);
 
 /* tLookupRange::prove (src/tlookup.cu:288-343).  d_S: D queries; when D is not a power of two the

@@ -37,7 +37,7 @@ def test_affine_commit_i32_matches_oracle(gctx, window_bits, n_windows, slots, c
         gctx.set_affine_commit(2, slots, chunks)
         raw = _commit_i32(gctx, table, arr, wd, 32)
     finally:
-        gctx.set_affine_commit(0)
+        gctx.set_affine_commit(-1)
     want = pr.commit_rows(s, wd, gens)
     assert g.decode_jacobian(raw) == want
     assert raw.tobytes() == b"".join(bn254.jacobian_to_bytes(p) for p in want)
@@ -63,7 +63,7 @@ def test_affine_commit_degenerate_generators(gctx):
         gctx.set_affine_commit(2, 8, 1)
         raw = _commit_i32(gctx, table, arr, wd, 32)
     finally:
-        gctx.set_affine_commit(0)
+        gctx.set_affine_commit(-1)
     assert g.decode_jacobian(raw) == pr.commit_rows(s, wd, gens)
     table.close()
 
@@ -84,7 +84,7 @@ def test_affine_commit_fr_matches_oracle(gctx, window_bits, n_windows, slots, ch
         gctx.set_affine_commit(2, slots, chunks)
         g.commit_fr(gctx, table, d, rows * wd, wd, out)
     finally:
-        gctx.set_affine_commit(0)
+        gctx.set_affine_commit(-1)
     raw = gctx.download(out, rows * 96).reshape(rows, 24)
     assert g.decode_jacobian(raw) == pr.commit_rows(s, wd, gens)
     table.close()
@@ -118,7 +118,7 @@ def test_affine_commit_equals_extended_kernel(gctx, rows, wd, slots, chunks):
                     g.commit_i32(gctx, table, d_i, n, wd, o, max_bits=16)
                 outs.append(gctx.download(o, (n // wd) * 96).tobytes())
             finally:
-                gctx.set_affine_commit(0)
+                gctx.set_affine_commit(-1)
         assert outs[0] == outs[1]
         assert gctx.status() == 0
         table.close()

@@ -101,7 +101,7 @@ def test_commit_i32_matches_oracle(gctx, window_bits, n_windows, max_bits):
         g.commit_i32(gctx, table, gctx.upload(t), rows * wd, wd, out2, max_bits=max_bits)
         assert _dec_jac(gctx.download(out2, rows * 144)) == want
     finally:
-        gctx.set_affine_commit(0)
+        gctx.set_affine_commit(-1)
     assert got[0] is None
     # the records are canonical: Z is the Montgomery one (or zero for infinity)
     raw = gctx.download(out, rows * 144).tobytes()
