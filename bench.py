@@ -213,7 +213,11 @@ def run_reference(args):
     if rank != 0:
         return
     cfg = workload_config()
+    sampler = ClockSampler(0)   # over the whole child process: its table build and warm-up are inside
+    sampler.start()
     ref = reference_cuda(cfg["rows_per_step"], max(args.steps, 1), max(args.warmup, 1))
+    clocks = sampler.stop()
+    clocks["note"] = (clocks.get("note", "") + " sampled while the reference's process ran (set-up, warm-up and timed steps)").strip()
     if ref and "points_per_s" in ref and ref.get("cuda_status") == "no error":
         line = {"impl": "reference", "metric": METRIC, "value": ref["points_per_s"], "unit": UNIT, "n_gpus": args.gpus,
                 "gpus_used": 1, "steps": args.steps, "warmup": ref.get("warmup", 1), "ms_per_step": ref["ms_per_step"],
@@ -225,7 +229,7 @@ def run_reference(args):
                 "e2e": {"value": ref["e2e_points_per_s"], "unit": UNIT, "h2d_bytes_per_step": 0,
                         "d2h_bytes_per_step": 0, "ms_per_step": ref["e2e_ms_per_step"],
                         "note": "the reference's own data movement (cudaMemcpy from pageable memory) is inside"},
-                "gpu_launches": 0, "reference_build": ref["what"],
+                "gpu_launches": 0, "clocks": clocks, "reference_build": ref["what"],
                 "multi_gpu_note": "the reference has no multi-GPU path: at any N its kernels run on one GPU"}
         print(json.dumps(line))
         return
