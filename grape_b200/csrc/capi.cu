@@ -67,6 +67,7 @@ extern "C" int grape_ctx_destroy(grape_ctx* ctx) {
   if (!ctx) return GRAPE_OK;
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
+  if (ctx->g_table) grape_table_destroy(ctx->g_table);
   for (auto& b : ctx->arena) cudaFree(b.ptr);
   if (ctx->dstage) cudaFree(ctx->dstage);
   if (ctx->pinned) cudaFreeHost(ctx->pinned);

@@ -9,6 +9,8 @@
 #include "../../include/grape_b200.h"
 #include "rng.cuh"
 
+struct grape_table;
+
 struct grape_ctx {
   int device = 0;
   cudaStream_t stream = nullptr;
@@ -41,6 +43,10 @@ struct grape_ctx {
   int affine_mode = 0;
   int affine_mode_fr = 1;
   int affine_b = 0, affine_chunks = 0;
+  // fixed-base table of the opening protocol's point G (one generator, 16 x 16-bit windows), built on
+  // the first opening and rebuilt when another G is passed; g_key: the 96 bytes of that G
+  grape_table* g_table = nullptr;
+  unsigned char g_key[96] = {0};
   // launch counters (own kernels launched since creation), read by the benchmark
   uint64_t launches = 0;
   // wall-clock bracket on the stream (grape_timer_begin / grape_timer_end)

@@ -100,6 +100,54 @@ __device__ __forceinline__ XyzzT<F> xyzz_dbl(const XyzzT<F>& p) {
   return r;
 }
 
+// 2 * P with the field operations as calls (see fe_mul_call): for serial doubling loops.
+template <class F>
+__device__ __forceinline__ XyzzT<F> xyzz_dbl_compact(const XyzzT<F>& p) {
+  if (p.is_inf()) return p;
+  F U = fe_dbl(p.y);
+  F V = fe_sqr_call(U);
+  F W = fe_mul_call(U, V);
+  F S = fe_mul_call(p.x, V);
+  F X2 = fe_sqr_call(p.x);
+  F M = fe_add(fe_dbl(X2), X2);
+  XyzzT<F> r;
+  r.x = fe_sub(fe_sqr_call(M), fe_dbl(S));
+  r.y = fe_sub(fe_mul_call(M, fe_sub(S, r.x)), fe_mul_call(W, p.y));
+  r.zz = fe_mul_call(V, p.zz);
+  r.zzz = fe_mul_call(W, p.zzz);
+  return r;
+}
+
+// acc += q (both XYZZ), the field operations as calls.
+template <class F>
+__device__ __forceinline__ void xyzz_add_compact(XyzzT<F>& acc, const XyzzT<F>& q) {
+  if (q.is_inf()) return;
+  if (acc.is_inf()) {
+    acc = q;
+    return;
+  }
+  F U1 = fe_mul_call(acc.x, q.zz);
+  F U2 = fe_mul_call(q.x, acc.zz);
+  F S1 = fe_mul_call(acc.y, q.zzz);
+  F S2 = fe_mul_call(q.y, acc.zzz);
+  F Pd = fe_sub(U2, U1);
+  F Rd = fe_sub(S2, S1);
+  if (Pd.is_zero()) {
+    if (Rd.is_zero()) acc = xyzz_dbl_compact(acc);
+    else acc = XyzzT<F>::inf();
+    return;
+  }
+  F PP = fe_sqr_call(Pd);
+  F PPP = fe_mul_call(Pd, PP);
+  F Q = fe_mul_call(U1, PP);
+  F X3 = fe_sub(fe_sub(fe_sqr_call(Rd), PPP), fe_dbl(Q));
+  F Y3 = fe_sub(fe_mul_call(Rd, fe_sub(Q, X3)), fe_mul_call(S1, PPP));
+  acc.x = X3;
+  acc.y = Y3;
+  acc.zz = fe_mul_call(fe_mul_call(acc.zz, q.zz), PP);
+  acc.zzz = fe_mul_call(fe_mul_call(acc.zzz, q.zzz), PPP);
+}
+
 // acc += q (q affine).  The rare cases branch; the common path is straight-line.
 template <class F>
 __device__ __forceinline__ void xyzz_madd(XyzzT<F>& acc, const AffineT<F>& q) {

@@ -1203,6 +1203,14 @@ __device__ __noinline__ Fe<P> fe_inv(const Fe<P>& a) {
   return fe_mul(fe_mul(x, Fe<P>::r2()), Fe<P>::r2());
 }
 
+// The multiplication and the squaring as real function calls, for code that runs as ONE serial
+// instruction stream (a thread doubling a point a few hundred times): with every product inlined such a
+// loop body is tens of kilobytes and the warp waits on instruction fetch as much as on arithmetic.
+template <class P>
+__device__ __noinline__ Fe<P> fe_mul_call(Fe<P> a, Fe<P> b) { return fe_mul(a, b); }  // by value: in registers
+template <class P>
+__device__ __noinline__ Fe<P> fe_sqr_call(Fe<P> a) { return fe_sqr(a); }
+
 // Signed 32-bit integer -> Montgomery residue; negatives map to m - |x|
 // (reference: int_to_fr, src/fr-tensor.cu:30-39).
 template <class P>

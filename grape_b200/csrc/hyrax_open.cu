@@ -7,6 +7,8 @@
 #include <algorithm>
 #include <vector>
 
+#include <cstring>
+
 #include "ctx.cuh"
 #include "curve.cuh"
 #include "hostfr.hpp"
@@ -76,26 +78,27 @@ __global__ void k_rng_fr_chacha(RngKey key, uint64_t position0, uint64_t n, uint
   }
 }
 
-// out = [s] * P for one Jacobian point and one Fr scalar (Montgomery form): double-and-add, one thread.
-__global__ void k_scalar_mul(const uint32_t* __restrict__ point_jac, const uint32_t* __restrict__ scalar,
-                             uint32_t* __restrict__ out_jac) {
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
-  Jacobian j;
-  j.x = Fp::load(point_jac);
-  j.y = Fp::load(point_jac + 8);
-  j.z = Fp::load(point_jac + 16);
-  Xyzz base = xyzz_from_jacobian(j);
-  Fr s = fe_from_mont(Fr::load(scalar));
-  Xyzz acc = Xyzz::inf();
-  for (int w = 7; w >= 0; w--) {
-    for (int b = 31; b >= 0; b--) {
-      acc = xyzz_dbl(acc);
-      if ((s.v[w] >> b) & 1u) xyzz_add(acc, base);
-    }
+// The opening's second commitment is [sum_ad] * G for the protocol's fixed point G.  A double-and-add
+// by one thread is 254 dependent doublings (1.8 ms with the rest of the GPU idle, as much as the
+// whole rest of an opening), so G gets a fixed-base table of its own (16 windows of 16 bits, 32 MB, built
+// once per context and per G) and the product becomes a one-element commitment: 16 table additions.
+static int g_table_for(grape_ctx* ctx, const void* h_G_jacobian, const uint32_t* d_G, const grape_table** out) {
+  if (ctx->g_table && memcmp(ctx->g_key, h_G_jacobian, sizeof ctx->g_key) == 0) {
+    *out = ctx->g_table;
+    return GRAPE_OK;
   }
-  bool inf = acc.is_inf();
-  Affine a = xyzz_to_affine(acc);
-  store_jacobian_normalised(out_jac, a, inf);
+  if (ctx->g_table) {
+    GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    grape_table_destroy(ctx->g_table);
+    ctx->g_table = nullptr;
+  }
+  grape_table* t = nullptr;
+  int rc = grape_table_create(ctx, d_G, 1, 16, 16, &t);
+  if (rc) return rc;
+  ctx->g_table = t;
+  memcpy(ctx->g_key, h_G_jacobian, sizeof ctx->g_key);
+  *out = t;
+  return GRAPE_OK;
 }
 
 }  // namespace grape
@@ -165,9 +168,10 @@ extern "C" int grape_hyrax_open(grape_ctx* ctx, const grape_table* table, const 
   if ((rc = fold_axis_async<false>(ctx, xp, new_n, d_e, new_n, 1, d_small))) return rc;
   if ((rc = grape_fr_axpy(ctx, xp, d_cG, d_d, d_z, new_n))) return rc;
   if ((rc = fold_axis_async<false>(ctx, d_d, new_n, d_e, new_n, 1, d_small + 8))) return rc;
-  k_scalar_mul<<<1, 32, 0, ctx->stream>>>(d_cG + 8, d_small + 8, d_pts + 24);
-  ctx->launches += 1;
-  GRAPE_CUDA_TRY(ctx, cudaGetLastError());
+  // com_ad = [sum_ad] * G
+  const grape_table* g_table = nullptr;
+  if ((rc = g_table_for(ctx, h_G_jacobian, d_cG + 8, &g_table))) return rc;
+  if ((rc = commit_fr_async(ctx, g_table, d_small + 8, 1, 1, d_pts + 24))) return rc;
   GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(h_result, d_small, 32, cudaMemcpyDeviceToHost, ctx->stream));
   GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(h_z, d_z, (size_t)new_n * 32, cudaMemcpyDeviceToHost, ctx->stream));
   GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(h_com_d, d_pts, 96, cudaMemcpyDeviceToHost, ctx->stream));

@@ -339,15 +339,17 @@ __global__ void __launch_bounds__(128) commit_finalize_kernel(const XyzzT<typena
   uint64_t row = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= rows) return;
   Xyzz acc = Xyzz::inf();
+  // one serial stream per thread: the field operations are calls so that the loop stays in the
+  // instruction cache
 #pragma unroll 1
   for (int g = (int)groups - 1; g >= 0; g--) {
     if (g != (int)groups - 1) {
 #pragma unroll 1
-      for (uint32_t k = 0; k < group_bits; k++) acc = xyzz_dbl(acc);
+      for (uint32_t k = 0; k < group_bits; k++) acc = xyzz_dbl_compact(acc);
     }
     const Xyzz* p = partials + (row * groups + (uint32_t)g) * n_chunks;
 #pragma unroll 1
-    for (uint32_t k = 0; k < n_chunks; k++) xyzz_add(acc, Xyzz::load(p + k));
+    for (uint32_t k = 0; k < n_chunks; k++) xyzz_add_compact(acc, Xyzz::load(p + k));
   }
   if (extra) {  // the same point added to every row (the constant columns skipped by the accumulation)
     JacobianT<typename C::F> e;
@@ -397,9 +399,9 @@ __global__ void __launch_bounds__(FIN_THREADS) commit_finalize_block_kernel(
   for (int g = (int)groups - 1; g >= 0; g--) {
     if (g != (int)groups - 1) {
 #pragma unroll 1
-      for (uint32_t k = 0; k < group_bits; k++) acc = xyzz_dbl(acc);
+      for (uint32_t k = 0; k < group_bits; k++) acc = xyzz_dbl_compact(acc);
     }
-    xyzz_add(acc, Xyzz::load(sums + g));
+    xyzz_add_compact(acc, Xyzz::load(sums + g));
   }
   if (extra) {
     JacobianT<typename C::F> e;
@@ -725,10 +727,12 @@ __global__ void k_scale_point(const uint32_t* __restrict__ point_jac, const uint
   Xyzz base = xyzz_from_jacobian(j);
   Fr s = fe_from_mont(Fr::load(scalar));
   Xyzz acc = Xyzz::inf();
+#pragma unroll 1
   for (int w = 7; w >= 0; w--) {
+#pragma unroll 1
     for (int b = 31; b >= 0; b--) {
-      acc = xyzz_dbl(acc);
-      if ((s.v[w] >> b) & 1u) xyzz_add(acc, base);
+      acc = xyzz_dbl_compact(acc);
+      if ((s.v[w] >> b) & 1u) xyzz_add_compact(acc, base);
     }
   }
   bool inf = acc.is_inf();

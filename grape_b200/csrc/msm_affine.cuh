@@ -5,15 +5,15 @@
 //     lambda = (y2 - y1) / (x2 - x1),   x3 = lambda^2 - x1 - x2,   y3 = lambda (x1 - x3) - y1,
 // and B independent divisions share ONE inversion (Montgomery's trick: prefix products going up, one
 // inversion, two multiplications per element coming back down): 5 multiplications and 1 squaring per
-// addition plus 1/B of an inversion.  The inversion is a shift-and-subtract loop on the plain integer
-// pipe, so it overlaps the other warps' multiplications.
+// addition plus 1/B of an inversion (batched division steps, mostly on the plain integer pipe, so it
+// partly overlaps the other warps' multiplications: measured at 12 % of the kernel for B = 56).
 //
 // Independence comes from ROWS: all rows of a commitment share the generators, so a lane takes the same
 // generator for B different (row, window group) slots and adds one table point to each of its B
 // accumulators per step.  B accumulators of 64 bytes and B prefix products do not fit in registers or
 // shared memory; they live in a scratch region of device memory, laid out so that the 32 lanes of a warp
-// touch consecutive 16-byte words, and every word is read once after it was written (L2 traffic, about
-// 200 bytes per addition).
+// touch consecutive 16-byte words, and every word is read once after it was written (about 320 bytes of
+// L2 / device-memory traffic per addition, table gathers included).
 //
 //   unit            = B consecutive slots x one chunk of generators, one warp; the lanes walk the chunk
 //                     with stride 32 as in the XYZZ kernel
