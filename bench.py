@@ -406,7 +406,8 @@ def run_own(args):
     d_scalars = ctx.upload(h_scalars)                         # whole layer resident (the block is a slice of it)
     d_out = ctx.alloc(rows * 96)                              # all commitments, rank order = row order
     d_local = ctx.alloc(block * 96) if world > 1 else d_out
-    d_stage = ctx.alloc(block * wd * 4) if world > 1 else None
+    d_stage = None
+    h_scalars_dev = ctx.host_device_pointer(h_scalars) if world > 1 else None
     lib = ctx.lib
 
     def step_device():
@@ -417,23 +418,10 @@ def run_own(args):
         if world == 1:
             g.commit_i32_host(ctx, table, h_scalars, wd, max_bits=bits, out=h_out)
             return
-        # this rank's block from page-locked host memory in five row slices (1, 3, 7, 10, 11 of 32, as the
-        # library's own host-buffer entry point cuts them: each copy runs on the copy stream behind the
-        # commitment of the slice before it, only the first, small one is exposed), then the gather, then
-        # all commitments back to every rank's host
-        import ctypes as C
-        bounds = [0] + [block * k // 32 for k in (1, 4, 11, 21)] + [block]
-        tickets = []
-        for a, b in zip(bounds[:-1], bounds[1:]):
-            tk = C.c_uint32()
-            ctx._check(lib.grape_h2d_prefetch(ctx.handle, d_stage.at(a * wd * 4),
-                                              h_scalars[(r0 + a) * wd:(r0 + b) * wd].ctypes.data, (b - a) * wd * 4,
-                                              C.byref(tk)))
-            tickets.append(tk.value)
-        for (a, b), tk in zip(zip(bounds[:-1], bounds[1:]), tickets):
-            ctx._check(lib.grape_prefetch_wait(ctx.handle, tk))
-            if b > a:
-                g.commit_i32(ctx, table, d_stage.at(a * wd * 4), (b - a) * wd, wd, d_local.at(a * 96), max_bits=bits)
+        # this rank's block is read by the kernel where it lies in page-locked host memory (as the
+        # library's host-buffer entry point does at N = 1), then the gather, then all commitments back to
+        # every rank's host
+        g.commit_i32(ctx, table, h_scalars_dev + r0 * wd * 4, block * wd, wd, d_local, max_bits=bits)
         parallel.gather_rows_device(ctx, d_local, block, d_out, dist)
         ctx._check(lib.grape_d2h(ctx.handle, h_out.ctypes.data, d_out.ptr, rows * 96))
 

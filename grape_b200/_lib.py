@@ -145,6 +145,7 @@ def _declare(lib):
 # entry points added by later parts of the library register their signatures here
 _OPTIONAL: dict[str, list] = {
     "grape_commit_set_affine": [C.c_void_p, C.c_int, C.c_int, C.c_int],
+    "grape_host_device_pointer": [C.c_void_p, C.c_void_p, C.POINTER(C.c_void_p)],
     "grape_commit_i32_static": [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint64, C.c_uint32,
                                 C.c_uint32, C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32)],
 }

@@ -226,6 +226,18 @@ extern "C" int grape_host_alloc_pinned(grape_ctx* ctx, size_t bytes, void** h_ou
   return GRAPE_OK;
 }
 
+extern "C" int grape_host_device_pointer(grape_ctx* ctx, const void* h_ptr, void** d_out) {
+  if (ctx) grape::make_device_current(ctx);
+  if (!ctx || !h_ptr || !d_out) return GRAPE_ERR_INVALID;
+  cudaPointerAttributes attr;
+  if (cudaPointerGetAttributes(&attr, h_ptr) != cudaSuccess || attr.type != cudaMemoryTypeHost || !attr.devicePointer) {
+    cudaGetLastError();
+    return fail(ctx, GRAPE_ERR_INVALID, "not a page-locked host buffer");
+  }
+  *d_out = attr.devicePointer;
+  return GRAPE_OK;
+}
+
 extern "C" int grape_host_free_pinned(grape_ctx* ctx, void* h_ptr) {
   if (ctx) grape::make_device_current(ctx);
   if (!ctx) return GRAPE_ERR_INVALID;

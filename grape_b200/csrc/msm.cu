@@ -816,6 +816,32 @@ extern "C" int grape_commit_i32_host(grape_ctx* ctx, const grape_table* t, const
   size_t in_bytes = size * sizeof(int32_t);
   const size_t jac = jacobian_bytes(t);
   size_t out_bytes = rows * jac;
+  // Page-locked scalars are read by the kernel where they lie: every scalar is needed exactly once, the
+  // other warps of an SM cover the longer latency of a read across PCIe, and no slice waits for a copy
+  // (measured on 49 408 rows: 33.3 ms against 34.7 ms for the sliced copies below and 32.3 ms with the
+  // scalars already in device memory).  Pageable buffers take the staged path.
+  {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, h_scalars) == cudaSuccess && attr.type == cudaMemoryTypeHost &&
+        attr.devicePointer != nullptr) {
+      if (out_bytes > ctx->dstage_bytes) {
+        GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        if (ctx->dstage) cudaFree(ctx->dstage);
+        ctx->dstage = nullptr;
+        ctx->dstage_bytes = 0;
+        if (cudaMalloc(&ctx->dstage, out_bytes) != cudaSuccess)
+          return fail(ctx, GRAPE_ERR_NOMEM, "staging buffer allocation failed");
+        ctx->dstage_bytes = out_bytes;
+      }
+      rc = grape_commit_i32(ctx, t, reinterpret_cast<const int32_t*>(attr.devicePointer), size, wd, max_bits,
+                            ctx->dstage);
+      if (rc) return rc;
+      GRAPE_CUDA_TRY(ctx, cudaMemcpyAsync(h_out, ctx->dstage, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+      GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+      return GRAPE_OK;
+    }
+    cudaGetLastError();  // a pointer the runtime does not know is not an error here
+  }
   size_t need = ((in_bytes + 255) & ~size_t(255)) + out_bytes;
   if (need > ctx->dstage_bytes) {
     GRAPE_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));

@@ -183,6 +183,12 @@ class Context:
         self._pinned = getattr(self, "_pinned", []) + [(p.value, buf)]
         return arr
 
+    def host_device_pointer(self, arr: np.ndarray) -> int:
+        """Device-side address of a page-locked numpy array (``pinned_array``): kernels read it in place."""
+        p = C.c_void_p()
+        self._check(self.lib.grape_host_device_pointer(self.handle, arr.ctypes.data, C.byref(p)))
+        return p.value
+
     def measure_int_peak(self, kind: int) -> float:
         """Measured integer-pipe ceiling (ops/s): 0 mad.lo, 1 mad.wide, 2 lo/hi pairs, 3 field muls."""
         v = C.c_double()

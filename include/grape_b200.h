@@ -122,8 +122,11 @@ int grape_commit_i32(grape_ctx* ctx, const grape_table* t, const int32_t* d_scal
  * (src/Hyrax.cu:335-359, kernels :128-167) and single_commit (src/Hyrax.cu:176-185) for one row. */
 int grape_commit_fr(grape_ctx* ctx, const grape_table* t, const void* d_scalars, uint64_t size,
                     uint32_t wd, void* d_out);
-/* Host-buffer form of grape_commit_i32: copies the scalars in, commits, copies the Jacobian
- * records out and synchronises (reference flow: load_data + commit + savebin, test/commit.cu:60-72). */
+/* Host-buffer form of grape_commit_i32: brings the scalars in, commits, copies the Jacobian
+ * records out and synchronises (reference flow: load_data + commit + savebin, test/commit.cu:60-72).
+ * Page-locked scalars (cudaMallocHost / cudaHostAlloc / grape_host_alloc_pinned) are read by the kernel
+ * in place across PCIe; pageable ones are copied in row slices that overlap the commitment of the
+ * slice before.  The buffer must stay valid until the call returns (it synchronises). */
 int grape_commit_i32_host(grape_ctx* ctx, const grape_table* t, const int32_t* h_scalars,
                           uint64_t size, uint32_t wd, uint32_t max_bits, void* h_out);
 
@@ -396,6 +399,10 @@ int grape_prof_read(grape_ctx* ctx, float* total_ms, uint32_t* count);
 /* Page-locked host memory for the host-buffer entry points. */
 int grape_host_alloc_pinned(grape_ctx* ctx, size_t bytes, void** h_out);
 int grape_host_free_pinned(grape_ctx* ctx, void* h_ptr);
+/* The address at which kernels of this device can read a page-locked host buffer (the buffer itself on
+ * systems with unified addressing), or GRAPE_ERR_INVALID when h_ptr is not page-locked.  With it the
+ * device-pointer entry points (grape_commit_i32, ...) take their scalars straight from host memory. */
+int grape_host_device_pointer(grape_ctx* ctx, const void* h_ptr, void** d_out);
 
 #ifdef __cplusplus
 }

@@ -129,6 +129,28 @@ def test_commit_host_buffers_sliced_pipeline(gctx, gens64, rows):
     table.close()
 
 
+def test_commit_host_buffers_page_locked_read_in_place(gctx, gens64):
+    """Page-locked scalars are read by the kernel where they lie (no staging copy); pageable ones are staged:
+    both must give the records of the device-resident entry point, and the address helper refuses pageable memory."""
+    import grape_b200 as g
+    rows = 4500
+    rng = np.random.default_rng(77)
+    pageable = rng.integers(-2**15, 2**15, size=rows * 64).astype(np.int32)
+    pinned = gctx.pinned_array((rows * 64,), np.int32)
+    pinned[...] = pageable
+    table = g.GeneratorTable(gctx, g.encode_jacobian(gens64), 16, 1)
+    a = g.commit_i32_host(gctx, table, pinned, 64, max_bits=16)
+    b = g.commit_i32_host(gctx, table, pageable, 64, max_bits=16)
+    d_out = gctx.alloc(rows * 96)
+    g.commit_i32(gctx, table, gctx.host_device_pointer(pinned), rows * 64, 64, d_out, max_bits=16)
+    c = gctx.download(d_out, rows * 96).reshape(rows, 24)
+    assert np.array_equal(a, b) and np.array_equal(a, c)
+    assert g.decode_jacobian(a[:3]) == pr.commit_rows([int(v) for v in pageable[:3 * 64]], 64, gens64)
+    with pytest.raises(g.GrapeError):
+        gctx.host_device_pointer(pageable)
+    table.close()
+
+
 def test_commit_rejects_bad_shapes(gctx, gens64):
     import grape_b200 as g
     table = g.GeneratorTable(gctx, g.encode_jacobian(gens64), 8, 1)
