@@ -406,7 +406,6 @@ def run_own(args):
     d_scalars = ctx.upload(h_scalars)                         # whole layer resident (the block is a slice of it)
     d_out = ctx.alloc(rows * 96)                              # all commitments, rank order = row order
     d_local = ctx.alloc(block * 96) if world > 1 else d_out
-    d_stage = None
     h_scalars_dev = ctx.host_device_pointer(h_scalars) if world > 1 else None
     lib = ctx.lib
 
@@ -561,7 +560,7 @@ def run_own(args):
     proof = None
     if args.proof_layers and headline:
         table.close()
-        for b in (d_scalars, d_out, d_stage, d_local if world > 1 else None):
+        for b in (d_scalars, d_out, d_local if world > 1 else None):
             if b is not None:
                 b.free()
         barrier()
