@@ -169,11 +169,13 @@ def test_hyrax_open_and_verify(gctx, layer_num, N, rows):
     table.close()
 
 
-@pytest.mark.parametrize("inner,inner_pad,window_bits", [(11, 16, 8), (6, 8, 13), (24, 32, 16)])
-def test_lookup_commitment_of_padded_rows(gctx, inner, inner_pad, window_bits):
+@pytest.mark.parametrize("inner,inner_pad,window_bits,affine", [(11, 16, 8, False), (6, 8, 13, False), (24, 32, 16, False),
+                                                                  (11, 16, 8, True), (6, 8, 13, True)])
+def test_lookup_commitment_of_padded_rows(gctx, inner, inner_pad, window_bits, affine):
     """Rows padded inner -> inner_pad: the padded columns of A all hold 1 / (pad + beta).  The prover
     commits them through one shared point instead of one addition per column and window; the row
-    commitments must still equal a plain commitment of the padded A."""
+    commitments must still equal a plain commitment of the padded A.  With `affine` the accumulation is
+    forced onto the affine-accumulator kernel, which walks the same skipped columns."""
     import grape_b200 as g
     from grape_b200 import host, workloads as wl
     rng = random.Random(inner * 10 + window_bits)
@@ -199,7 +201,12 @@ def test_lookup_commitment_of_padded_rows(gctx, inner, inner_pad, window_bits):
     gctx._check(gctx.lib.grape_h2d(gctx.handle, dS.ptr, s_enc.ctypes.data, D * 32))
     gctx.sync()
     comA = gctx.alloc(Dp // wd * 96)
-    claim, tr = lk.prove(dS, D, dA, v, inner=inner, inner_pad=inner_pad, table=table, msm_size=msm, d_com_A=comA)
+    try:
+        if affine:
+            gctx.set_affine_commit(2, 8, 1)
+        claim, tr = lk.prove(dS, D, dA, v, inner=inner, inner_pad=inner_pad, table=table, msm_size=msm, d_com_A=comA)
+    finally:
+        gctx.set_affine_commit(-1)
     assert claim == want["claim"] and tr == want["transcript"]
     wantA = cport.commit_fr(host.encode_field(want["A"]), wd, ctable)
     assert gctx.download(comA, wantA.nbytes).tobytes() == wantA.tobytes()
